@@ -1,0 +1,442 @@
+// Split-KV decode over the paged bf16 KV cache (one query token per sequence, GQA).
+//
+// HBM-bound: every K and V byte is read exactly once and shared by the g query heads of
+// its kv head.  A persistent grid deals the pages of all (sequence, kv head) pairs out
+// evenly; a CTA's share is a list of segments (runs of pages of one (sequence, kv head)).
+// Inside a CTA one producer warp streams 4 KB page tiles with TMA into a shared-memory
+// ring (128-byte swizzle, one mbarrier pair per slot); four consumer warps take pages
+// round-robin, compute S = Q K^T and O += P V with warp-level tensor-core MMAs
+// (m16n8k16, the g query heads padded to the 16-row tile), keep an online-softmax state
+// per warp, and merge the four states at the end of each segment into one partial
+// (m, l, O) record.  decode_combine_kernel merges the records of a sequence by
+// log-sum-exp (the (m, d) rule of fusor-ml/core/src/composite/softmax.rs:59-82).
+//
+// Replaces the Sq == 1 regime of the reference's fused kernel
+// (fusor-ml/core/src/composite/flash_attention.rs:147-331), which walks all keys serially
+// per output row and re-reads K/V once per query head.
+#pragma once
+#include <cuda.h>
+
+#include "ptx_sm100.cuh"
+
+namespace fusor {
+
+constexpr int DEC_PT = 16;  // tokens per page
+constexpr int DEC_NW = 4;   // consumer warps
+constexpr int DEC_THREADS = (DEC_NW + 1) * 32;
+constexpr int DEC_GP = 8;   // query heads per kv head are padded to 8 rows (g <= 8)
+
+struct DecodeSegment {
+    int b, hk;
+    int page_begin, page_end;  // logical pages of sequence b
+    int kv_len;                // tokens in sequence b
+    int slot;                  // partial record index
+    int cta_page_off;          // index of this segment's first page in the CTA's page stream
+    int pad;
+};
+
+struct DecodeParams {
+    const void* q;
+    int q_dtype;
+    long long q_sb, q_sh;  // element strides of batch and head
+    const int* page_table;
+    int max_pages;
+    int num_pages;
+    const DecodeSegment* segs;
+    const int* cta_seg_start;  // [grid + 1]
+    float* part_o;             // [slots][DEC_GP][D]
+    float* part_ml;            // [slots][DEC_GP][2]  (m in log2 units, l)
+    int Hkv, g;
+    float scale_log2;
+    int ring;
+    int* err;
+};
+
+template <int D>
+struct DecodeSmem {
+    static constexpr int PAGE_BYTES = DEC_PT * D * 2;
+    static constexpr int MERGE_FLOATS = DEC_NW * DEC_GP * (D + 2);
+    static size_t bytes(int ring) {
+        return 1024 + (size_t)ring * 2 * PAGE_BYTES + MERGE_FLOATS * 4 + (size_t)ring * 16 + 64;
+    }
+};
+
+template <int D>
+__global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK,
+                                                                     const __grid_constant__ CUtensorMap tmV,
+                                                                     const DecodeParams P) {
+    constexpr int PAGE_BYTES = DecodeSmem<D>::PAGE_BYTES;
+    constexpr int HALF_BYTES = DEC_PT * 128;  // one 64-column half of a page tile
+    extern __shared__ uint8_t dec_smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_smem_raw) + 1023) & ~uintptr_t(1023));
+    const int R = P.ring;
+    uint8_t* ksm = base;
+    uint8_t* vsm = base + (size_t)R * PAGE_BYTES;
+    float* merge_o = reinterpret_cast<float*>(vsm + (size_t)R * PAGE_BYTES);  // [NW][GP][D]
+    float* merge_ml = merge_o + DEC_NW * DEC_GP * D;                            // [NW][GP][2]
+    uint64_t* full = reinterpret_cast<uint64_t*>(merge_ml + DEC_NW * DEC_GP * 2);
+    uint64_t* empty = full + R;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + R);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int i = 0; i < R; ++i) {
+            mbar_init(full + i, 1);
+            mbar_init(empty + i, 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    __syncthreads();
+
+    const int seg_begin = P.cta_seg_start[blockIdx.x];
+    const int seg_end = P.cta_seg_start[blockIdx.x + 1];
+
+    if (warp == DEC_NW) {
+        // ------------------------------------------------------------------ producer warp
+        int i = 0;
+        bool ok = true;
+        for (int sg = seg_begin; sg < seg_end && ok; ++sg) {
+            const DecodeSegment S = P.segs[sg];
+            const int* pt = P.page_table + (long long)S.b * P.max_pages;
+            for (int p0 = S.page_begin; p0 < S.page_end && ok; p0 += 32) {
+                const int n = min(32, S.page_end - p0);
+                const int my_phys = (lane < n) ? pt[p0 + lane] : 0;
+                for (int j = 0; j < n && ok; ++j, ++i) {
+                    int phys = __shfl_sync(0xffffffffu, my_phys, j);
+                    int good = 1;
+                    if (lane == 0) {
+                        const int slot = i % R, use = i / R;
+                        if (use > 0) good = mbar_wait(empty + slot, (use - 1) & 1, abort_flag, P.err) ? 1 : 0;
+                        if (good) {
+                            if (phys < 0 || phys >= P.num_pages) {  // record and read page 0 instead
+                                atomicExch(P.err, kErrBadPage);
+                                phys = 0;
+                            }
+                            const int row = (phys * P.Hkv + S.hk) * DEC_PT;
+                            mbar_arrive_expect_tx(full + slot, 2 * PAGE_BYTES);
+#pragma unroll
+                            for (int hf = 0; hf < D / 64; ++hf) {
+                                tma_load_2d(ksm + (size_t)slot * PAGE_BYTES + hf * HALF_BYTES, &tmK, full + slot,
+                                            hf * 64, row);
+                                tma_load_2d(vsm + (size_t)slot * PAGE_BYTES + hf * HALF_BYTES, &tmV, full + slot,
+                                            hf * 64, row);
+                            }
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, good, 0) != 0;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ consumer warps
+        const int r = lane >> 2;          // row of the 16-row MMA tile = query head within the group
+        const int cq = (lane & 3) * 2;    // column pair inside an 8-wide tile
+        const bool row_valid = r < P.g;
+        bool aborted = false;
+        // ldmatrix lane geometry
+        const int lm_j = lane >> 3, lm_r = lane & 7;
+        const uint32_t ksm_u = smem_u32(ksm), vsm_u = smem_u32(vsm);
+
+        for (int sg = seg_begin; sg < seg_end; ++sg) {
+            const DecodeSegment S = P.segs[sg];
+            // Q fragments: rows >= g are zero.
+            uint32_t qa[D / 16][2];
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                qa[ks][0] = 0;
+                qa[ks][1] = 0;
+            }
+            if (row_valid) {
+                const long long qoff = (long long)S.b * P.q_sb + (long long)(S.hk * P.g + r) * P.q_sh;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const int d0 = ks * 16 + cq;
+                    if (P.q_dtype == 1) {
+                        const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(P.q) + qoff;
+                        qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp + d0);
+                        qa[ks][1] = *reinterpret_cast<const uint32_t*>(qp + d0 + 8);
+                    } else {
+                        const float* qp = reinterpret_cast<const float*>(P.q) + qoff;
+                        qa[ks][0] = pack_bf16(qp[d0], qp[d0 + 1]);
+                        qa[ks][1] = pack_bf16(qp[d0 + 8], qp[d0 + 9]);
+                    }
+                }
+            }
+            float m_run = -INFINITY, l_run = 0.0f;
+            float o[D / 8][4];
+#pragma unroll
+            for (int nd = 0; nd < D / 8; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.0f;
+
+            const int n_pages = S.page_end - S.page_begin;
+            // first page of this segment (in CTA stream numbering) that belongs to this warp
+            int i = S.cta_page_off + ((warp - S.cta_page_off % DEC_NW + DEC_NW) % DEC_NW);
+            for (; i < S.cta_page_off + n_pages; i += DEC_NW) {
+                if (aborted) break;
+                const int slot = i % R;
+                const bool got = mbar_wait(full + slot, (i / R) & 1, abort_flag, P.err);
+                if (!__all_sync(0xffffffffu, got)) {
+                    aborted = true;
+                    break;
+                }
+                const int tok0 = (S.page_begin + (i - S.cta_page_off)) * DEC_PT;
+                const uint32_t kb = ksm_u + slot * PAGE_BYTES, vb = vsm_u + slot * PAGE_BYTES;
+
+                // ---- S = Q K^T for 16 tokens (two 8-token tiles)
+                float s[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+                for (int kp = 0; kp < D / 32; ++kp) {
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        const int token = nt * 8 + lm_r;
+                        const int cc = kp * 4 + lm_j;  // 16-byte chunk of the row, 0..D/8-1
+                        const uint32_t addr =
+                            kb + (cc >> 3) * HALF_BYTES + token * 128 + (((cc & 7) ^ (token & 7)) << 4);
+                        uint32_t bfr[4];
+                        ldmatrix_x4(bfr, addr);
+                        const uint32_t a0[4] = {qa[2 * kp][0], 0u, qa[2 * kp][1], 0u};
+                        const uint32_t a1[4] = {qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u};
+                        mma_bf16_16816(s[nt], a0, bfr[0], bfr[1]);
+                        mma_bf16_16816(s[nt], a1, bfr[2], bfr[3]);
+                    }
+                }
+                // ---- online softmax on this thread's 4 scores of row r
+                float t[4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int tok = tok0 + nt * 8 + cq + e;
+                        t[nt * 2 + e] = tok < S.kv_len ? s[nt][e] * P.scale_log2 : -INFINITY;
+                    }
+                float tmax = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3]));
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+                const float m_new = fmaxf(m_run, tmax);
+                const float m_sub = (m_new == -INFINITY) ? 0.0f : m_new;
+                const float alpha = fast_exp2(m_run - m_sub);
+                m_run = m_new;
+                __nv_bfloat162 p01 = __floats2bfloat162_rn(fast_exp2(t[0] - m_sub), fast_exp2(t[1] - m_sub));
+                __nv_bfloat162 p23 = __floats2bfloat162_rn(fast_exp2(t[2] - m_sub), fast_exp2(t[3] - m_sub));
+                // the row sum uses the rounded weights the MMA will use
+                l_run = l_run * alpha + (__low2float(p01) + __high2float(p01)) + (__low2float(p23) + __high2float(p23));
+                const uint32_t pa[4] = {*reinterpret_cast<uint32_t*>(&p01), 0u, *reinterpret_cast<uint32_t*>(&p23), 0u};
+#pragma unroll
+                for (int nd = 0; nd < D / 8; ++nd) {
+                    o[nd][0] *= alpha;
+                    o[nd][1] *= alpha;
+                }
+                // ---- O += P V
+#pragma unroll
+                for (int ndp = 0; ndp < D / 16; ++ndp) {
+                    const int token = (lm_j & 1) * 8 + lm_r;
+                    const int cc = ndp * 2 + (lm_j >> 1);
+                    const uint32_t addr = vb + (cc >> 3) * HALF_BYTES + token * 128 + (((cc & 7) ^ (token & 7)) << 4);
+                    uint32_t bfr[4];
+                    ldmatrix_x4_trans(bfr, addr);
+                    mma_bf16_16816(o[2 * ndp], pa, bfr[0], bfr[1]);
+                    mma_bf16_16816(o[2 * ndp + 1], pa, bfr[2], bfr[3]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + slot);
+            }
+
+            // ---- merge the consumer warps' states of this segment
+            l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+            l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+            if (r < DEC_GP) {
+                float* mo = merge_o + (warp * DEC_GP + r) * D;
+#pragma unroll
+                for (int nd = 0; nd < D / 8; ++nd)
+                    *reinterpret_cast<float2*>(mo + nd * 8 + cq) = make_float2(o[nd][0], o[nd][1]);
+                if ((lane & 3) == 0) {
+                    merge_ml[(warp * DEC_GP + r) * 2 + 0] = m_run;
+                    merge_ml[(warp * DEC_GP + r) * 2 + 1] = l_run;
+                }
+            }
+            named_bar_sync(1, DEC_NW * 32);
+            for (int idx = tid; idx < P.g * D; idx += DEC_NW * 32) {
+                const int rr = idx / D, d = idx - rr * D;
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < DEC_NW; ++w) M = fmaxf(M, merge_ml[(w * DEC_GP + rr) * 2]);
+                float acc = 0.0f, L = 0.0f;
+#pragma unroll
+                for (int w = 0; w < DEC_NW; ++w) {
+                    const float mw = merge_ml[(w * DEC_GP + rr) * 2];
+                    const float a = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - M);
+                    acc += a * merge_o[(w * DEC_GP + rr) * D + d];
+                    L += a * merge_ml[(w * DEC_GP + rr) * 2 + 1];
+                }
+                if (!aborted) {
+                    P.part_o[((long long)S.slot * DEC_GP + rr) * D + d] = acc;
+                    if (d == 0) {
+                        P.part_ml[((long long)S.slot * DEC_GP + rr) * 2 + 0] = M;
+                        P.part_ml[((long long)S.slot * DEC_GP + rr) * 2 + 1] = L;
+                    }
+                }
+            }
+            named_bar_sync(1, DEC_NW * 32);
+        }
+    }
+}
+
+// Merges the partial records of each (sequence, query head).
+//   mode 0: out[b][h][0][:] = sum_i O_i 2^(m_i - M) / L        (dtype f32 or bf16, strided)
+//   mode 1: partial[b][h][:] = { M ln2, L, sum_i O_i 2^(m_i - M) }   (f32, packed [B][Hq][D+2])
+struct CombineParams {
+    const float* part_o;
+    const float* part_ml;
+    const int* seq_slot_begin;  // [B*Hkv + 1]
+    void* out;
+    int out_dtype;
+    long long o_sb, o_sh;
+    int Hq, Hkv, g, D;
+    int mode;
+};
+
+__global__ void decode_combine_kernel(const CombineParams P) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int seq = b * P.Hkv + h / P.g, rr = h % P.g;
+    const int s0 = P.seq_slot_begin[seq], s1 = P.seq_slot_begin[seq + 1];
+    float M = -INFINITY;
+    for (int s = s0; s < s1; ++s) M = fmaxf(M, P.part_ml[((long long)s * DEC_GP + rr) * 2]);
+    float L = 0.0f;
+    for (int s = s0; s < s1; ++s) {
+        const float mw = P.part_ml[((long long)s * DEC_GP + rr) * 2];
+        if (mw != -INFINITY) L += P.part_ml[((long long)s * DEC_GP + rr) * 2 + 1] * fast_exp2(mw - M);
+    }
+    for (int d = threadIdx.x; d < P.D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = s0; s < s1; ++s) {
+            const float mw = P.part_ml[((long long)s * DEC_GP + rr) * 2];
+            if (mw != -INFINITY) acc += P.part_o[((long long)s * DEC_GP + rr) * P.D + d] * fast_exp2(mw - M);
+        }
+        if (P.mode == 0) {
+            const long long idx = (long long)b * P.o_sb + (long long)h * P.o_sh + d;
+            const float v = acc / L;
+            if (P.out_dtype == 0) reinterpret_cast<float*>(P.out)[idx] = v;
+            else reinterpret_cast<__nv_bfloat16*>(P.out)[idx] = __float2bfloat16_rn(v);
+        } else {
+            float* rec = reinterpret_cast<float*>(P.out) + ((long long)b * P.Hq + h) * (P.D + 2);
+            rec[2 + d] = acc;
+            if (d == 0) {
+                rec[0] = M * 0.6931471805599453f;
+                rec[1] = L;
+            }
+        }
+    }
+}
+
+// parts [n_parts][n_rows][D+2] (m in natural-log units) -> out [n_rows][D]
+__global__ void lse_combine_kernel(const float* parts, int n_parts, long long n_rows, int D, float* out) {
+    const long long row = blockIdx.x;
+    const long long rec = D + 2;
+    float M = -INFINITY;
+    for (int p = 0; p < n_parts; ++p) {
+        const float* pr = parts + ((long long)p * n_rows + row) * rec;
+        if (pr[1] != 0.0f) M = fmaxf(M, pr[0]);
+    }
+    float L = 0.0f;
+    for (int p = 0; p < n_parts; ++p) {
+        const float* pr = parts + ((long long)p * n_rows + row) * rec;
+        if (pr[1] != 0.0f) L += pr[1] * __expf(pr[0] - M);
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int p = 0; p < n_parts; ++p) {
+            const float* pr = parts + ((long long)p * n_rows + row) * rec;
+            if (pr[1] != 0.0f) acc += pr[2 + d] * __expf(pr[0] - M);
+        }
+        out[row * D + d] = acc / L;
+    }
+}
+
+// ---------------------------------------------------------------------------------- cache maintenance
+// Appends n new rows per (sequence, kv head): k_new/v_new [B][Hkv][n][D] (strided, f32 or bf16) -> pages.
+struct AppendParams {
+    const void* k_new;
+    const void* v_new;
+    int k_dtype, v_dtype;
+    long long ks[3], vs[3];
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+    const int* page_table;
+    const int* len_before;  // [B]
+    int max_pages, Hkv, D, n, B;
+};
+
+__global__ void kvcache_append_kernel(const AppendParams P) {
+    const long long total = (long long)P.B * P.Hkv * P.n * P.D;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int d = (int)(i % P.D);
+        const int t = (int)((i / P.D) % P.n);
+        const int hk = (int)((i / ((long long)P.D * P.n)) % P.Hkv);
+        const int b = (int)(i / ((long long)P.D * P.n * P.Hkv));
+        const int pos = P.len_before[b] + t;
+        const int page = P.page_table[(long long)b * P.max_pages + pos / DEC_PT];
+        const long long dst = (((long long)page * P.Hkv + hk) * DEC_PT + pos % DEC_PT) * P.D + d;
+        const long long ksrc = b * P.ks[0] + hk * P.ks[1] + t * P.ks[2] + d;
+        const long long vsrc = b * P.vs[0] + hk * P.vs[1] + t * P.vs[2] + d;
+        const float kf = P.k_dtype == 0 ? reinterpret_cast<const float*>(P.k_new)[ksrc]
+                                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.k_new)[ksrc]);
+        const float vf = P.v_dtype == 0 ? reinterpret_cast<const float*>(P.v_new)[vsrc]
+                                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.v_new)[vsrc]);
+        P.k_pages[dst] = __float2bfloat16_rn(kf);
+        P.v_pages[dst] = __float2bfloat16_rn(vf);
+    }
+}
+
+// Dense export: out [B][Hkv][len][D] (strided, f32 or bf16); rows past a sequence's length are zero.
+// `skip[b]` tokens at the front of sequence b have been evicted and are not exported.
+struct GatherParams {
+    void* k_out;
+    void* v_out;
+    int k_dtype, v_dtype;
+    long long ks[3], vs[3];
+    const __nv_bfloat16* k_pages;
+    const __nv_bfloat16* v_pages;
+    const int* page_table;
+    const int* kv_len;  // [B]
+    int max_pages, Hkv, D, len, B;
+};
+
+__global__ void kvcache_gather_kernel(const GatherParams P) {
+    const long long total = (long long)P.B * P.Hkv * P.len * P.D;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int d = (int)(i % P.D);
+        const int t = (int)((i / P.D) % P.len);
+        const int hk = (int)((i / ((long long)P.D * P.len)) % P.Hkv);
+        const int b = (int)(i / ((long long)P.D * P.len * P.Hkv));
+        float kf = 0.0f, vf = 0.0f;
+        if (t < P.kv_len[b]) {
+            const int page = P.page_table[(long long)b * P.max_pages + t / DEC_PT];
+            const long long src = (((long long)page * P.Hkv + hk) * DEC_PT + t % DEC_PT) * P.D + d;
+            kf = __bfloat162float(P.k_pages[src]);
+            vf = __bfloat162float(P.v_pages[src]);
+        }
+        const long long kd = b * P.ks[0] + hk * P.ks[1] + t * P.ks[2] + d;
+        const long long vd = b * P.vs[0] + hk * P.vs[1] + t * P.vs[2] + d;
+        if (P.k_dtype == 0) reinterpret_cast<float*>(P.k_out)[kd] = kf;
+        else reinterpret_cast<__nv_bfloat16*>(P.k_out)[kd] = __float2bfloat16_rn(kf);
+        if (P.v_dtype == 0) reinterpret_cast<float*>(P.v_out)[vd] = vf;
+        else reinterpret_cast<__nv_bfloat16*>(P.v_out)[vd] = __float2bfloat16_rn(vf);
+    }
+}
+
+__global__ void cast_f32_to_bf16_kernel(const float* src, __nv_bfloat16* dst, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = __float2bfloat16_rn(src[i]);
+}
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* src, float* dst, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = __bfloat162float(src[i]);
+}
+
+}  // namespace fusor

@@ -1,0 +1,1015 @@
+// libfusor_cuda.so: the C ABI declared in include/fusor_cuda.h.
+// Host side: contexts, buffers, argument validation (what the reference asserts on), tensor-map
+// construction, kernel dispatch, the paged KV cache and its split-KV work plan.
+// There is no CPU path here: without a device every compute call fails.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/fusor_cuda.h"
+#include "decode_splitkv.cuh"
+#include "general_attention.cuh"
+#include "prefill_sm100.cuh"
+
+using namespace fusor;
+
+// =============================================================================== context
+struct fusor_cuda_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int num_sms = 0;
+    int* d_err = nullptr;  // device error word written by kernels
+    long long launches = 0;
+    std::string last_error;
+    PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+    // scratch owned by the context for the _host entry points
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    void* pinned = nullptr;
+    size_t pinned_bytes = 0;
+};
+
+static thread_local std::string g_last_error;
+
+static int32_t fail(fusor_cuda_ctx* ctx, int32_t code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->last_error = buf;
+    g_last_error = buf;
+    return code;
+}
+
+#define CUDA_TRY(ctx, expr)                                                                              \
+    do {                                                                                                 \
+        cudaError_t _e = (expr);                                                                         \
+        if (_e != cudaSuccess)                                                                           \
+            return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                        __FILE__, __LINE__);                                                             \
+    } while (0)
+
+#define TRY(expr)                               \
+    do {                                        \
+        int32_t _rc = (expr);                   \
+        if (_rc != FUSOR_CUDA_OK) return _rc;   \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+extern "C" int32_t fusor_cuda_device_count(int32_t* count) {
+    if (!count) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "count is null");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        *count = 0;
+        cudaGetLastError();
+        return fail(nullptr, FUSOR_CUDA_NO_DEVICE, "cudaGetDeviceCount: %s", cudaGetErrorString(e));
+    }
+    *count = n;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cuda_ctx** out) {
+    if (!out) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return fail(nullptr, FUSOR_CUDA_NO_DEVICE, "no CUDA device is available; this library has no CPU path");
+    }
+    if (device < 0 || device >= n) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "device %d out of range [0,%d)", device, n);
+    cudaDeviceProp prop;
+    CUDA_TRY(nullptr, cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(nullptr, FUSOR_CUDA_NO_DEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only", device,
+                    prop.major, prop.minor);
+    CUDA_TRY(nullptr, cudaSetDevice(device));
+    fusor_cuda_ctx* ctx = new fusor_cuda_ctx();
+    ctx->device = device;
+    ctx->num_sms = prop.multiProcessorCount;
+    if (stream) {
+        ctx->stream = static_cast<cudaStream_t>(stream);
+    } else {
+        cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            delete ctx;
+            return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cudaStreamCreate: %s", cudaGetErrorString(e));
+        }
+        ctx->owns_stream = true;
+    }
+    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess) {
+        delete ctx;
+        return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cannot allocate the device error word");
+    }
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) {
+        delete ctx;
+        return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cuTensorMapEncodeTiled is not available in this driver");
+    }
+    ctx->encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    // opt in to large dynamic shared memory once per context
+    cudaFuncSetAttribute(prefill_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
+    cudaFuncSetAttribute(prefill_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
+    cudaFuncSetAttribute(decode_splitkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024);
+    cudaFuncSetAttribute(decode_splitkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024);
+    cudaFuncSetAttribute(general_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)general_smem_bytes(GEN_MAX_D));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        delete ctx;
+        return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "kernel attribute setup: %s", cudaGetErrorString(e));
+    }
+    *out = ctx;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_ctx_destroy(fusor_cuda_ctx* ctx) {
+    if (!ctx) return FUSOR_CUDA_OK;
+    DeviceGuard g(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    if (ctx->d_err) cudaFree(ctx->d_err);
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_ctx_set_stream(fusor_cuda_ctx* ctx, void* stream) {
+    if (!ctx) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "ctx is null");
+    if (ctx->owns_stream) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamDestroy(ctx->stream);
+        ctx->owns_stream = false;
+    }
+    ctx->stream = static_cast<cudaStream_t>(stream);
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" void* fusor_cuda_ctx_stream(fusor_cuda_ctx* ctx) { return ctx ? ctx->stream : nullptr; }
+
+extern "C" const char* fusor_cuda_last_error(fusor_cuda_ctx* ctx) {
+    return ctx ? ctx->last_error.c_str() : g_last_error.c_str();
+}
+
+extern "C" int64_t fusor_cuda_launch_count(fusor_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+static int32_t check_device_error(fusor_cuda_ctx* ctx) {
+    int h = 0;
+    CUDA_TRY(ctx, cudaMemcpyAsync(&h, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (h != 0) {
+        cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream);
+        if (h == kErrWaitTimeout)
+            return fail(ctx, FUSOR_CUDA_TIMEOUT, "a bounded device-side wait ran out (kernel unwound, result invalid)");
+        if (h == kErrBadPage)
+            return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "page table holds a page index outside the pool");
+        return fail(ctx, FUSOR_CUDA_INTERNAL, "device error word = %d", h);
+    }
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_stream_sync(fusor_cuda_ctx* ctx) {
+    if (!ctx) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "ctx is null");
+    DeviceGuard g(ctx->device);
+    return check_device_error(ctx);
+}
+
+extern "C" int32_t fusor_cuda_buffer_alloc(fusor_cuda_ctx* ctx, size_t bytes, void** device_ptr) {
+    if (!ctx || !device_ptr) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    DeviceGuard g(ctx->device);
+    CUDA_TRY(ctx, cudaMalloc(device_ptr, bytes ? bytes : 1));
+    return FUSOR_CUDA_OK;
+}
+extern "C" int32_t fusor_cuda_buffer_free(fusor_cuda_ctx* ctx, void* device_ptr) {
+    if (!ctx) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "ctx is null");
+    DeviceGuard g(ctx->device);
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(ctx, cudaFree(device_ptr));
+    return FUSOR_CUDA_OK;
+}
+extern "C" int32_t fusor_cuda_buffer_upload(fusor_cuda_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || (bytes && (!dst || !src))) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    DeviceGuard g(ctx->device);
+    CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return FUSOR_CUDA_OK;
+}
+extern "C" int32_t fusor_cuda_buffer_download(fusor_cuda_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || (bytes && (!dst || !src))) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    DeviceGuard g(ctx->device);
+    CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return FUSOR_CUDA_OK;
+}
+
+static int32_t launch_check(fusor_cuda_ctx* ctx, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "%s launch failed: %s", what, cudaGetErrorString(e));
+    ctx->launches++;
+    return FUSOR_CUDA_OK;
+}
+
+static size_t dtype_size(int32_t dt) { return dt == FUSOR_CUDA_F32 ? 4 : 2; }
+static bool dtype_ok(int32_t dt) { return dt == FUSOR_CUDA_F32 || dt == FUSOR_CUDA_BF16; }
+
+extern "C" int32_t fusor_cuda_cast(fusor_cuda_ctx* ctx, void* dst, int32_t dst_dtype, const void* src, int32_t src_dtype,
+                                   int64_t n) {
+    if (!ctx || !dst || !src || n < 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument or negative count");
+    if (!dtype_ok(dst_dtype) || !dtype_ok(src_dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    DeviceGuard g(ctx->device);
+    if (n == 0) return FUSOR_CUDA_OK;
+    if (dst_dtype == src_dtype) {
+        CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, n * dtype_size(dst_dtype), cudaMemcpyDeviceToDevice, ctx->stream));
+        return FUSOR_CUDA_OK;
+    }
+    const int blocks = (int)std::min<long long>((n + 255) / 256, (long long)ctx->num_sms * 16);
+    if (dst_dtype == FUSOR_CUDA_BF16)
+        cast_f32_to_bf16_kernel<<<blocks, 256, 0, ctx->stream>>>((const float*)src, (__nv_bfloat16*)dst, n);
+    else
+        cast_bf16_to_f32_kernel<<<blocks, 256, 0, ctx->stream>>>((const __nv_bfloat16*)src, (float*)dst, n);
+    return launch_check(ctx, "cast");
+}
+
+// =============================================================================== attention: validation
+struct AttnShape {
+    int B, Hq, Hkv, Sq, Skv, D;
+};
+
+// The checks the reference performs with assert!/panic! (fusor/src/composite/flash_attention.rs:94-99,153-172;
+// core/src/composite/flash_attention.rs:82-87), reported as status codes.
+static int32_t validate_attention(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                  const fusor_cuda_tensor4* v, const fusor_cuda_tensor2* mask, int32_t mask_kind,
+                                  int32_t window, const fusor_cuda_tensor4* out, AttnShape* S) {
+    if (!ctx) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "ctx is null");
+    if (!q || !k || !v || !out) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "q, k, v and out must be given");
+    if (!q->data || !k->data || !v->data || !out->data) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null data pointer");
+    const fusor_cuda_tensor4* ts[4] = {q, k, v, out};
+    for (auto* t : ts) {
+        if (!dtype_ok(t->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype %d", t->dtype);
+        for (int i = 0; i < 4; ++i)
+            if (t->shape[i] <= 0 || t->shape[i] > 0x7fffffff)
+                return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "tensor extent %lld out of range", (long long)t->shape[i]);
+        if (t->stride[3] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the head_dim axis must be contiguous");
+    }
+    S->B = (int)q->shape[0];
+    S->Hq = (int)q->shape[1];
+    S->Sq = (int)q->shape[2];
+    S->D = (int)q->shape[3];
+    S->Hkv = (int)k->shape[1];
+    S->Skv = (int)k->shape[2];
+    if (k->shape[0] != S->B || v->shape[0] != S->B || k->shape[3] != S->D)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "q [%d,%d,%d,%d] and k [%lld,%lld,%lld,%lld] disagree on batch or head_dim", S->B,
+                    S->Hq, S->Sq, S->D, (long long)k->shape[0], (long long)k->shape[1], (long long)k->shape[2], (long long)k->shape[3]);
+    for (int i = 0; i < 4; ++i)
+        if (v->shape[i] != k->shape[i]) return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "k and v shapes differ");
+    for (int i = 0; i < 4; ++i)
+        if (out->shape[i] != q->shape[i]) return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "out must have q's shape");
+    if (S->Hq % S->Hkv != 0)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "Number of Q heads (%d) must be divisible by number of K/V heads (%d)", S->Hq,
+                    S->Hkv);
+    if (S->D > GEN_MAX_D) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "head_dim %d > %d", S->D, GEN_MAX_D);
+    if (mask_kind < FUSOR_CUDA_MASK_NONE || mask_kind > FUSOR_CUDA_MASK_SLIDING)
+        return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown mask kind %d", mask_kind);
+    if (mask_kind == FUSOR_CUDA_MASK_QK || mask_kind == FUSOR_CUDA_MASK_BATCH_KEY) {
+        if (!mask || !mask->data) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "mask kind %d needs a mask tensor", mask_kind);
+        const long long e0 = mask_kind == FUSOR_CUDA_MASK_QK ? S->Sq : S->B;
+        if (mask->shape[0] != e0 || mask->shape[1] != S->Skv)
+            return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "%s shape [%lld, %lld] does not match expected [%lld, %d]",
+                        mask_kind == FUSOR_CUDA_MASK_QK ? "QKMask" : "BatchKeyMask", (long long)mask->shape[0],
+                        (long long)mask->shape[1], e0, S->Skv);
+    }
+    if ((mask_kind == FUSOR_CUDA_MASK_CAUSAL || mask_kind == FUSOR_CUDA_MASK_SLIDING) && S->Skv < S->Sq)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "causal attention needs kv_len (%d) >= q_len (%d)", S->Skv, S->Sq);
+    if (mask_kind == FUSOR_CUDA_MASK_SLIDING && window <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "window must be positive");
+    return FUSOR_CUDA_OK;
+}
+
+// =============================================================================== attention: launches
+static int32_t launch_general(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
+                              const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale,
+                              const fusor_cuda_tensor2* mask, int32_t mask_kind, int32_t window,
+                              const fusor_cuda_tensor4* out) {
+    GeneralParams P;
+    P.q = q->data; P.k = k->data; P.v = v->data; P.out = out->data;
+    P.mask = (mask_kind == FUSOR_CUDA_MASK_QK || mask_kind == FUSOR_CUDA_MASK_BATCH_KEY) ? (const float*)mask->data : nullptr;
+    P.q_dtype = q->dtype; P.k_dtype = k->dtype; P.v_dtype = v->dtype; P.out_dtype = out->dtype;
+    P.B = S.B; P.Hq = S.Hq; P.Hkv = S.Hkv; P.Sq = S.Sq; P.Skv = S.Skv; P.D = S.D;
+    for (int i = 0; i < 3; ++i) {
+        P.qs[i] = q->stride[i]; P.ks[i] = k->stride[i]; P.vs[i] = v->stride[i]; P.os[i] = out->stride[i];
+    }
+    P.ms[0] = P.mask ? mask->stride[0] : 0;
+    P.ms[1] = P.mask ? mask->stride[1] : 0;
+    P.mask_kind = mask_kind; P.window = window; P.scale = scale;
+    if (S.Hq > 65535 || S.B > 65535) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "more than 65535 heads or batches");
+    dim3 grid((S.Sq + GEN_BM - 1) / GEN_BM, S.Hq, S.B);
+    general_attention_kernel<<<grid, GEN_THREADS, general_smem_bytes(S.D), ctx->stream>>>(P);
+    return launch_check(ctx, "general_attention_kernel");
+}
+
+// [B,H,S,D] view -> 4-D tensor map {D, S, H, B}, box {64, box_rows, 1, 1}, 128-byte swizzle, zero fill.
+static int32_t make_tmap_bhsd(fusor_cuda_ctx* ctx, CUtensorMap* tm, const fusor_cuda_tensor4* t, int box_rows) {
+    cuuint64_t dims[4] = {(cuuint64_t)t->shape[3], (cuuint64_t)t->shape[2], (cuuint64_t)t->shape[1], (cuuint64_t)t->shape[0]};
+    cuuint64_t strides[3] = {(cuuint64_t)t->stride[2] * 2, (cuuint64_t)t->stride[1] * 2, (cuuint64_t)t->stride[0] * 2};
+    // an extent-1 axis may carry any stride; give the encoder a legal one
+    for (int i = 0; i < 3; ++i)
+        if (dims[i + 1] == 1) strides[i] = (i == 0 ? dims[0] * 2 : strides[i - 1] * dims[i]);
+    cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = ctx->encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t->data, dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return FUSOR_CUDA_OK;
+}
+
+static bool tma_view_ok(const fusor_cuda_tensor4* t) {
+    if (t->dtype != FUSOR_CUDA_BF16) return false;
+    if (reinterpret_cast<uintptr_t>(t->data) % 16) return false;
+    for (int i = 0; i < 3; ++i)
+        if (t->shape[i] > 1 && (t->stride[i] % 8 != 0 || t->stride[i] <= 0)) return false;
+    return true;
+}
+
+static int g_prefill_p_format = 0;  // 0 = f16 P (default), 1 = bf16 P
+
+static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                             const fusor_cuda_tensor4* v, float scale, int32_t mask_kind, const fusor_cuda_tensor4* out) {
+    if (S.D != PF_D) return false;
+    if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL)) return false;
+    if (!tma_view_ok(q) || !tma_view_ok(k) || !tma_view_ok(v)) return false;
+    if (!(scale > 0.0f) || !std::isfinite(scale)) return false;
+    const int al = out->dtype == FUSOR_CUDA_F32 ? 4 : 8;
+    if (reinterpret_cast<uintptr_t>(out->data) % 16) return false;
+    for (int i = 0; i < 3; ++i)
+        if (out->shape[i] > 1 && out->stride[i] % al != 0) return false;
+    return true;
+}
+
+static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
+                              const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
+                              const fusor_cuda_tensor4* out, float* debug) {
+    CUtensorMap tmQ, tmK, tmV;
+    TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM));
+    TRY(make_tmap_bhsd(ctx, &tmK, k, PF_BN));
+    TRY(make_tmap_bhsd(ctx, &tmV, v, PF_BN));
+    PrefillParams P;
+    P.out = out->data; P.out_dtype = out->dtype;
+    for (int i = 0; i < 3; ++i) P.os[i] = out->stride[i];
+    P.B = S.B; P.Hq = S.Hq; P.Hkv = S.Hkv; P.Sq = S.Sq; P.Skv = S.Skv;
+    P.causal = mask_kind == FUSOR_CUDA_MASK_CAUSAL;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
+    P.err = ctx->d_err;
+    P.debug = debug;
+    const long long grid = (long long)P.n_q_tiles * S.Hq * S.B;
+    if (grid > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "grid too large");
+    if (g_prefill_p_format == 0)
+        prefill_sm100_kernel<0><<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, P);
+    else
+        prefill_sm100_kernel<1><<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, P);
+    return launch_check(ctx, "prefill_sm100_kernel");
+}
+
+extern "C" int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                              const fusor_cuda_tensor4* v, float scale, const fusor_cuda_tensor2* mask,
+                                              int32_t mask_kind, int32_t window, const fusor_cuda_tensor4* out) {
+    AttnShape S;
+    TRY(validate_attention(ctx, q, k, v, mask, mask_kind, window, out, &S));
+    DeviceGuard g(ctx->device);
+    if (prefill_eligible(S, q, k, v, scale, mask_kind, out)) return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, nullptr);
+    return launch_general(ctx, S, q, k, v, scale, mask, mask_kind, window, out);
+}
+
+extern "C" int32_t fusor_cuda_flash_attention_general(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q,
+                                                      const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale,
+                                                      const fusor_cuda_tensor2* mask, int32_t mask_kind, int32_t window,
+                                                      const fusor_cuda_tensor4* out) {
+    AttnShape S;
+    TRY(validate_attention(ctx, q, k, v, mask, mask_kind, window, out, &S));
+    DeviceGuard g(ctx->device);
+    return launch_general(ctx, S, q, k, v, scale, mask, mask_kind, window, out);
+}
+
+// Diagnostic: runs the tensor-core prefill kernel (P format 0 = f16, 1 = bf16) and dumps, for CTA 0,
+// [128][258] floats: raw S of its first key tile, un-normalised O, running max (log2 units) and row sum.
+extern "C" int32_t fusor_cuda_prefill_probe(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                            const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
+                                            const fusor_cuda_tensor4* out, int32_t p_format, float* debug_device) {
+    AttnShape S;
+    TRY(validate_attention(ctx, q, k, v, nullptr, mask_kind, 0, out, &S));
+    DeviceGuard g(ctx->device);
+    if (!prefill_eligible(S, q, k, v, scale, mask_kind, out))
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "arguments are not eligible for the tensor-core prefill kernel");
+    const int saved = g_prefill_p_format;
+    g_prefill_p_format = p_format ? 1 : 0;
+    int32_t rc = launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, debug_device);
+    g_prefill_p_format = saved;
+    return rc;
+}
+
+// --------------------------------------------------------------------------- host-memory variants
+static int32_t ensure_scratch(fusor_cuda_ctx* ctx, size_t bytes) {
+    if (ctx->scratch_bytes >= bytes) return FUSOR_CUDA_OK;
+    if (ctx->scratch) {
+        CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        CUDA_TRY(ctx, cudaFree(ctx->scratch));
+        ctx->scratch = nullptr;
+        ctx->scratch_bytes = 0;
+    }
+    CUDA_TRY(ctx, cudaMalloc(&ctx->scratch, bytes));
+    ctx->scratch_bytes = bytes;
+    return FUSOR_CUDA_OK;
+}
+
+static bool contiguous4(const fusor_cuda_tensor4* t) {
+    long long expect = 1;
+    for (int i = 3; i >= 0; --i) {
+        if (t->shape[i] != 1 && t->stride[i] != expect) return false;
+        expect *= t->shape[i];
+    }
+    return true;
+}
+static size_t numel4(const fusor_cuda_tensor4* t) { return (size_t)t->shape[0] * t->shape[1] * t->shape[2] * t->shape[3]; }
+static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+static void set_contiguous(fusor_cuda_tensor4* t) {
+    t->stride[3] = 1;
+    t->stride[2] = t->shape[3];
+    t->stride[1] = t->shape[3] * t->shape[2];
+    t->stride[0] = t->shape[3] * t->shape[2] * t->shape[1];
+}
+
+extern "C" int32_t fusor_cuda_flash_attention_host(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                                   const fusor_cuda_tensor4* v, float scale, const fusor_cuda_tensor2* mask,
+                                                   int32_t mask_kind, int32_t window, const fusor_cuda_tensor4* out) {
+    AttnShape S;
+    TRY(validate_attention(ctx, q, k, v, mask, mask_kind, window, out, &S));
+    if (!contiguous4(q) || !contiguous4(k) || !contiguous4(v) || !contiguous4(out))
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "host tensors must be contiguous");
+    DeviceGuard g(ctx->device);
+    const bool has_mask = mask_kind == FUSOR_CUDA_MASK_QK || mask_kind == FUSOR_CUDA_MASK_BATCH_KEY;
+    if (has_mask && (mask->stride[1] != 1 || mask->stride[0] != mask->shape[1]))
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "host mask must be contiguous");
+    const size_t qb = numel4(q) * dtype_size(q->dtype), kb = numel4(k) * dtype_size(k->dtype),
+                 vb = numel4(v) * dtype_size(v->dtype), ob = numel4(out) * dtype_size(out->dtype);
+    const size_t mb = has_mask ? (size_t)mask->shape[0] * mask->shape[1] * 4 : 0;
+    TRY(ensure_scratch(ctx, align256(qb) + align256(kb) + align256(vb) + align256(ob) + align256(mb)));
+    uint8_t* p = (uint8_t*)ctx->scratch;
+    fusor_cuda_tensor4 dq = *q, dk = *k, dv = *v, dout = *out;
+    fusor_cuda_tensor2 dm;
+    dq.data = p; p += align256(qb);
+    dk.data = p; p += align256(kb);
+    dv.data = p; p += align256(vb);
+    dout.data = p; p += align256(ob);
+    set_contiguous(&dq); set_contiguous(&dk); set_contiguous(&dv); set_contiguous(&dout);
+    CUDA_TRY(ctx, cudaMemcpyAsync(dq.data, q->data, qb, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(dk.data, k->data, kb, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(dv.data, v->data, vb, cudaMemcpyHostToDevice, ctx->stream));
+    if (has_mask) {
+        dm = *mask;
+        dm.data = p;
+        CUDA_TRY(ctx, cudaMemcpyAsync(dm.data, mask->data, mb, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    TRY(fusor_cuda_flash_attention(ctx, &dq, &dk, &dv, scale, has_mask ? &dm : nullptr, mask_kind, window, &dout));
+    CUDA_TRY(ctx, cudaMemcpyAsync(out->data, dout.data, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    return check_device_error(ctx);
+}
+
+// =============================================================================== paged KV cache
+struct fusor_cuda_kvcache {
+    fusor_cuda_ctx* ctx = nullptr;
+    int max_batch = 0, Hkv = 0, D = 0, PT = 0, num_pages = 0, max_pages = 0;
+    __nv_bfloat16* k_pages = nullptr;
+    __nv_bfloat16* v_pages = nullptr;
+    int* d_page_table = nullptr;
+    int* d_kv_len = nullptr;
+    int* d_len_before = nullptr;
+    std::vector<int> h_page_table, h_kv_len;
+    std::vector<int> free_list;
+    std::vector<char> page_used;
+    int active_B = 0;
+    bool table_dirty = true;
+    CUtensorMap tmK, tmV;
+    // split-KV plan
+    bool plan_dirty = true;
+    int plan_g = 0;
+    int grid = 0, n_slots = 0, max_grid = 0, max_slots = 0;
+    DecodeSegment* d_segs = nullptr;
+    int* d_cta_seg_start = nullptr;
+    int* d_seq_slot_begin = nullptr;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    int ring = 0;
+    size_t smem = 0;
+};
+
+static int32_t kv_fail(fusor_cuda_kvcache* c, int32_t code, const char* msg) { return fail(c ? c->ctx : nullptr, code, "%s", msg); }
+
+extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_batch, int32_t num_kv_heads, int32_t head_dim,
+                                             int32_t page_tokens, int32_t num_pages, int32_t max_pages_per_seq,
+                                             fusor_cuda_kvcache** out) {
+    if (!ctx || !out) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (max_batch <= 0 || num_kv_heads <= 0 || num_pages <= 0 || max_pages_per_seq <= 0)
+        return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "sizes must be positive");
+    if (page_tokens != DEC_PT) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "page_tokens must be %d", DEC_PT);
+    if (head_dim != 128 && head_dim != 64) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "paged cache supports head_dim 64 or 128");
+    if ((long long)num_pages * num_kv_heads * DEC_PT > 0x7fffffffLL)
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "page pool has more than 2^31 rows");
+    DeviceGuard g(ctx->device);
+    fusor_cuda_kvcache* c = new fusor_cuda_kvcache();
+    c->ctx = ctx; c->max_batch = max_batch; c->Hkv = num_kv_heads; c->D = head_dim; c->PT = page_tokens;
+    c->num_pages = num_pages; c->max_pages = max_pages_per_seq;
+    const size_t pool_bytes = (size_t)num_pages * num_kv_heads * DEC_PT * head_dim * 2;
+    c->max_grid = 2 * ctx->num_sms;
+    c->max_slots = max_batch * num_kv_heads + c->max_grid;
+    bool ok = cudaMalloc(&c->k_pages, pool_bytes) == cudaSuccess && cudaMalloc(&c->v_pages, pool_bytes) == cudaSuccess &&
+              cudaMalloc(&c->d_page_table, (size_t)max_batch * max_pages_per_seq * 4) == cudaSuccess &&
+              cudaMalloc(&c->d_kv_len, (size_t)max_batch * 4) == cudaSuccess &&
+              cudaMalloc(&c->d_len_before, (size_t)max_batch * 4) == cudaSuccess &&
+              cudaMalloc(&c->d_segs, (size_t)c->max_slots * sizeof(DecodeSegment)) == cudaSuccess &&
+              cudaMalloc(&c->d_cta_seg_start, (size_t)(c->max_grid + 1) * 4) == cudaSuccess &&
+              cudaMalloc(&c->d_seq_slot_begin, (size_t)(max_batch * num_kv_heads + 1) * 4) == cudaSuccess &&
+              cudaMalloc(&c->part_o, (size_t)c->max_slots * DEC_GP * head_dim * 4) == cudaSuccess &&
+              cudaMalloc(&c->part_ml, (size_t)c->max_slots * DEC_GP * 2 * 4) == cudaSuccess;
+    if (ok) ok = cudaMemsetAsync(c->k_pages, 0, pool_bytes, ctx->stream) == cudaSuccess &&
+                 cudaMemsetAsync(c->v_pages, 0, pool_bytes, ctx->stream) == cudaSuccess &&
+                 cudaMemsetAsync(c->d_page_table, 0, (size_t)max_batch * max_pages_per_seq * 4, ctx->stream) == cudaSuccess &&
+                 cudaMemsetAsync(c->d_kv_len, 0, (size_t)max_batch * 4, ctx->stream) == cudaSuccess;
+    if (!ok) {
+        cudaError_t e = cudaGetLastError();
+        fusor_cuda_kvcache_destroy(c);
+        return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "KV cache allocation failed: %s", cudaGetErrorString(e));
+    }
+    c->h_page_table.assign((size_t)max_batch * max_pages_per_seq, 0);
+    c->h_kv_len.assign(max_batch, 0);
+    c->page_used.assign(num_pages, 0);
+    c->free_list.resize(num_pages);
+    for (int i = 0; i < num_pages; ++i) c->free_list[i] = num_pages - 1 - i;  // pop_back hands out page 0 first
+    // 2-D tensor maps over the pools: {D, num_pages*Hkv*16 rows}, box {64, 16}, 128-byte swizzle
+    for (int which = 0; which < 2; ++which) {
+        cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)num_pages * num_kv_heads * DEC_PT};
+        cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+        cuuint32_t box[2] = {64, DEC_PT};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = ctx->encode(which ? &c->tmV : &c->tmK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                 which ? (void*)c->v_pages : (void*)c->k_pages, dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            fusor_cuda_kvcache_destroy(c);
+            return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "cuTensorMapEncodeTiled (page pool) failed with %d", (int)r);
+        }
+    }
+    // ring depth: two CTAs per SM, each within 113 KB of dynamic shared memory
+    const int page_bytes = DEC_PT * head_dim * 2;
+    c->ring = head_dim == 128 ? 10 : 20;
+    c->smem = head_dim == 128 ? DecodeSmem<128>::bytes(c->ring) : DecodeSmem<64>::bytes(c->ring);
+    (void)page_bytes;
+    *out = c;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_kvcache_destroy(fusor_cuda_kvcache* c) {
+    if (!c) return FUSOR_CUDA_OK;
+    DeviceGuard g(c->ctx->device);
+    cudaStreamSynchronize(c->ctx->stream);
+    void* ptrs[] = {c->k_pages, c->v_pages, c->d_page_table, c->d_kv_len, c->d_len_before, c->d_segs,
+                    c->d_cta_seg_start, c->d_seq_slot_begin, c->part_o, c->part_ml};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    delete c;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_kvcache_reset(fusor_cuda_kvcache* c) {
+    if (!c) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "cache is null");
+    std::fill(c->h_kv_len.begin(), c->h_kv_len.end(), 0);
+    std::fill(c->page_used.begin(), c->page_used.end(), 0);
+    c->free_list.resize(c->num_pages);
+    for (int i = 0; i < c->num_pages; ++i) c->free_list[i] = c->num_pages - 1 - i;
+    c->active_B = 0;
+    c->table_dirty = true;
+    c->plan_dirty = true;
+    return FUSOR_CUDA_OK;
+}
+
+static int32_t kv_sync_tables(fusor_cuda_kvcache* c) {
+    if (!c->table_dirty) return FUSOR_CUDA_OK;
+    fusor_cuda_ctx* ctx = c->ctx;
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_page_table, c->h_page_table.data(), c->h_page_table.size() * 4, cudaMemcpyHostToDevice,
+                                  ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_kv_len, c->h_kv_len.data(), c->h_kv_len.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    c->table_dirty = false;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* k_new,
+                                             const fusor_cuda_tensor4* v_new) {
+    if (!c || !k_new || !v_new || !k_new->data || !v_new->data) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    fusor_cuda_ctx* ctx = c->ctx;
+    if (!dtype_ok(k_new->dtype) || !dtype_ok(v_new->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    for (int i = 0; i < 4; ++i)
+        if (k_new->shape[i] != v_new->shape[i]) return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "k and v shapes differ");
+    const int B = (int)k_new->shape[0], n = (int)k_new->shape[2];
+    if (k_new->shape[1] != c->Hkv || k_new->shape[3] != c->D)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "appended tensor is [%lld,%lld,%lld,%lld]; cache holds %d kv heads of dim %d",
+                    (long long)k_new->shape[0], (long long)k_new->shape[1], (long long)k_new->shape[2], (long long)k_new->shape[3],
+                    c->Hkv, c->D);
+    if (B <= 0 || B > c->max_batch || n <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "batch %d (max %d) or token count %d invalid", B, c->max_batch, n);
+    if (k_new->stride[3] != 1 || v_new->stride[3] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the head_dim axis must be contiguous");
+    if (c->active_B != 0 && c->active_B != B)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "cache holds %d sequences, append brings %d", c->active_B, B);
+    // page allocation on the host
+    int need = 0;
+    for (int b = 0; b < B; ++b) {
+        const int have = (c->h_kv_len[b] + DEC_PT - 1) / DEC_PT, want = (c->h_kv_len[b] + n + DEC_PT - 1) / DEC_PT;
+        if (want > c->max_pages) return fail(ctx, FUSOR_CUDA_OUT_OF_PAGES, "sequence %d would need %d pages (max %d per sequence)", b, want, c->max_pages);
+        need += want - have;
+    }
+    if (need > (int)c->free_list.size()) return fail(ctx, FUSOR_CUDA_OUT_OF_PAGES, "need %d pages, %d free", need, (int)c->free_list.size());
+    DeviceGuard g(ctx->device);
+    std::vector<int> before(c->h_kv_len.begin(), c->h_kv_len.begin() + B);
+    for (int b = 0; b < B; ++b) {
+        const int have = (c->h_kv_len[b] + DEC_PT - 1) / DEC_PT, want = (c->h_kv_len[b] + n + DEC_PT - 1) / DEC_PT;
+        for (int p = have; p < want; ++p) {
+            const int page = c->free_list.back();
+            c->free_list.pop_back();
+            c->page_used[page] = 1;
+            c->h_page_table[(size_t)b * c->max_pages + p] = page;
+        }
+        c->h_kv_len[b] += n;
+    }
+    c->active_B = B;
+    c->table_dirty = true;
+    c->plan_dirty = true;
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_len_before, before.data(), (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+    TRY(kv_sync_tables(c));
+    AppendParams P;
+    P.k_new = k_new->data; P.v_new = v_new->data; P.k_dtype = k_new->dtype; P.v_dtype = v_new->dtype;
+    for (int i = 0; i < 3; ++i) { P.ks[i] = k_new->stride[i]; P.vs[i] = v_new->stride[i]; }
+    P.k_pages = c->k_pages; P.v_pages = c->v_pages; P.page_table = c->d_page_table; P.len_before = c->d_len_before;
+    P.max_pages = c->max_pages; P.Hkv = c->Hkv; P.D = c->D; P.n = n; P.B = B;
+    const long long total = (long long)B * c->Hkv * n * c->D;
+    const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
+    kvcache_append_kernel<<<blocks, 256, 0, ctx->stream>>>(P);
+    return launch_check(ctx, "kvcache_append_kernel");
+}
+
+extern "C" int32_t fusor_cuda_kvcache_seq_len(fusor_cuda_kvcache* c, int32_t b, int32_t* len) {
+    if (!c || !len) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (b < 0 || b >= c->max_batch) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "sequence index out of range");
+    *len = c->h_kv_len[b];
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_kvcache_set_page_table(fusor_cuda_kvcache* c, const int32_t* page_table, const int32_t* kv_len,
+                                                     int32_t B) {
+    if (!c || !page_table || !kv_len) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    fusor_cuda_ctx* ctx = c->ctx;
+    if (B <= 0 || B > c->max_batch) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "batch %d out of range (max %d)", B, c->max_batch);
+    std::vector<char> used(c->num_pages, 0);
+    for (int b = 0; b < B; ++b) {
+        if (kv_len[b] < 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "kv_len[%d] is negative", b);
+        const int np = (kv_len[b] + DEC_PT - 1) / DEC_PT;
+        if (np > c->max_pages) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "kv_len[%d] = %d needs %d pages (max %d)", b, kv_len[b], np, c->max_pages);
+        for (int p = 0; p < np; ++p) {
+            const int page = page_table[(size_t)b * c->max_pages + p];
+            if (page < 0 || page >= c->num_pages)
+                return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "page_table[%d][%d] = %d is outside the pool of %d pages", b, p, page, c->num_pages);
+            if (used[page]) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "page %d is mapped twice", page);
+            used[page] = 1;
+        }
+    }
+    std::fill(c->h_kv_len.begin(), c->h_kv_len.end(), 0);
+    for (int b = 0; b < B; ++b) {
+        c->h_kv_len[b] = kv_len[b];
+        std::memcpy(&c->h_page_table[(size_t)b * c->max_pages], &page_table[(size_t)b * c->max_pages], (size_t)c->max_pages * 4);
+    }
+    c->page_used = used;
+    c->free_list.clear();
+    for (int i = c->num_pages - 1; i >= 0; --i)
+        if (!used[i]) c->free_list.push_back(i);
+    c->active_B = B;
+    c->table_dirty = true;
+    c->plan_dirty = true;
+    DeviceGuard g(ctx->device);
+    return kv_sync_tables(c);
+}
+
+extern "C" int32_t fusor_cuda_kvcache_write_pages(fusor_cuda_kvcache* c, int32_t first_page, int32_t n_pages, const void* k_host,
+                                                  const void* v_host) {
+    if (!c || !k_host || !v_host) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (first_page < 0 || n_pages < 0 || first_page + (long long)n_pages > c->num_pages)
+        return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "page range outside the pool");
+    fusor_cuda_ctx* ctx = c->ctx;
+    DeviceGuard g(ctx->device);
+    const size_t per = (size_t)c->Hkv * DEC_PT * c->D;
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->k_pages + first_page * per, k_host, n_pages * per * 2, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->v_pages + first_page * per, v_host, n_pages * per * 2, cudaMemcpyHostToDevice, ctx->stream));
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_kvcache_read_pages(fusor_cuda_kvcache* c, int32_t first_page, int32_t n_pages, void* k_host,
+                                                 void* v_host) {
+    if (!c || !k_host || !v_host) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (first_page < 0 || n_pages < 0 || first_page + (long long)n_pages > c->num_pages)
+        return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "page range outside the pool");
+    fusor_cuda_ctx* ctx = c->ctx;
+    DeviceGuard g(ctx->device);
+    const size_t per = (size_t)c->Hkv * DEC_PT * c->D;
+    CUDA_TRY(ctx, cudaMemcpyAsync(k_host, c->k_pages + first_page * per, n_pages * per * 2, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(v_host, c->v_pages + first_page * per, n_pages * per * 2, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_kvcache_pools(fusor_cuda_kvcache* c, void** k_pages, void** v_pages) {
+    if (!c || !k_pages || !v_pages) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    *k_pages = c->k_pages;
+    *v_pages = c->v_pages;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_kvcache_gather(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* k_out, const fusor_cuda_tensor4* v_out) {
+    if (!c || !k_out || !v_out || !k_out->data || !v_out->data) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    fusor_cuda_ctx* ctx = c->ctx;
+    if (c->active_B == 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "the cache is empty");
+    if (!dtype_ok(k_out->dtype) || !dtype_ok(v_out->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    for (int i = 0; i < 4; ++i)
+        if (k_out->shape[i] != v_out->shape[i]) return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "k and v shapes differ");
+    int longest = 0;
+    for (int b = 0; b < c->active_B; ++b) longest = std::max(longest, c->h_kv_len[b]);
+    if (k_out->shape[0] != c->active_B || k_out->shape[1] != c->Hkv || k_out->shape[2] != longest || k_out->shape[3] != c->D)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "gather target must be [%d,%d,%d,%d]", c->active_B, c->Hkv, longest, c->D);
+    if (k_out->stride[3] != 1 || v_out->stride[3] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the head_dim axis must be contiguous");
+    DeviceGuard g(ctx->device);
+    TRY(kv_sync_tables(c));
+    GatherParams P;
+    P.k_out = k_out->data; P.v_out = v_out->data; P.k_dtype = k_out->dtype; P.v_dtype = v_out->dtype;
+    for (int i = 0; i < 3; ++i) { P.ks[i] = k_out->stride[i]; P.vs[i] = v_out->stride[i]; }
+    P.k_pages = c->k_pages; P.v_pages = c->v_pages; P.page_table = c->d_page_table; P.kv_len = c->d_kv_len;
+    P.max_pages = c->max_pages; P.Hkv = c->Hkv; P.D = c->D; P.len = longest; P.B = c->active_B;
+    const long long total = (long long)P.B * P.Hkv * P.len * P.D;
+    const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
+    kvcache_gather_kernel<<<blocks, 256, 0, ctx->stream>>>(P);
+    return launch_check(ctx, "kvcache_gather_kernel");
+}
+
+extern "C" int32_t fusor_cuda_kvcache_truncate_front(fusor_cuda_kvcache* c, int32_t b, int32_t keep) {
+    if (!c) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "cache is null");
+    fusor_cuda_ctx* ctx = c->ctx;
+    if (b < 0 || b >= c->active_B) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "sequence index out of range");
+    const int len = c->h_kv_len[b];
+    if (keep < 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "keep must be non-negative");
+    if (keep >= len) return FUSOR_CUDA_OK;
+    DeviceGuard g(ctx->device);
+    const int drop = len - keep;
+    int* row = &c->h_page_table[(size_t)b * c->max_pages];
+    const int old_pages = (len + DEC_PT - 1) / DEC_PT;
+    if (drop % DEC_PT == 0) {
+        // whole pages fall off the front: shift the table row
+        const int dp = drop / DEC_PT;
+        for (int p = 0; p < dp; ++p) {
+            c->page_used[row[p]] = 0;
+            c->free_list.push_back(row[p]);
+        }
+        for (int p = dp; p < old_pages; ++p) row[p - dp] = row[p];
+    } else {
+        // token-granular shift: copy the kept rows into fresh positions through a dense staging buffer
+        const size_t elems = (size_t)c->Hkv * keep * c->D;
+        TRY(ensure_scratch(ctx, 2 * align256(elems * 2)));
+        __nv_bfloat16* sk = (__nv_bfloat16*)ctx->scratch;
+        __nv_bfloat16* sv = (__nv_bfloat16*)((uint8_t*)ctx->scratch + align256(elems * 2));
+        TRY(kv_sync_tables(c));
+        // gather rows [drop, len) of sequence b: reuse the gather kernel on a one-sequence view shifted by `drop`
+        // (implemented as a strided device copy per page row run)
+        const size_t row_bytes = (size_t)c->D * 2;
+        for (int hk = 0; hk < c->Hkv; ++hk) {
+            int t = drop;
+            while (t < len) {
+                const int page = row[t / DEC_PT];
+                const int in_page = t % DEC_PT;
+                const int run = std::min(DEC_PT - in_page, len - t);
+                const size_t src = (((size_t)page * c->Hkv + hk) * DEC_PT + in_page) * c->D;
+                const size_t dst = ((size_t)hk * keep + (t - drop)) * c->D;
+                CUDA_TRY(ctx, cudaMemcpyAsync(sk + dst, c->k_pages + src, run * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+                CUDA_TRY(ctx, cudaMemcpyAsync(sv + dst, c->v_pages + src, run * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+                t += run;
+            }
+        }
+        const int new_pages = (keep + DEC_PT - 1) / DEC_PT;
+        for (int p = new_pages; p < old_pages; ++p) {
+            c->page_used[row[p]] = 0;
+            c->free_list.push_back(row[p]);
+        }
+        for (int hk = 0; hk < c->Hkv; ++hk) {
+            int t = 0;
+            while (t < keep) {
+                const int page = row[t / DEC_PT];
+                const int run = std::min(DEC_PT, keep - t);
+                const size_t dst = (((size_t)page * c->Hkv + hk) * DEC_PT) * c->D;
+                const size_t src = ((size_t)hk * keep + t) * c->D;
+                CUDA_TRY(ctx, cudaMemcpyAsync(c->k_pages + dst, sk + src, run * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+                CUDA_TRY(ctx, cudaMemcpyAsync(c->v_pages + dst, sv + src, run * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+                t += run;
+            }
+        }
+    }
+    c->h_kv_len[b] = keep;
+    c->table_dirty = true;
+    c->plan_dirty = true;
+    return kv_sync_tables(c);
+}
+
+// =============================================================================== decode
+// Deals the pages of all (sequence, kv head) pairs evenly to `grid` CTAs (pure host logic).
+// Flattened page order is (b, hk, page); CTA c owns global pages [c*total/grid, (c+1)*total/grid).
+// A segment is the run of pages of one (b, hk) inside one CTA's range; segments are numbered in
+// global order, so the partial records of one (b, hk) are contiguous: [seq_slot[s], seq_slot[s+1]).
+static void plan_segments(const int* kv_len, int B, int Hkv, int grid, std::vector<DecodeSegment>& segs,
+                          std::vector<int>& cta_start, std::vector<int>& seq_slot) {
+    long long total = 0;
+    for (int b = 0; b < B; ++b) total += (long long)((kv_len[b] + DEC_PT - 1) / DEC_PT) * Hkv;
+    segs.clear();
+    cta_start.assign(grid + 1, 0);
+    seq_slot.assign((size_t)B * Hkv + 1, 0);
+    int cta = 0;
+    long long pos = 0;
+    long long cta_end = total / grid;
+    int cta_off = 0;
+    for (int b = 0; b < B; ++b) {
+        const int np = (kv_len[b] + DEC_PT - 1) / DEC_PT;
+        for (int hk = 0; hk < Hkv; ++hk) {
+            seq_slot[(size_t)b * Hkv + hk] = (int)segs.size();
+            int p = 0;
+            while (p < np) {
+                while (pos >= cta_end) {
+                    ++cta;
+                    cta_start[cta] = (int)segs.size();
+                    cta_end = total * (cta + 1) / grid;
+                    cta_off = 0;
+                }
+                const int take = (int)std::min<long long>(np - p, cta_end - pos);
+                DecodeSegment s;
+                s.b = b; s.hk = hk; s.page_begin = p; s.page_end = p + take; s.kv_len = kv_len[b];
+                s.slot = (int)segs.size(); s.cta_page_off = cta_off; s.pad = 0;
+                segs.push_back(s);
+                p += take; pos += take; cta_off += take;
+            }
+        }
+    }
+    seq_slot[(size_t)B * Hkv] = (int)segs.size();
+    for (int i = cta + 1; i <= grid; ++i) cta_start[i] = (int)segs.size();
+}
+
+extern "C" int32_t fusor_cuda_decode_plan(const int32_t* kv_len, int32_t B, int32_t num_kv_heads, int32_t grid,
+                                          int32_t* segments, int32_t segment_capacity, int32_t* n_segments,
+                                          int32_t* cta_seg_start, int32_t* seq_slot_begin) {
+    if (!kv_len || !segments || !n_segments || !cta_seg_start || !seq_slot_begin || B <= 0 || num_kv_heads <= 0 || grid <= 0)
+        return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument or non-positive size");
+    long long total = 0;
+    for (int b = 0; b < B; ++b) {
+        if (kv_len[b] <= 0) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "sequence %d is empty", b);
+        total += (long long)((kv_len[b] + DEC_PT - 1) / DEC_PT) * num_kv_heads;
+    }
+    if (grid > total) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "grid %d exceeds the %lld pages", grid, total);
+    std::vector<DecodeSegment> segs;
+    std::vector<int> cta_start, seq_slot;
+    plan_segments(kv_len, B, num_kv_heads, grid, segs, cta_start, seq_slot);
+    *n_segments = (int)segs.size();
+    if ((int)segs.size() > segment_capacity) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "segment capacity %d < %d", segment_capacity, (int)segs.size());
+    std::memcpy(segments, segs.data(), segs.size() * sizeof(DecodeSegment));
+    std::memcpy(cta_seg_start, cta_start.data(), cta_start.size() * 4);
+    std::memcpy(seq_slot_begin, seq_slot.data(), seq_slot.size() * 4);
+    return FUSOR_CUDA_OK;
+}
+
+static int32_t build_decode_plan(fusor_cuda_kvcache* c) {
+    fusor_cuda_ctx* ctx = c->ctx;
+    const int B = c->active_B, Hkv = c->Hkv;
+    long long total = 0;
+    for (int b = 0; b < B; ++b) {
+        if (c->h_kv_len[b] <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "sequence %d is empty; decode needs at least one cached token", b);
+        total += (long long)((c->h_kv_len[b] + DEC_PT - 1) / DEC_PT) * Hkv;
+    }
+    const int grid = (int)std::min<long long>(c->max_grid, total);
+    std::vector<DecodeSegment> segs;
+    std::vector<int> cta_start, seq_slot;
+    plan_segments(c->h_kv_len.data(), B, Hkv, grid, segs, cta_start, seq_slot);
+    if ((int)segs.size() > c->max_slots) return fail(ctx, FUSOR_CUDA_INTERNAL, "plan has %d segments, room for %d", (int)segs.size(), c->max_slots);
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_segs, segs.data(), segs.size() * sizeof(DecodeSegment), cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_cta_seg_start, cta_start.data(), cta_start.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_seq_slot_begin, seq_slot.data(), seq_slot.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    c->grid = grid;
+    c->n_slots = (int)segs.size();
+    c->plan_dirty = false;
+    return FUSOR_CUDA_OK;
+}
+
+static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fusor_cuda_tensor4* q, float scale, void* out,
+                           int out_dtype, long long o_sb, long long o_sh, int mode) {
+    if (!ctx || !c || !q || !q->data || !out) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (c->ctx != ctx) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "cache belongs to another context");
+    if (!dtype_ok(q->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    if (c->active_B == 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "the cache is empty");
+    const int B = (int)q->shape[0], Hq = (int)q->shape[1];
+    if (q->shape[2] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "decode takes one query token per sequence (q_len = %lld)", (long long)q->shape[2]);
+    if (B != c->active_B || q->shape[3] != c->D)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "q is [%d,%d,1,%lld]; cache holds %d sequences of head_dim %d", B, Hq, (long long)q->shape[3], c->active_B, c->D);
+    if (Hq <= 0 || Hq % c->Hkv != 0)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "Number of Q heads (%d) must be divisible by number of K/V heads (%d)", Hq, c->Hkv);
+    const int g = Hq / c->Hkv;
+    if (g > DEC_GP) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "more than %d query heads per kv head", DEC_GP);
+    if (q->stride[3] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the head_dim axis must be contiguous");
+    if (q->dtype == FUSOR_CUDA_BF16 && ((q->stride[0] | q->stride[1]) & 1 || reinterpret_cast<uintptr_t>(q->data) % 4))
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "bf16 q rows must be 4-byte aligned");
+    if (Hq > 65535 || B > 65535) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "more than 65535 heads or batches");
+    DeviceGuard guard(ctx->device);
+    TRY(kv_sync_tables(c));
+    if (c->plan_dirty) TRY(build_decode_plan(c));
+    DecodeParams P;
+    P.q = q->data; P.q_dtype = q->dtype; P.q_sb = q->stride[0]; P.q_sh = q->stride[1];
+    P.page_table = c->d_page_table; P.max_pages = c->max_pages; P.num_pages = c->num_pages;
+    P.segs = c->d_segs; P.cta_seg_start = c->d_cta_seg_start;
+    P.part_o = c->part_o; P.part_ml = c->part_ml;
+    P.Hkv = c->Hkv; P.g = g; P.scale_log2 = scale * 1.4426950408889634f; P.ring = c->ring; P.err = ctx->d_err;
+    if (c->D == 128)
+        decode_splitkv_kernel<128><<<c->grid, DEC_THREADS, c->smem, ctx->stream>>>(c->tmK, c->tmV, P);
+    else
+        decode_splitkv_kernel<64><<<c->grid, DEC_THREADS, c->smem, ctx->stream>>>(c->tmK, c->tmV, P);
+    TRY(launch_check(ctx, "decode_splitkv_kernel"));
+    CombineParams C;
+    C.part_o = c->part_o; C.part_ml = c->part_ml; C.seq_slot_begin = c->d_seq_slot_begin;
+    C.out = out; C.out_dtype = out_dtype; C.o_sb = o_sb; C.o_sh = o_sh;
+    C.Hq = Hq; C.Hkv = c->Hkv; C.g = g; C.D = c->D; C.mode = mode;
+    decode_combine_kernel<<<dim3(Hq, B), c->D, 0, ctx->stream>>>(C);
+    return launch_check(ctx, "decode_combine_kernel");
+}
+
+extern "C" int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
+                                                     float scale, const fusor_cuda_tensor4* out) {
+    if (!out || !q) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (!dtype_ok(out->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    for (int i = 0; i < 4; ++i)
+        if (out->shape[i] != q->shape[i]) return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "out must have q's shape");
+    if (out->stride[3] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the head_dim axis must be contiguous");
+    return decode_impl(ctx, cache, q, scale, out->data, out->dtype, out->stride[0], out->stride[1], 0);
+}
+
+extern "C" int32_t fusor_cuda_flash_attention_decode_partial(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
+                                                             const fusor_cuda_tensor4* q, float scale, float* partial) {
+    return decode_impl(ctx, cache, q, scale, partial, FUSOR_CUDA_F32, 0, 0, 1);
+}
+
+extern "C" int32_t fusor_cuda_lse_combine(fusor_cuda_ctx* ctx, const float* parts, int32_t n_parts, int64_t n_rows,
+                                          int32_t head_dim, float* out) {
+    if (!ctx || !parts || !out) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (n_parts <= 0 || n_rows <= 0 || head_dim <= 0 || n_rows > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "sizes must be positive");
+    DeviceGuard g(ctx->device);
+    lse_combine_kernel<<<(unsigned)n_rows, std::min(head_dim, 256), 0, ctx->stream>>>(parts, n_parts, n_rows, head_dim, out);
+    return launch_check(ctx, "lse_combine_kernel");
+}
+
+extern "C" int32_t fusor_cuda_flash_attention_decode_host(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
+                                                          const fusor_cuda_tensor4* q, float scale,
+                                                          const fusor_cuda_tensor4* out) {
+    if (!ctx || !q || !out || !q->data || !out->data) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (!dtype_ok(q->dtype) || !dtype_ok(out->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    for (int i = 0; i < 4; ++i)
+        if (q->shape[i] <= 0 || out->shape[i] != q->shape[i]) return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "out must have q's shape");
+    if (!contiguous4(q) || !contiguous4(out)) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "host tensors must be contiguous");
+    DeviceGuard g(ctx->device);
+    const size_t qb = numel4(q) * dtype_size(q->dtype), ob = numel4(out) * dtype_size(out->dtype);
+    TRY(ensure_scratch(ctx, align256(qb) + align256(ob)));
+    fusor_cuda_tensor4 dq = *q, dout = *out;
+    dq.data = ctx->scratch;
+    dout.data = (uint8_t*)ctx->scratch + align256(qb);
+    set_contiguous(&dq); set_contiguous(&dout);
+    CUDA_TRY(ctx, cudaMemcpyAsync(dq.data, q->data, qb, cudaMemcpyHostToDevice, ctx->stream));
+    TRY(fusor_cuda_flash_attention_decode(ctx, cache, &dq, scale, &dout));
+    CUDA_TRY(ctx, cudaMemcpyAsync(out->data, dout.data, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    return check_device_error(ctx);
+}

@@ -1,0 +1,310 @@
+// Causal / full flash-attention prefill on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// One CTA owns a 128-row query tile of one (batch, query head) and walks the 128-key tiles
+// it can see (causal tile skip).  Roles, by warp:
+//   warp 0      TMA producer: Q once, then K and V tiles into two 3-slot shared-memory rings
+//               (128-byte swizzle; no multicast).
+//   warp 1      allocates TMEM and issues every tcgen05.mma from one thread:
+//               S_j = Q K_j^T   (SS: both operands in shared memory, K-major),
+//               O  += P_j V_j   (TS: P read from TMEM, V from shared memory, MN-major).
+//               S is double-buffered in TMEM so S_{j+1} is computed while the softmax of tile j runs.
+//   warps 4-7   softmax: one thread per query row reads its S row from TMEM, keeps the running
+//               max / sum, writes P (16-bit) back over S, rescales O in TMEM only when the row
+//               max has grown by more than 2^8 (lazy rescale), and finally writes O / l.
+// TMEM columns: [0,128) S0/P0, [128,256) S1/P1, [256,384) O.
+// All waits are bounded (ptx_sm100.cuh); on a timeout the CTA unwinds and frees its TMEM.
+//
+// Replaces the reference's fused kernel for Sq > 1
+// (fusor-ml/core/src/composite/flash_attention.rs:147-331: one subgroup per output row,
+// keys visited serially, mask read from a dense [Sq,Skv] tensor).
+#pragma once
+#include <cuda.h>
+
+#include "ptx_sm100.cuh"
+
+namespace fusor {
+
+constexpr int PF_BM = 128, PF_BN = 128, PF_D = 128;
+constexpr int PF_STAGES = 3;
+constexpr int PF_THREADS = 256;
+constexpr int PF_TILE_BYTES = 128 * 128 * 2;  // one 128x128 16-bit tile = two [128][64] halves
+constexpr int PF_HALF_BYTES = PF_TILE_BYTES / 2;
+constexpr uint32_t PF_TMEM_COLS = 512;
+constexpr uint32_t PF_COL_S0 = 0, PF_COL_S1 = 128, PF_COL_O = 256;
+constexpr float PF_RESCALE_THRESHOLD = 8.0f;  // in log2 units
+
+struct PrefillParams {
+    void* out;
+    int out_dtype;             // 0 f32, 1 bf16
+    long long os[3];           // element strides of batch, head, row
+    int B, Hq, Hkv, Sq, Skv;
+    int causal;
+    float scale_log2;
+    int n_q_tiles;
+    int* err;
+    float* debug;              // optional [128][128 + 128 + 2] dump from CTA 0: raw S of tile 0, un-normalised O, m, l
+};
+
+constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_TILE_BYTES * (1 + 2 * PF_STAGES) + 256;
+
+// kPFormat: 0 = P stored as f16, 1 = P stored as bf16 (V is always bf16).
+template <int kPFormat>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+    prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV, const PrefillParams P) {
+    extern __shared__ uint8_t pf_smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_sm = base;
+    uint8_t* k_sm = q_sm + PF_TILE_BYTES;
+    uint8_t* v_sm = k_sm + PF_STAGES * PF_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + PF_STAGES * PF_TILE_BYTES);
+    uint64_t* q_full = bars;                    // 1
+    uint64_t* k_full = bars + 1;                // STAGES
+    uint64_t* k_empty = k_full + PF_STAGES;     // STAGES
+    uint64_t* v_full = k_empty + PF_STAGES;     // STAGES
+    uint64_t* v_empty = v_full + PF_STAGES;     // STAGES
+    uint64_t* s_full = v_empty + PF_STAGES;     // 2
+    uint64_t* p_full = s_full + 2;              // 2
+    uint64_t* pv_done = p_full + 2;             // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // ---- which tile: heavy (late) query tiles first; consecutive CTAs share a kv head
+    const int heads_total = P.Hq * P.B;
+    const int qt = P.n_q_tiles - 1 - (int)(blockIdx.x / heads_total);
+    const int hb = blockIdx.x % heads_total;
+    const int h = hb % P.Hq, b = hb / P.Hq;
+    const int hk = h / (P.Hq / P.Hkv);
+    const int q0 = qt * PF_BM;
+    const int offset = P.Skv - P.Sq;
+    int n_kv = (P.Skv + PF_BN - 1) / PF_BN;
+    if (P.causal) n_kv = min(n_kv, (q0 + PF_BM - 1 + offset) / PF_BN + 1);
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < PF_STAGES; ++i) {
+            mbar_init(k_full + i, 1);
+            mbar_init(k_empty + i, 1);
+            mbar_init(v_full + i, 1);
+            mbar_init(v_empty + i, 1);
+        }
+        mbar_init(s_full + 0, 1);
+        mbar_init(s_full + 1, 1);
+        mbar_init(p_full + 0, 128);
+        mbar_init(p_full + 1, 128);
+        mbar_init(pv_done, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, PF_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, PF_TILE_BYTES);
+            tma_load_4d(q_sm, &tmQ, q_full, 0, q0, h, b);
+            tma_load_4d(q_sm + PF_HALF_BYTES, &tmQ, q_full, 64, q0, h, b);
+            for (int j = 0; j < n_kv; ++j) {
+                const int s = j % PF_STAGES, use = j / PF_STAGES;
+                if (use > 0 && !mbar_wait(k_empty + s, (use - 1) & 1, abort_flag, P.err)) break;
+                mbar_arrive_expect_tx(k_full + s, PF_TILE_BYTES);
+                tma_load_4d(k_sm + s * PF_TILE_BYTES, &tmK, k_full + s, 0, j * PF_BN, hk, b);
+                tma_load_4d(k_sm + s * PF_TILE_BYTES + PF_HALF_BYTES, &tmK, k_full + s, 64, j * PF_BN, hk, b);
+                if (use > 0 && !mbar_wait(v_empty + s, (use - 1) & 1, abort_flag, P.err)) break;
+                mbar_arrive_expect_tx(v_full + s, PF_TILE_BYTES);
+                tma_load_4d(v_sm + s * PF_TILE_BYTES, &tmV, v_full + s, 0, j * PF_BN, hk, b);
+                tma_load_4d(v_sm + s * PF_TILE_BYTES + PF_HALF_BYTES, &tmV, v_full + s, 64, j * PF_BN, hk, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // S = Q K^T : A, B bf16, both K-major, M = N = 128
+            constexpr uint32_t idesc_qk = make_idesc_f16(1, 1, 0, 0, PF_BM, PF_BN);
+            // O += P V  : A = P (TMEM, K-major), B = V bf16 MN-major, M = 128, N = D
+            constexpr uint32_t idesc_pv = make_idesc_f16(kPFormat, 1, 0, 1, PF_BM, PF_D);
+            const uint32_t q_addr = smem_u32(q_sm);
+            auto issue_qk = [&](int j) {
+                const uint32_t k_addr = smem_u32(k_sm + (j % PF_STAGES) * PF_TILE_BYTES);
+                const uint32_t d_tmem = tmem_base + ((j & 1) ? PF_COL_S1 : PF_COL_S0);
+#pragma unroll
+                for (int kk = 0; kk < PF_D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * PF_HALF_BYTES + (kk & 3) * 32;
+                    tc_mma_ss(d_tmem, make_smem_desc_sw128(q_addr + off, 16, 1024),
+                              make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0);
+                }
+                tc_commit(s_full + (j & 1));
+                tc_commit(k_empty + (j % PF_STAGES));
+            };
+            bool ok = mbar_wait(q_full, 0, abort_flag, P.err);
+            ok = ok && mbar_wait(k_full + 0, 0, abort_flag, P.err);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (j + 1 < n_kv) {
+                    ok = mbar_wait(k_full + (j + 1) % PF_STAGES, ((j + 1) / PF_STAGES) & 1, abort_flag, P.err);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                ok = mbar_wait(p_full + (j & 1), (j >> 1) & 1, abort_flag, P.err) &&
+                     mbar_wait(v_full + j % PF_STAGES, (j / PF_STAGES) & 1, abort_flag, P.err);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(v_sm + (j % PF_STAGES) * PF_TILE_BYTES);
+                const uint32_t p_tmem = tmem_base + ((j & 1) ? PF_COL_S1 : PF_COL_S0);
+#pragma unroll
+                for (int kk = 0; kk < PF_BN / 16; ++kk) {
+                    // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2 KB) of the V tile
+                    tc_mma_ts(tmem_base + PF_COL_O, p_tmem + kk * 8,
+                              make_smem_desc_sw128(v_addr + kk * 2048, PF_HALF_BYTES, 1024), idesc_pv,
+                              (j > 0 || kk > 0));
+                }
+                tc_commit(v_empty + (j % PF_STAGES));
+                tc_commit(pv_done);
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ softmax / correction / epilogue
+        const int row = tid - 128;                                   // 0..127 = TMEM lane
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lane quadrant
+        const int qi = q0 + row;
+        const int k_limit = P.causal ? min(P.Skv - 1, qi + offset) : P.Skv - 1;  // last key this row may see
+        float m_ref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            ok = mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag, P.err);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t s_tmem = tmem_base + lane_base + ((j & 1) ? PF_COL_S1 : PF_COL_S0);
+            uint32_t sr[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, sr[c]);
+            tc_wait_ld();
+            if (P.debug && blockIdx.x == 0 && j == 0) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) P.debug[row * 258 + c * 32 + i] = __uint_as_float(sr[c][i]);
+            }
+            const int k0 = j * PF_BN;
+            const bool need_mask = k0 + PF_BN - 1 > k_limit;
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float t = __uint_as_float(sr[c][i]) * P.scale_log2;
+                    if (need_mask && k0 + c * 32 + i > k_limit) t = -INFINITY;
+                    sr[c][i] = __float_as_uint(t);
+                    tmax = fmaxf(tmax, t);
+                }
+            // lazy rescale: keep the reference max until the true max has moved by more than the threshold
+            float alpha = 1.0f;
+            if (tmax > m_ref + PF_RESCALE_THRESHOLD) {  // also true on the first tile (m_ref = -inf)
+                alpha = fast_exp2(m_ref - tmax);        // 0 on the first tile
+                m_ref = tmax;
+            }
+            float psum = 0.0f;
+            const uint32_t p_tmem = s_tmem;  // P overwrites the first 64 columns of this S buffer
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = fast_exp2(__uint_as_float(sr[c][2 * i]) - m_ref);
+                    const float p1 = fast_exp2(__uint_as_float(sr[c][2 * i + 1]) - m_ref);
+                    psum += p0 + p1;
+                    pk[i] = kPFormat == 0 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+                }
+                tmem_st16(p_tmem + c * 16, pk);
+            }
+            l = l * alpha + psum;
+            tc_wait_st();
+            if (j > 0) {
+                // O must be complete up to tile j-1 before it is rescaled and before P_j is handed over
+                ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, P.err);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                    const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t orr[32];
+                        tmem_ld32(o_tmem + c * 32, orr);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+                        tmem_st32(o_tmem + c * 32, orr);
+                    }
+                    tc_wait_st();
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(p_full + (j & 1));
+        }
+        if (ok) ok = mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, P.err);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O;
+            const float inv_l = 1.0f / l;
+            const long long obase = (long long)b * P.os[0] + (long long)h * P.os[1] + (long long)qi * P.os[2];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t orr[32];
+                tmem_ld32(o_tmem + c * 32, orr);
+                tc_wait_ld();
+                if (P.debug && blockIdx.x == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) P.debug[row * 258 + 128 + c * 32 + i] = __uint_as_float(orr[i]);
+                    if (c == 0) {
+                        P.debug[row * 258 + 256] = m_ref;
+                        P.debug[row * 258 + 257] = l;
+                    }
+                }
+                if (qi < P.Sq) {
+                    if (P.out_dtype == 0) {
+                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + obase + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            dst[i] = make_float4(__uint_as_float(orr[4 * i]) * inv_l, __uint_as_float(orr[4 * i + 1]) * inv_l,
+                                                 __uint_as_float(orr[4 * i + 2]) * inv_l,
+                                                 __uint_as_float(orr[4 * i + 3]) * inv_l);
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(P.out) + obase + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            dst[i] = make_uint4(
+                                pack_bf16(__uint_as_float(orr[8 * i]) * inv_l, __uint_as_float(orr[8 * i + 1]) * inv_l),
+                                pack_bf16(__uint_as_float(orr[8 * i + 2]) * inv_l, __uint_as_float(orr[8 * i + 3]) * inv_l),
+                                pack_bf16(__uint_as_float(orr[8 * i + 4]) * inv_l, __uint_as_float(orr[8 * i + 5]) * inv_l),
+                                pack_bf16(__uint_as_float(orr[8 * i + 6]) * inv_l, __uint_as_float(orr[8 * i + 7]) * inv_l));
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown: every role falls through to here, also after a timeout
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, PF_TMEM_COLS);
+    }
+}
+
+}  // namespace fusor

@@ -1,0 +1,205 @@
+/*
+ * fusor_cuda.h -- C ABI of libfusor_cuda.so: B200 (sm_100a) attention for fusor-ml.
+ *
+ * This is what a `fusor-cuda` Rust crate binds (bindgen / hand-written `extern "C"`) to
+ * replace the wgpu arm of fusor's attention path.  Plain pointers and sizes only.  No
+ * function aborts or throws: each returns a status code, and `fusor_cuda_last_error`
+ * gives the message.  A context is bound to one device and one stream; calls on one
+ * context must be serialised by the caller, contexts on different devices are independent.
+ * All work is stream-ordered; results are visible after `fusor_cuda_stream_sync` (or any
+ * `_host` variant, which synchronises itself).  There is no CPU fallback: without a
+ * usable sm_100 device every compute entry point fails with FUSOR_CUDA_NO_DEVICE.
+ *
+ * Citations are paths inside floneum/floneum.
+ */
+#ifndef FUSOR_CUDA_H
+#define FUSOR_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (reference: assert!/panic! for misuse, fusor-ml/fusor/src/composite/flash_attention.rs:66,94-99,153-172;
+ *      Result<_, Error> for device errors, fusor-ml/fusor/src/error.rs:5-17) */
+#define FUSOR_CUDA_OK 0
+#define FUSOR_CUDA_INVALID_ARGUMENT 1 /* null pointer, bad enum, non-positive size */
+#define FUSOR_CUDA_SHAPE_MISMATCH 2   /* what the reference asserts on: head divisibility, mask shape, q/k/v shapes */
+#define FUSOR_CUDA_UNSUPPORTED 3      /* valid request the kernels do not cover (e.g. head_dim > 256) */
+#define FUSOR_CUDA_CUDA_ERROR 4       /* a CUDA runtime / driver call failed */
+#define FUSOR_CUDA_NO_DEVICE 5        /* no usable sm_100 device */
+#define FUSOR_CUDA_TIMEOUT 6          /* a bounded device-side wait ran out; the context stays usable */
+#define FUSOR_CUDA_OUT_OF_PAGES 7     /* KV cache page pool exhausted */
+#define FUSOR_CUDA_INTERNAL 8
+
+/* ---- element types (reference DataTypeEnum is F32/F16/U32, fusor-ml/core/src/tensor.rs:112-116; bf16 is added) */
+#define FUSOR_CUDA_F32 0
+#define FUSOR_CUDA_BF16 1
+
+/* ---- mask kinds (enum MaskKind, fusor-ml/fusor/src/composite/flash_attention.rs:10-19) */
+#define FUSOR_CUDA_MASK_NONE 0
+#define FUSOR_CUDA_MASK_QK 1        /* additive f32 [Sq, Skv], same for every (batch, head)  */
+#define FUSOR_CUDA_MASK_BATCH_KEY 2 /* additive f32 [B, Skv], broadcast over heads and queries */
+#define FUSOR_CUDA_MASK_CAUSAL 3    /* analytic: key k allowed for query q iff k <= q + (Skv - Sq); equals the tensor
+                                       MaskCache::get_mask(Sq, Skv - Sq, None) builds
+                                       (fusor-ml/fusor/src/cache/mask_cache.rs:36-86) without materialising it */
+#define FUSOR_CUDA_MASK_SLIDING 4   /* analytic sliding window of `window` keys on top of CAUSAL
+                                       (mask_cache.rs:88-116: -inf where i < j or j + w <= i) */
+
+typedef struct fusor_cuda_ctx fusor_cuda_ctx;
+typedef struct fusor_cuda_kvcache fusor_cuda_kvcache;
+
+/* Rank-4 strided tensor view [B, H, S, D]: element strides, like Layout {offset, shape, strides}
+ * (fusor-ml/types/src/layout.rs:88-211).  `data` is a device pointer except in `_host` entry points.
+ * The innermost dimension must be contiguous (stride[3] == 1), as at the reference call site
+ * (models/kalosm-llama/src/raw/attention_layer.rs:225-228). */
+typedef struct fusor_cuda_tensor4 {
+    void* data;
+    int32_t dtype;
+    int32_t _pad;
+    int64_t shape[4];
+    int64_t stride[4];
+} fusor_cuda_tensor4;
+
+/* Rank-2 strided f32 view (the mask tensor). */
+typedef struct fusor_cuda_tensor2 {
+    void* data;
+    int64_t shape[2];
+    int64_t stride[2];
+} fusor_cuda_tensor2;
+
+/* ------------------------------------------------------------------------------------------------
+ * Context, stream, buffers.
+ * Replaces fusor_core::Device creation and buffer ownership (fusor-ml/core/src/device.rs:82-201,305-354)
+ * and upload / readback (fusor-ml/fusor/src/composite/construction.rs:100-122,
+ * fusor-ml/core/src/tensor.rs:797-835). */
+int32_t fusor_cuda_device_count(int32_t* count);
+/* `stream` = an existing cudaStream_t to launch on, or NULL to let the context create its own. */
+int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cuda_ctx** out);
+int32_t fusor_cuda_ctx_destroy(fusor_cuda_ctx* ctx);
+int32_t fusor_cuda_ctx_set_stream(fusor_cuda_ctx* ctx, void* stream);
+void* fusor_cuda_ctx_stream(fusor_cuda_ctx* ctx);
+/* Message of the last failing call on this context (or of the last failing call without a context when NULL). */
+const char* fusor_cuda_last_error(fusor_cuda_ctx* ctx);
+/* Waits for the stream and reports a device-side timeout recorded by any kernel since the last sync. */
+int32_t fusor_cuda_stream_sync(fusor_cuda_ctx* ctx);
+/* Number of kernels this context has launched so far. */
+int64_t fusor_cuda_launch_count(fusor_cuda_ctx* ctx);
+
+int32_t fusor_cuda_buffer_alloc(fusor_cuda_ctx* ctx, size_t bytes, void** device_ptr);
+int32_t fusor_cuda_buffer_free(fusor_cuda_ctx* ctx, void* device_ptr);
+int32_t fusor_cuda_buffer_upload(fusor_cuda_ctx* ctx, void* device_dst, const void* host_src, size_t bytes);
+int32_t fusor_cuda_buffer_download(fusor_cuda_ctx* ctx, void* host_dst, const void* device_src, size_t bytes);
+/* f32 -> bf16 (round to nearest even) / bf16 -> f32 on the device, n contiguous elements. */
+int32_t fusor_cuda_cast(fusor_cuda_ctx* ctx, void* dst, int32_t dst_dtype, const void* src, int32_t src_dtype, int64_t n);
+
+/* ------------------------------------------------------------------------------------------------
+ * Attention.  Replaces fusor::Tensor::<4>::flash_attention(&self, k, v, scale, mask) -> Self
+ * (fusor-ml/fusor/src/composite/flash_attention.rs:52-73) and the fused kernel behind its GPU arm
+ * (fusor-ml/core/src/composite/flash_attention.rs:28-52,56-557).
+ *   q [B,Hq,Sq,D], k and v [B,Hkv,Skv,D], out [B,Hq,Sq,D]; Hq % Hkv == 0, query head h reads kv head h/(Hq/Hkv).
+ *   out = softmax(q k^T * scale + mask) v, f32 accumulation.
+ * Dispatch: bf16 q/k/v with D == 128, no mask tensor (NONE / CAUSAL) run the tcgen05 tensor-core kernel;
+ * everything else (f32 inputs, any D <= 256, additive mask tensors, sliding window) runs the general kernel
+ * in f32 arithmetic.  out dtype f32 or bf16.  `mask` is read only for MASK_QK / MASK_BATCH_KEY;
+ * `window` only for MASK_SLIDING. */
+int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                   const fusor_cuda_tensor4* v, float scale, const fusor_cuda_tensor2* mask,
+                                   int32_t mask_kind, int32_t window, const fusor_cuda_tensor4* out);
+
+/* The same call for tensors in HOST memory: uploads q, k, v (and the mask), runs, downloads `out`, synchronises.
+ * This is the path of a caller that holds CPU tensors, as the reference's as_slice().await round trip
+ * (fusor-ml/fusor/src/lib.rs:391-403). */
+int32_t fusor_cuda_flash_attention_host(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                        const fusor_cuda_tensor4* v, float scale, const fusor_cuda_tensor2* mask,
+                                        int32_t mask_kind, int32_t window, const fusor_cuda_tensor4* out);
+
+/* Forces the general (f32-arithmetic) kernel for any input; used to cross-check the tensor-core kernels. */
+int32_t fusor_cuda_flash_attention_general(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q,
+                                           const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale,
+                                           const fusor_cuda_tensor2* mask, int32_t mask_kind, int32_t window,
+                                           const fusor_cuda_tensor4* out);
+
+/* Diagnostic (no reference counterpart): runs the tensor-core prefill kernel with P kept as f16 (p_format 0)
+ * or bf16 (p_format 1) and copies out of the first CTA, into debug_device f32 [128][258], the raw scores of its
+ * first key tile [0,128), its un-normalised O [128,256), the running max in log2 units [256] and the row sum [257].
+ * Fails with FUSOR_CUDA_UNSUPPORTED when the arguments are not eligible for that kernel. */
+int32_t fusor_cuda_prefill_probe(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                 const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
+                                 const fusor_cuda_tensor4* out, int32_t p_format, float* debug_device);
+
+/* ------------------------------------------------------------------------------------------------
+ * Paged bf16 KV cache.  Replaces fusor::cache::KvCache / TensorCache
+ * (fusor-ml/fusor/src/cache/kv_cache.rs:12-68, tensor_cache.rs:9-124; per-layer owner
+ * models/kalosm-llama/src/raw/cache.rs:14-54).  The reference keeps a dense f32 [B,Hkv,len,D] tensor and copies
+ * the whole valid cache on every append; here K and V live in pools of 16-token pages,
+ *   k_pages, v_pages : bf16 [num_pages][Hkv][16][D]   (one (page, head) tile = 16*D*2 bytes contiguous)
+ *   page_table       : int32 [max_batch][max_pages_per_seq],  kv_len : int32 [max_batch]
+ * and an append writes only the new rows. */
+int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_batch, int32_t num_kv_heads, int32_t head_dim,
+                                  int32_t page_tokens, int32_t num_pages, int32_t max_pages_per_seq,
+                                  fusor_cuda_kvcache** out);
+int32_t fusor_cuda_kvcache_destroy(fusor_cuda_kvcache* cache);
+/* KvCache::reset (kv_cache.rs:42-46): every sequence back to length 0, all pages free. */
+int32_t fusor_cuda_kvcache_reset(fusor_cuda_kvcache* cache);
+/* KvCache::append (kv_cache.rs:50-62): k_new, v_new [B,Hkv,n,D] (f32 or bf16, device) are appended to sequences
+ * 0..B-1; pages are taken from the free list as needed.  Sets the active batch to B. */
+int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* k_new,
+                                  const fusor_cuda_tensor4* v_new);
+/* TensorCache eviction (tensor_cache.rs:55-78): keep only the newest `keep` tokens of sequence b. */
+int32_t fusor_cuda_kvcache_truncate_front(fusor_cuda_kvcache* cache, int32_t b, int32_t keep);
+/* KvCache::current_seq_len (kv_cache.rs:65-67) of sequence b. */
+int32_t fusor_cuda_kvcache_seq_len(fusor_cuda_kvcache* cache, int32_t b, int32_t* len);
+/* Installs a caller-built mapping (host arrays): page_table [B][max_pages_per_seq], kv_len [B]. Entries beyond
+ * ceil(kv_len/page_tokens) are ignored.  Marks the listed pages used and sets the active batch to B. */
+int32_t fusor_cuda_kvcache_set_page_table(fusor_cuda_kvcache* cache, const int32_t* page_table, const int32_t* kv_len,
+                                          int32_t B);
+/* Raw pool access: copies `n_pages` whole pages starting at `first_page` from / to host memory
+ * (bf16 [n_pages][Hkv][page_tokens][D]). */
+int32_t fusor_cuda_kvcache_write_pages(fusor_cuda_kvcache* cache, int32_t first_page, int32_t n_pages,
+                                       const void* k_host, const void* v_host);
+int32_t fusor_cuda_kvcache_read_pages(fusor_cuda_kvcache* cache, int32_t first_page, int32_t n_pages, void* k_host,
+                                      void* v_host);
+/* Device pointers of the pools (for callers that fill pages with their own kernels). */
+int32_t fusor_cuda_kvcache_pools(fusor_cuda_kvcache* cache, void** k_pages, void** v_pages);
+/* Dense export (what KvCache::k()/v() hand back, kv_cache.rs:32-39): k_out, v_out [B,Hkv,len,D] device tensors,
+ * len = the longest active sequence; rows past a sequence's length are zero. */
+int32_t fusor_cuda_kvcache_gather(fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* k_out,
+                                  const fusor_cuda_tensor4* v_out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Decode: one query token per sequence against the paged cache (the Sq == 1 regime of the call site,
+ * models/kalosm-llama/src/raw/attention_layer.rs:405-448; all-zero mask [1, kv_len]).
+ *   q [B,Hq,1,D] (bf16 or f32), out [B,Hq,1,D] (f32 or bf16).
+ * Split-KV: the pages of all (sequence, kv head) pairs are dealt evenly to a persistent grid; each CTA emits
+ * a partial (m, l, O) per run of pages, and a combine kernel merges them by log-sum-exp. */
+int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
+                                          float scale, const fusor_cuda_tensor4* out);
+/* Same, but leaves the result un-normalised for a merge across GPUs that each hold a chunk of the keys:
+ * partial f32 [B][Hq][D+2] = { m = max scaled score, l = sum exp(s - m), O[D] = sum exp(s - m) v }. */
+int32_t fusor_cuda_flash_attention_decode_partial(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
+                                                  const fusor_cuda_tensor4* q, float scale, float* partial);
+/* Merge: parts f32 [n_parts][n_rows][D+2] -> out f32 [n_rows][D]  (M = max m, L = sum l e^(m-M),
+ * out = sum O e^(m-M) / L; the (m, d) rule of fusor-ml/core/src/composite/softmax.rs:59-82).
+ * A part with l == 0 contributes nothing. */
+int32_t fusor_cuda_lse_combine(fusor_cuda_ctx* ctx, const float* parts, int32_t n_parts, int64_t n_rows,
+                               int32_t head_dim, float* out);
+/* The split-KV work plan, as pure host logic (no device needed): deals the 16-token pages of all
+ * (sequence, kv head) pairs, flattened in (b, hk, page) order, evenly to `grid` CTAs.  Writes
+ * segments as int32[8] records {b, hk, page_begin, page_end, kv_len, slot, cta_page_offset, 0},
+ * cta_seg_start [grid + 1] and seq_slot_begin [B * num_kv_heads + 1].  No reference counterpart
+ * (the reference has no split-KV); exported so the partition can be checked without a GPU. */
+int32_t fusor_cuda_decode_plan(const int32_t* kv_len, int32_t B, int32_t num_kv_heads, int32_t grid, int32_t* segments,
+                               int32_t segment_capacity, int32_t* n_segments, int32_t* cta_seg_start,
+                               int32_t* seq_slot_begin);
+/* Host-memory variant of decode: uploads q, runs, downloads out, synchronises. */
+int32_t fusor_cuda_flash_attention_decode_host(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
+                                               const fusor_cuda_tensor4* q, float scale,
+                                               const fusor_cuda_tensor4* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUSOR_CUDA_H */

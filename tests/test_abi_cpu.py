@@ -1,0 +1,126 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol include/fusor_cuda.h declares,
+reports NO_DEVICE instead of computing on the CPU, and its host-only logic (the split-KV plan) is right."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fusor_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fusor_cuda_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from floneum_b200 import _lib
+    L = _lib.load()
+    declared = _declared_symbols()
+    assert len(declared) >= 30
+    for name in declared:
+        assert hasattr(L, name), f"{name} is declared in include/fusor_cuda.h but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == declared
+
+
+def test_no_cpu_fallback_without_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from floneum_b200 import Device, FusorCudaError, _lib
+    with pytest.raises(FusorCudaError) as e:
+        Device.gpu(0)
+    assert e.value.code == _lib.NO_DEVICE
+    with pytest.raises(FusorCudaError):
+        Device.cpu()
+
+
+def test_null_arguments_are_status_codes():
+    from floneum_b200 import _lib
+    L = _lib.load()
+    assert L.fusor_cuda_ctx_create(0, None, None) == _lib.INVALID_ARGUMENT
+    assert L.fusor_cuda_flash_attention(None, None, None, None, 1.0, None, 0, 0, None) == _lib.INVALID_ARGUMENT
+    assert L.fusor_cuda_kvcache_reset(None) == _lib.INVALID_ARGUMENT
+    assert b"null" in L.fusor_cuda_last_error(None)
+
+
+def _plan(kv_len, Hkv, grid):
+    from floneum_b200 import _lib
+    L = _lib.load()
+    kv = np.ascontiguousarray(kv_len, np.int32)
+    B = kv.size
+    cap = B * Hkv + grid
+    segs = np.zeros((cap, 8), np.int32)
+    n = ctypes.c_int32()
+    cta = np.zeros(grid + 1, np.int32)
+    seq = np.zeros(B * Hkv + 1, np.int32)
+    p = ctypes.POINTER(ctypes.c_int32)
+    rc = L.fusor_cuda_decode_plan(kv.ctypes.data_as(p), B, Hkv, grid, segs.ctypes.data_as(p), cap, ctypes.byref(n),
+                                  cta.ctypes.data_as(p), seq.ctypes.data_as(p))
+    assert rc == 0, L.fusor_cuda_last_error(None)
+    return segs[:n.value], cta, seq
+
+
+@pytest.mark.parametrize("kv_len,Hkv,grid", [([1], 1, 1), ([17, 5, 300], 2, 7), ([1024, 8192, 4000, 1025], 8, 296),
+                                             ([131072], 8, 296), (list(range(1, 70)), 3, 148)])
+def test_decode_plan_partitions_every_page_once_and_evenly(kv_len, Hkv, grid):
+    pages = [(n + 15) // 16 for n in kv_len]
+    total = sum(pages) * Hkv
+    grid = min(grid, total)
+    segs, cta, seq = _plan(kv_len, Hkv, grid)
+    seen = {}
+    per_cta = np.zeros(grid, np.int64)
+    assert cta[0] == 0 and cta[-1] == len(segs) and np.all(np.diff(cta) >= 0)
+    for c in range(grid):
+        off = 0
+        for i in range(cta[c], cta[c + 1]):
+            b, hk, p0, p1, n, slot, coff, _ = segs[i]
+            assert slot == i and n == kv_len[b] and 0 <= p0 < p1 <= pages[b] and coff == off
+            for pg in range(p0, p1):
+                assert (b, hk, pg) not in seen
+                seen[(b, hk, pg)] = c
+            off += p1 - p0
+        per_cta[c] = off
+    assert len(seen) == total
+    assert per_cta.max() - per_cta.min() <= 1  # even split
+    # partial records of one (sequence, kv head) are contiguous and in page order
+    for b in range(len(kv_len)):
+        for hk in range(Hkv):
+            s0, s1 = seq[b * Hkv + hk], seq[b * Hkv + hk + 1]
+            assert s1 > s0
+            rng = [(segs[i][2], segs[i][3]) for i in range(s0, s1)]
+            assert all(segs[i][0] == b and segs[i][1] == hk for i in range(s0, s1))
+            assert rng[0][0] == 0 and rng[-1][1] == pages[b] and all(rng[i][1] == rng[i + 1][0] for i in range(len(rng) - 1))
+
+
+def test_decode_plan_rejects_bad_input():
+    from floneum_b200 import _lib
+    L = _lib.load()
+    kv = np.array([0], np.int32)
+    p = ctypes.POINTER(ctypes.c_int32)
+    buf = np.zeros(64, np.int32)
+    n = ctypes.c_int32()
+    rc = L.fusor_cuda_decode_plan(kv.ctypes.data_as(p), 1, 1, 1, buf.ctypes.data_as(p), 8, ctypes.byref(n),
+                                  buf.ctypes.data_as(p), buf.ctypes.data_as(p))
+    assert rc == _lib.INVALID_ARGUMENT
+
+
+def test_mask_mirror_matches_reference_patterns():
+    """AttentionMask / MaskCache mirrors produce the dense values of the reference without a device."""
+    from floneum_b200.cache import AttentionMask, MaskCache
+    from oracle import oracle as O
+    NEG = float("-inf")
+    m = AttentionMask.causal(None, 3)
+    assert m.host_values().tolist() == [[0.0, NEG, NEG], [0.0, 0.0, NEG], [0.0, 0.0, 0.0]]
+    mc = MaskCache()
+    assert mc.get_mask(3, 0, None, None) is mc.get_mask(3, 0, None, None)  # memoised
+    assert mc.get_mask(2, 3, None, None).shape() == (2, 5)
+    for (s, off, w) in [(2, 3, None), (4, 0, 2), (4, 9, 6), (5, 2, 3), (1, 17, None)]:
+        assert np.array_equal(mc.get_mask(s, off, w, None).host_values(), O.get_mask(s, off, w)), (s, off, w)
+    from floneum_b200 import _lib
+    assert mc.get_mask(4, 6, None, None).analytic_kind(4, 10) == (_lib.MASK_CAUSAL, 0)
+    assert mc.get_mask(4, 6, None, None).analytic_kind(4, 11) is None

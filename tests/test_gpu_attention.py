@@ -1,0 +1,277 @@
+"""GPU parity tests of Tensor.flash_attention through the C ABI, against the CPU oracle.
+
+They follow the reference's own attention tests (fusor-ml/core/src/composite/flash_attention.rs:559-1060,
+fusor-ml/fusor/src/composite/flash_attention.rs:203-360) with seeded data and the oracle as the expected value.
+Tolerance of the path: max-abs <= 2e-3 and mean-abs <= 2e-4 against the f32 oracle on the same
+(bf16-rounded where the kernel takes bf16) inputs; f32 inputs through the general kernel are held to 2e-5."""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+NEG = float("-inf")
+
+
+def _mods():
+    import floneum_b200 as fb
+    return fb
+
+
+def _run(device, q, k, v, scale, mask=None, dtype=0, out_dtype=0):
+    fb = _mods()
+    tq = fb.Tensor.from_slice(device, q.shape, q, dtype)
+    tk = fb.Tensor.from_slice(device, k.shape, k, dtype)
+    tv = fb.Tensor.from_slice(device, v.shape, v, dtype)
+    return tq.flash_attention(tk, tv, float(scale), mask, out_dtype).as_slice()
+
+
+def test_flash_attention(device):
+    """test_flash_attention: [1,1,2,2] identity q,k vs unfused attention, tol 0.01 in the reference."""
+    z = np.load(__file__.replace("test_gpu_attention.py", "golden/ref_identity.npz"))
+    out = _run(device, z["q"], z["k"], z["v"], z["scale"])
+    assert out.shape == (1, 1, 2, 2)
+    assert np.abs(out - z["out"]).max() < 1e-6
+
+
+def test_flash_attention_causal_mask(device):
+    """test_flash_attention_causal_mask: explicit [[0,-inf],[0,0]] mask tensor; row 0 equals V row 0."""
+    fb = _mods()
+    z = np.load(__file__.replace("test_gpu_attention.py", "golden/ref_identity_causal.npz"))
+    mask = fb.Tensor.from_slice(device, (2, 2), z["mask"])
+    out = _run(device, z["q"], z["k"], z["v"], z["scale"], (mask, fb.MaskKind.QKMask))
+    assert np.abs(out - z["out"]).max() < 1e-6
+    assert abs(out[0, 0, 0, 0] - 1.0) < 0.01 and abs(out[0, 0, 0, 1] - 2.0) < 0.01
+    # AttentionMask::causal applied analytically gives the same values
+    out2 = _run(device, z["q"], z["k"], z["v"], z["scale"], (fb.AttentionMask.causal(device, 2), fb.MaskKind.QKMask))
+    assert np.array_equal(out, out2)
+    # and its dense tensor is the reference's
+    assert fb.AttentionMask.causal(device, 3).mask().as_slice().tolist() == [[0, NEG, NEG], [0, 0, NEG], [0, 0, 0]]
+
+
+def test_flash_attention_gqa_and_batch_key_mask(device):
+    fb = _mods()
+    z = np.load(__file__.replace("test_gpu_attention.py", "golden/ref_gqa.npz"))
+    out = _run(device, z["q"], z["k"], z["v"], z["scale"])
+    assert out.shape == (1, 4, 2, 2) and np.abs(out - z["out"]).max() < 1e-6
+    z = np.load(__file__.replace("test_gpu_attention.py", "golden/ref_batch_key.npz"))
+    mask = fb.Tensor.from_slice(device, z["mask"].shape, z["mask"])
+    out = _run(device, z["q"], z["k"], z["v"], z["scale"], (mask, fb.MaskKind.BatchKeyMask))
+    assert out.shape == (2, 1, 3, 2) and np.abs(out - z["out"]).max() < 1e-6
+
+
+def test_asserts_like_the_reference(device):
+    fb = _mods()
+    q = fb.Tensor.zeros(device, (1, 3, 2, 2))
+    k = fb.Tensor.zeros(device, (1, 2, 2, 2))
+    with pytest.raises(AssertionError, match="must be divisible"):
+        q.flash_attention(k, k, 1.0, None)
+    q = fb.Tensor.zeros(device, (1, 2, 2, 2))
+    bad = fb.Tensor.zeros(device, (3, 2))
+    with pytest.raises(AssertionError, match="QKMask shape"):
+        q.flash_attention(k, k, 1.0, (bad, fb.MaskKind.QKMask))
+    # the same misuse through the raw C ABI comes back as a status code
+    import ctypes
+    from floneum_b200 import _lib
+    L = _lib.load()
+    q3 = fb.Tensor.zeros(device, (1, 3, 2, 2))
+    out = fb.Tensor.zeros(device, (1, 3, 2, 2))
+    cq, ck, co = q3._c4(), k._c4(), out._c4()
+    rc = L.fusor_cuda_flash_attention(device.handle, ctypes.byref(cq), ctypes.byref(ck), ctypes.byref(ck), 1.0, None, 0, 0,
+                                      ctypes.byref(co))
+    assert rc == _lib.SHAPE_MISMATCH and b"divisible" in L.fusor_cuda_last_error(device.handle)
+
+
+@pytest.mark.parametrize("it", range(12))
+def test_flash_attention_masked_fuzz(device, it):
+    """Seeded test_flash_attention_masked_fuzz: batch 1-2, heads 1-16, seq 1-128, head_dim 1-64, U(-1,1),
+    causal mask with random +-0.25 on the allowed part (general kernel, f32)."""
+    fb = _mods()
+    rng = np.random.default_rng(100 + it)
+    B, H, S, D = int(rng.integers(1, 3)), int(rng.integers(1, 17)), int(rng.integers(1, 129)), int(rng.integers(1, 65))
+    q, k, v = (rng.uniform(-1, 1, (B, H, S, D)).astype(np.float32) for _ in range(3))
+    mask = O.causal_mask(S)
+    mask = np.where(np.isinf(mask), mask, rng.uniform(-0.25, 0.25, (S, S)).astype(np.float32))
+    scale = np.float32(1.0 / np.sqrt(D))
+    want = O.flash_attention(q, k, v, scale, mask, O.MASK_QK)
+    got = _run(device, q, k, v, scale, (fb.Tensor.from_slice(device, mask.shape, mask), fb.MaskKind.QKMask))
+    assert_close(got, want, 2e-5, 2e-6, f"masked fuzz {B}x{H}x{S}x{D}")
+
+
+@pytest.mark.parametrize("it", range(8))
+def test_flash_attention_kv_cache_fuzz(device, it):
+    """Seeded test_flash_attention_kv_cache_fuzz: q_len 1-4 < kv_len <= q_len+31, zero mask."""
+    fb = _mods()
+    rng = np.random.default_rng(200 + it)
+    B, H, D = int(rng.integers(1, 3)), int(rng.integers(1, 9)), int(rng.integers(1, 65))
+    Sq = int(rng.integers(1, 5))
+    Skv = Sq + int(rng.integers(1, 32))
+    q = rng.uniform(-1, 1, (B, H, Sq, D)).astype(np.float32)
+    k, v = (rng.uniform(-1, 1, (B, H, Skv, D)).astype(np.float32) for _ in range(2))
+    mask = np.zeros((Sq, Skv), np.float32)
+    scale = np.float32(1.0 / np.sqrt(D))
+    want = O.flash_attention(q, k, v, scale, mask, O.MASK_QK)
+    got = _run(device, q, k, v, scale, (fb.Tensor.from_slice(device, mask.shape, mask), fb.MaskKind.QKMask))
+    assert_close(got, want, 2e-5, 2e-6, "kv cache fuzz")
+
+
+@pytest.mark.parametrize("it", range(8))
+def test_flash_attention_gqa_fuzz(device, it):
+    """Seeded test_flash_attention_gqa_fuzz: kv_heads 1-4 x groups 1-4, reference head map kv_h = h / groups."""
+    rng = np.random.default_rng(300 + it)
+    Hkv, g = int(rng.integers(1, 5)), int(rng.integers(1, 5))
+    B, S, D = int(rng.integers(1, 3)), int(rng.integers(1, 65)), int(rng.integers(1, 33))
+    q = rng.uniform(-1, 1, (B, Hkv * g, S, D)).astype(np.float32)
+    k, v = (rng.uniform(-1, 1, (B, Hkv, S, D)).astype(np.float32) for _ in range(2))
+    scale = np.float32(1.0 / np.sqrt(D))
+    assert_close(_run(device, q, k, v, scale), O.flash_attention(q, k, v, scale), 2e-5, 2e-6, "gqa fuzz")
+
+
+def test_sliding_window_and_offset_masks(device):
+    """MaskCache masks (sliding window, left-padded offset) applied analytically equal the dense tensors."""
+    fb = _mods()
+    rng = np.random.default_rng(5)
+    mc = fb.MaskCache()
+    for (Sq, off, w) in [(40, 0, 8), (6, 10, 16), (33, 5, None), (1, 50, None)]:
+        Skv = Sq + (min(off, max(w - Sq, 0)) if w is not None else off)
+        q = rng.standard_normal((1, 4, Sq, 32), dtype=np.float32)
+        k, v = (rng.standard_normal((1, 2, Skv, 32), dtype=np.float32) for _ in range(2))
+        m = mc.get_mask(Sq, off, w, device)
+        want = O.flash_attention(q, k, v, 0.2, O.get_mask(Sq, off, w), O.MASK_QK)
+        assert_close(_run(device, q, k, v, 0.2, (m, fb.MaskKind.QKMask)), want, 2e-5, 2e-6, f"analytic {Sq},{off},{w}")
+        dense = fb.AttentionMask.new(m.mask())
+        assert_close(_run(device, q, k, v, 0.2, (dense, fb.MaskKind.QKMask)), want, 2e-5, 2e-6, "dense")
+
+
+def test_cfg1_cpu_reference_config_f32(device):
+    """BASELINE config 1 in full: B1 S512 Hq32 Hkv8 D64 f32, causal, scale 1/8."""
+    fb = _mods()
+    from floneum_b200 import workloads as W
+    w = W.cfg1()
+    want = O.flash_attention(w.q, w.k, w.v, w.scale, O.causal_mask(512), O.MASK_QK)
+    got = _run(device, w.q, w.k, w.v, w.scale, (fb.AttentionMask.causal(device, 512), fb.MaskKind.QKMask))
+    assert_close(got, want, 2e-5, 2e-6, "cfg1")
+
+
+def test_host_entry_point(device):
+    """fusor_cuda_flash_attention_host: host buffers in, host buffer out."""
+    import ctypes
+    from floneum_b200 import _lib
+    L = _lib.load()
+    rng = np.random.default_rng(9)
+    q = rng.standard_normal((2, 4, 50, 64), dtype=np.float32)
+    k, v = (rng.standard_normal((2, 2, 70, 64), dtype=np.float32) for _ in range(2))
+    out = np.empty_like(q)
+
+    def t4(a):
+        t = _lib.Tensor4()
+        t.data, t.dtype = a.ctypes.data, _lib.F32
+        acc = 1
+        for i in range(3, -1, -1):
+            t.shape[i], t.stride[i] = a.shape[i], acc
+            acc *= a.shape[i]
+        return t
+    cq, ck, cv, co = t4(q), t4(k), t4(v), t4(out)
+    rc = L.fusor_cuda_flash_attention_host(device.handle, ctypes.byref(cq), ctypes.byref(ck), ctypes.byref(cv), 0.125, None,
+                                           _lib.MASK_CAUSAL, 0, ctypes.byref(co))
+    _lib.check(rc, device.handle)
+    assert_close(out, O.flash_attention(q, k, v, 0.125, mask_kind=O.MASK_CAUSAL), 2e-5, 2e-6, "host entry")
+
+
+# ----------------------------------------------------------------------------- tensor-core prefill (bf16, D = 128)
+def _bf16_case(seed, B, Hq, Hkv, Sq, Skv, sigma=1.0):
+    from floneum_b200 import workloads as W
+    rng = np.random.default_rng(seed)
+    q = W.bf16_round(sigma * rng.standard_normal((B, Hq, Sq, 128), dtype=np.float32))
+    k = W.bf16_round(sigma * rng.standard_normal((B, Hkv, Skv, 128), dtype=np.float32))
+    v = W.bf16_round(sigma * rng.standard_normal((B, Hkv, Skv, 128), dtype=np.float32))
+    return q, k, v, np.float32(1.0 / np.sqrt(128.0))
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,causal", [
+    (1, 1, 1, 128, 128, True), (1, 4, 2, 200, 200, True), (2, 8, 2, 256, 256, False), (1, 4, 1, 1, 300, True),
+    (1, 2, 2, 129, 257, True), (1, 4, 4, 384, 512, True), (2, 4, 2, 77, 77, False), (1, 8, 8, 640, 640, True),
+    (1, 2, 1, 1000, 1000, True), (1, 1, 1, 5, 5, True),
+])
+def test_prefill_tensor_core_shapes(device, B, Hq, Hkv, Sq, Skv, causal):
+    """Ragged and offset shapes through the tcgen05 kernel: partial query/key tiles, Skv > Sq, GQA, batch."""
+    fb = _mods()
+    q, k, v, scale = _bf16_case(1000 * Sq + Skv, B, Hq, Hkv, Sq, Skv)
+    mask = (fb.MaskCache().get_mask(Sq, Skv - Sq, None, device), fb.MaskKind.QKMask) if causal else None
+    got = _run(device, q, k, v, scale, mask, dtype=1)
+    want = O.flash_attention(q, k, v, scale, mask_kind=O.MASK_CAUSAL if causal else O.MASK_NONE, skip_masked=True)
+    assert_close(got, want, what=f"prefill {B}x{Hq}/{Hkv}x{Sq}/{Skv} causal={causal}")
+
+
+def test_prefill_golden_fixture(device):
+    fb = _mods()
+    z = np.load(__file__.replace("test_gpu_attention.py", "golden/seeded_bf16_d128_causal.npz"))
+    got = _run(device, z["q"], z["k"], z["v"], z["scale"], (fb.AttentionMask.causal(device, 200), fb.MaskKind.QKMask), dtype=1)
+    assert_close(got, z["out"], what="golden bf16 d128")
+
+
+def test_prefill_matches_general_kernel(device):
+    """The two GPU kernels agree on the same bf16 inputs (general kernel = f32 arithmetic)."""
+    import ctypes
+    fb = _mods()
+    from floneum_b200 import _lib
+    q, k, v, scale = _bf16_case(77, 1, 8, 2, 300, 300)
+    tq, tk, tv = (fb.Tensor.from_slice(device, a.shape, a, 1) for a in (q, k, v))
+    fast = tq.flash_attention(tk, tv, float(scale), (fb.AttentionMask.causal(device, 300), fb.MaskKind.QKMask)).as_slice()
+    out = fb.Tensor.empty(device, q.shape, 0)
+    cq, ck, cv, co = tq._c4(), tk._c4(), tv._c4(), out._c4()
+    _lib.check(_lib.load().fusor_cuda_flash_attention_general(device.handle, ctypes.byref(cq), ctypes.byref(ck), ctypes.byref(cv),
+                                                              ctypes.c_float(scale), None, _lib.MASK_CAUSAL, 0, ctypes.byref(co)),
+               device.handle)
+    assert_close(fast, out.as_slice(), what="tcgen05 vs general")
+
+
+def test_prefill_strided_views_and_bf16_out(device):
+    """Non-contiguous [B,H,S,D] views (a transposed [B,S,H,D] buffer, as after the projection reshape) and bf16 output."""
+    fb = _mods()
+    q, k, v, scale = _bf16_case(31, 2, 4, 2, 160, 160)
+
+    def strided(a):
+        B, H, S, D = a.shape
+        buf = fb.Tensor.from_slice(device, (B, S, H, D), np.ascontiguousarray(a.transpose(0, 2, 1, 3)), 1)
+        return fb.Tensor(device, buf.ptr, (B, H, S, D), 1, (S * H * D, D, H * D, 1), owner=buf)
+    got = strided(q).flash_attention(strided(k), strided(v), float(scale), (fb.AttentionMask.causal(device, 160), fb.MaskKind.QKMask), out_dtype=1).as_slice()
+    want = O.flash_attention(q, k, v, scale, mask_kind=O.MASK_CAUSAL)
+    assert_close(got, O.bf16_round(want), max_tol=2e-3 + 2.0 ** -7, mean_tol=2e-3, what="strided, bf16 out")
+
+
+def test_prefill_cfg5_value_distribution(device):
+    """cfg5's distribution at reduced length: N(0, 0.5^2) with 5% of K rows x8 (softmax range stress)."""
+    fb = _mods()
+    from floneum_b200 import workloads as W
+    w = W.cfg5(S=1536, Hq=8, Hkv=2)
+    got = _run(device, w.q, w.k, w.v, w.scale, (fb.AttentionMask.causal(device, 1536), fb.MaskKind.QKMask), dtype=1)
+    want = O.flash_attention(w.q, w.k, w.v, w.scale, mask_kind=O.MASK_CAUSAL, skip_masked=True)
+    assert_close(got, want, what="cfg5 distribution")
+
+
+def test_prefill_cfg2_full_size_sampled_rows(device):
+    """BASELINE config 2 at full size (B4 S4096 Hq32 Hkv8 D128): sampled rows against the oracle, plus
+    size-independent properties: row 0 of every head equals V row 0, and permuting batches permutes outputs."""
+    fb = _mods()
+    from floneum_b200 import workloads as W
+    w = W.cfg2()
+    B, Hq, S, D = w.q.shape
+    tq, tk, tv = (fb.Tensor.from_slice(device, a.shape, a, 1) for a in (w.q, w.k, w.v))
+    mask = (fb.AttentionMask.causal(device, S), fb.MaskKind.QKMask)
+    got = tq.flash_attention(tk, tv, w.scale, mask).as_slice()
+    assert np.isfinite(got).all()
+    rng = np.random.default_rng(0)
+    rows = np.unique(np.concatenate([rng.integers(0, B * Hq * S, 1500), np.arange(0, B * Hq * S, S), np.arange(S - 1, B * Hq * S, S),
+                                     np.arange(127, B * Hq * S, 8 * S), np.arange(128, B * Hq * S, 8 * S)]))
+    want = O.flash_attention(w.q, w.k, w.v, w.scale, mask_kind=O.MASK_CAUSAL, rows=rows, skip_masked=True)
+    assert_close(got.reshape(-1, D)[rows], want, what="cfg2 sampled rows")
+    g = Hq // w.k.shape[1]
+    for b in range(B):
+        for h in range(Hq):
+            assert np.abs(got[b, h, 0] - w.v[b, h // g, 0]).max() <= 2e-3
+    perm = [2, 0, 3, 1]
+    tq2, tk2, tv2 = (fb.Tensor.from_slice(device, a.shape, np.ascontiguousarray(a[perm]), 1) for a in (w.q, w.k, w.v))
+    got2 = tq2.flash_attention(tk2, tv2, w.scale, mask).as_slice()
+    assert np.array_equal(got2, got[perm])

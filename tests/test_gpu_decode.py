@@ -1,0 +1,199 @@
+"""GPU parity tests of the paged KV cache, split-KV decode and the KvCache mirror, against the CPU oracle."""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _fb():
+    import floneum_b200 as fb
+    return fb
+
+
+def _install(device, w):
+    fb = _fb()
+    B = w.q.shape[0]
+    cache = fb.PagedKvCache(device, B, w.k_pages.shape[1], w.k_pages.shape[3], w.k_pages.shape[0], w.page_table.shape[1])
+    cache.write_pages(0, w.k_pages, w.v_pages)
+    cache.set_page_table(w.page_table, w.kv_len)
+    return cache
+
+
+def _oracle_decode(w):
+    return np.stack([O.flash_attention(w.q[b:b + 1], w.k_dense[b][None], w.v_dense[b][None], w.scale)[0]
+                     for b in range(w.q.shape[0])])
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,lo,hi", [(1, 4, 1, 1, 1), (3, 8, 2, 20, 90), (4, 32, 8, 100, 700), (2, 8, 8, 15, 17),
+                                             (5, 16, 2, 1, 40), (2, 64, 8, 3000, 5000)])
+def test_paged_decode_ragged(device, B, Hq, Hkv, lo, hi):
+    """Ragged lengths (including partial last pages and 1-token sequences), permuted page table, g = 1..8."""
+    fb = _fb()
+    from floneum_b200 import workloads as W
+    w = W.cfg3(B=B, Hq=Hq, Hkv=Hkv, lo=lo, hi=hi)
+    cache = _install(device, w)
+    q = fb.Tensor.from_slice(device, w.q.shape, w.q, 1)
+    got = cache.decode(q, w.scale).as_slice()
+    assert_close(got, _oracle_decode(w), what=f"decode B{B} Hq{Hq}/{Hkv} len[{lo},{hi}]")
+    # f32 query tensor (the reference call site passes f32) gives the same result
+    got32 = cache.decode(fb.Tensor.from_slice(device, w.q.shape, w.q, 0), w.scale).as_slice()
+    assert np.array_equal(got, got32)
+    # host-memory entry point
+    assert np.array_equal(cache.decode_host(w.q, w.scale), got)
+
+
+def test_paged_decode_golden_fixture(device):
+    fb = _fb()
+    z = np.load(__file__.replace("test_gpu_decode.py", "golden/seeded_decode_paged.npz"))
+    cache = fb.PagedKvCache(device, 3, 2, 128, z["k_pages"].shape[0], z["page_table"].shape[1])
+    cache.write_pages(0, z["k_pages"], z["v_pages"])
+    cache.set_page_table(z["page_table"], z["kv_len"])
+    got = cache.decode(fb.Tensor.from_slice(device, z["q"].shape, z["q"], 1), float(z["scale"])).as_slice()
+    assert_close(got, z["out"], what="golden decode")
+
+
+def test_decode_head_dim_64(device):
+    fb = _fb()
+    from floneum_b200 import workloads as W
+    rng = np.random.default_rng(12)
+    B, Hq, Hkv, D = 2, 8, 2, 64
+    lens = np.array([75, 130])
+    q = W.bf16_round(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+    cache = fb.KvCache.new(2, 1024)
+    ks = W.bf16_round(rng.standard_normal((B, Hkv, 130, D), dtype=np.float32))
+    vs = W.bf16_round(rng.standard_normal((B, Hkv, 130, D), dtype=np.float32))
+    paged = fb.PagedKvCache(device, B, Hkv, D, 32, 16)
+    pt = np.arange(32, dtype=np.int32).reshape(2, 16)[:, ::-1].copy()
+    kp = np.zeros((32, Hkv, 16, D), np.uint16)
+    vp = np.zeros_like(kp)
+    for b in range(B):
+        for t in range(lens[b]):
+            kp[pt[b, t // 16], :, t % 16] = W.bf16_bits(ks[b, :, t])
+            vp[pt[b, t // 16], :, t % 16] = W.bf16_bits(vs[b, :, t])
+    paged.write_pages(0, kp, vp)
+    paged.set_page_table(pt, lens)
+    got = paged.decode(fb.Tensor.from_slice(device, q.shape, q, 1), 0.125).as_slice()
+    want = np.stack([O.flash_attention(q[b:b + 1], ks[b:b + 1, :, :lens[b]], vs[b:b + 1, :, :lens[b]], 0.125)[0] for b in range(B)])
+    assert_close(got, want, what="decode D=64")
+    del cache
+
+
+def test_decode_partial_and_lse_combine(device):
+    """KV-sequence chunks: per-chunk partials {m, l, O} merged by log-sum-exp equal attention over all keys,
+    and each partial matches the oracle's partial of that key range."""
+    fb = _fb()
+    from floneum_b200 import workloads as W
+    from floneum_b200.cache import lse_combine
+    world = 4
+    full = W.cfg4(Skv=4096 + 160, Hq=16, Hkv=2)
+    parts = []
+    for r in range(world):
+        w = W.cfg4(Skv=4096 + 160, Hq=16, Hkv=2, rank=r, world=world)
+        cache = _install(device, w)
+        p = cache.decode_partial(fb.Tensor.from_slice(device, w.q.shape, w.q, 1), w.scale)
+        parts.append(p.as_slice())
+        lo, hi = r * (4096 + 160) // world, (r + 1) * (4096 + 160) // world
+        want = O.attention_partial(full.q, full.k_dense[0][None], full.v_dense[0][None], full.scale, lo, hi)[:, :, 0]
+        got = parts[-1]
+        assert np.abs(got[..., 0] - want[..., 0]).max() < 1e-4          # m
+        assert np.abs(got[..., 1] / want[..., 1] - 1).max() < 2e-3      # l
+        assert np.abs(got[..., 2:] - want[..., 2:]).max() < 2e-2 * np.abs(want[..., 2:]).max()
+    stacked = fb.Tensor.from_slice(device, (world,) + parts[0].shape, np.stack(parts))
+    got = lse_combine(device, stacked).as_slice()
+    want = O.flash_attention(full.q, full.k_dense[0][None], full.v_dense[0][None], full.scale)[:, :, 0]
+    assert_close(got, want, what="chunked decode + combine")
+    # an empty part is a no-op
+    empty = np.zeros_like(parts[0])
+    empty[..., 0] = -np.inf
+    stacked = fb.Tensor.from_slice(device, (world + 1,) + parts[0].shape, np.stack(parts + [empty]))
+    assert np.array_equal(lse_combine(device, stacked).as_slice(), got)
+
+
+def test_kv_cache_append_reset_like_the_reference(device):
+    """test_kv_cache_first_append / _multiple_appends / _reset (fusor/src/cache/kv_cache.rs:70-158), with the
+    sequence on axis 2 of [B, Hkv, S, D] as kalosm-llama uses the cache."""
+    fb = _fb()
+    D = 128
+    cache = fb.KvCache.new(2, 64)
+    k1 = np.arange(D, dtype=np.float32).reshape(1, 1, 1, D)
+    v1 = k1 + 300
+    k, v = cache.append(device, fb.Tensor.from_slice(device, k1.shape, k1), fb.Tensor.from_slice(device, v1.shape, v1))
+    assert k.shape() == (1, 1, 1, D) and v.shape() == (1, 1, 1, D)
+    assert np.array_equal(k.as_slice(), k1) and np.array_equal(v.as_slice(), v1)
+    k2, v2 = k1 + 1000, v1 + 1000
+    k, v = cache.append(device, fb.Tensor.from_slice(device, k2.shape, k2), fb.Tensor.from_slice(device, v2.shape, v2))
+    assert k.shape() == (1, 1, 2, D) and cache.current_seq_len() == 2
+    assert np.array_equal(k.as_slice(), np.concatenate([k1, k2], 2)) and np.array_equal(v.as_slice(), np.concatenate([v1, v2], 2))
+    cache.reset()
+    assert cache.k() is None and cache.v() is None and cache.current_seq_len() == 0
+
+
+def test_kv_cache_growth_eviction_matches_tensor_cache_semantics(device):
+    """Append / evict sequences against the numpy restatement of TensorCache (tensor_cache.rs:48-118)."""
+    fb = _fb()
+    rng = np.random.default_rng(3)
+    B, Hkv, D, mx = 2, 2, 64, 50
+    cache, ref = fb.KvCache.new(2, mx), O.KvCacheOracle(2, mx)
+    for n in [1, 7, 16, 1, 20, 9, 33, 60, 2]:
+        k = O.bf16_round(rng.standard_normal((B, Hkv, n, D), dtype=np.float32))
+        v = O.bf16_round(rng.standard_normal((B, Hkv, n, D), dtype=np.float32))
+        gk, gv = cache.append(device, fb.Tensor.from_slice(device, k.shape, k), fb.Tensor.from_slice(device, v.shape, v))
+        rk, rv = ref.append(k, v)
+        assert cache.current_seq_len() == ref.current_seq_len()
+        assert gk.shape() == rk.shape
+        assert np.array_equal(gk.as_slice(), rk) and np.array_equal(gv.as_slice(), rv), f"after append of {n}"
+
+
+def test_decode_through_the_reference_call_pattern(device):
+    """LlamaAttention::forward's sequence (attention_layer.rs:405-448): prefill appends S tokens and attends with the
+    causal mask; every decode step appends one token and attends with get_mask(1, index_pos)."""
+    fb = _fb()
+    rng = np.random.default_rng(21)
+    B, Hq, Hkv, D, S, steps = 1, 8, 2, 128, 70, 5
+    scale = float(1 / np.sqrt(D))
+    ks = O.bf16_round(rng.standard_normal((B, Hkv, S + steps, D), dtype=np.float32))
+    vs = O.bf16_round(rng.standard_normal((B, Hkv, S + steps, D), dtype=np.float32))
+    qs = O.bf16_round(rng.standard_normal((B, Hq, S + steps, D), dtype=np.float32))
+    cache, masks = fb.KvCache.new(2, 4096), fb.MaskCache()
+    T = lambda a: fb.Tensor.from_slice(device, a.shape, np.ascontiguousarray(a))
+    k, v = cache.append(device, T(ks[:, :, :S]), T(vs[:, :, :S]))
+    out = T(qs[:, :, :S]).flash_attention(k, v, scale, (masks.get_mask(S, 0, None, device), fb.MaskKind.QKMask)).as_slice()
+    assert_close(out, O.flash_attention(qs[:, :, :S], ks[:, :, :S], vs[:, :, :S], scale, mask_kind=O.MASK_CAUSAL), what="prefill via cache")
+    for t in range(S, S + steps):
+        k, v = cache.append(device, T(ks[:, :, t:t + 1]), T(vs[:, :, t:t + 1]))
+        before = device.launch_count()
+        out = T(qs[:, :, t:t + 1]).flash_attention(k, v, scale, (masks.get_mask(1, t, None, device), fb.MaskKind.QKMask)).as_slice()
+        assert device.launch_count() - before == 2  # split-KV kernel + combine: the pages are read in place
+        want = O.flash_attention(qs[:, :, t:t + 1], ks[:, :, :t + 1], vs[:, :, :t + 1], scale)
+        assert_close(out, want, what=f"decode step {t}")
+    # chunked continuation: 3 new tokens on a warm cache (structured.rs:143-150)
+    cache2 = fb.KvCache.new(2, 4096)
+    cache2.append(device, T(ks[:, :, :S]), T(vs[:, :, :S]))
+    k, v = cache2.append(device, T(ks[:, :, S:S + 3]), T(vs[:, :, S:S + 3]))
+    out = T(qs[:, :, S:S + 3]).flash_attention(k, v, scale, (masks.get_mask(3, S, None, device), fb.MaskKind.QKMask)).as_slice()
+    want = O.flash_attention(qs[:, :, S:S + 3], ks[:, :, :S + 3], vs[:, :, :S + 3], scale, mask_kind=O.MASK_CAUSAL)
+    assert_close(out, want, what="chunked continuation")
+
+
+def test_bad_page_table_is_rejected_on_the_host(device):
+    fb = _fb()
+    cache = fb.PagedKvCache(device, 1, 1, 128, 4, 4)
+    with pytest.raises(fb.FusorCudaError, match="outside the pool"):
+        cache.set_page_table(np.array([[0, 9, 0, 0]], np.int32), np.array([20], np.int32))
+    with pytest.raises(fb.FusorCudaError, match="mapped twice"):
+        cache.set_page_table(np.array([[1, 1, 0, 0]], np.int32), np.array([20], np.int32))
+    with pytest.raises(fb.FusorCudaError):
+        fb.PagedKvCache(device, 1, 1, 128, 2, 2).append(fb.Tensor.zeros(device, (1, 1, 40, 128)), fb.Tensor.zeros(device, (1, 1, 40, 128)))
+
+
+def test_cfg3_full_size(device):
+    """BASELINE config 3 at full size: B64, Hq32, Hkv8, D128, kv_len ~ U[1024, 8192], permuted pages."""
+    fb = _fb()
+    from floneum_b200 import workloads as W
+    w = W.cfg3()
+    cache = _install(device, w)
+    got = cache.decode(fb.Tensor.from_slice(device, w.q.shape, w.q, 1), w.scale).as_slice()
+    assert_close(got, _oracle_decode(w), what="cfg3 full")
