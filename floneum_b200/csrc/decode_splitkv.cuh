@@ -101,9 +101,12 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
         for (int sg = seg_begin; sg < seg_end && ok; ++sg) {
             const DecodeSegment S = P.segs[sg];
             const int* pt = P.page_table + (long long)S.b * P.max_pages;
+            int next_phys = (S.page_begin + lane < S.page_end) ? pt[S.page_begin + lane] : 0;
             for (int p0 = S.page_begin; p0 < S.page_end && ok; p0 += 32) {
                 const int n = min(32, S.page_end - p0);
-                const int my_phys = (lane < n) ? pt[p0 + lane] : 0;
+                const int my_phys = next_phys;
+                // page ids of the next batch are fetched before this batch is issued
+                next_phys = (p0 + 32 + lane < S.page_end) ? pt[p0 + 32 + lane] : 0;
                 for (int j = 0; j < n && ok; ++j, ++i) {
                     int phys = __shfl_sync(0xffffffffu, my_phys, j);
                     int good = 1;
@@ -171,9 +174,10 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
             for (int nd = 0; nd < D / 8; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.0f;
 
             const int n_pages = S.page_end - S.page_begin;
-            // first page of this segment (in CTA stream numbering) that belongs to this warp
-            int i = S.cta_page_off + ((warp - S.cta_page_off % DEC_NW + DEC_NW) % DEC_NW);
-            for (; i < S.cta_page_off + n_pages; i += DEC_NW) {
+            // Every consumer warp waits for every page of the CTA's stream in order, so that it observes each
+            // phase of each ring slot's barrier (a warp that skipped the pages of other warps could meet a slot
+            // two phases later, which a parity wait cannot tell from "ready"); only the owner processes a page.
+            for (int i = S.cta_page_off; i < S.cta_page_off + n_pages; ++i) {
                 if (aborted) break;
                 const int slot = i % R;
                 const bool got = mbar_wait(full + slot, (i / R) & 1, abort_flag, P.err);
@@ -181,6 +185,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
                     aborted = true;
                     break;
                 }
+                if (i % DEC_NW != warp) continue;
                 const int tok0 = (S.page_begin + (i - S.cta_page_off)) * DEC_PT;
                 const uint32_t kb = ksm_u + slot * PAGE_BYTES, vb = vsm_u + slot * PAGE_BYTES;
 
@@ -220,11 +225,16 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
                 const float m_sub = (m_new == -INFINITY) ? 0.0f : m_new;
                 const float alpha = fast_exp2(m_run - m_sub);
                 m_run = m_new;
-                __nv_bfloat162 p01 = __floats2bfloat162_rn(fast_exp2(t[0] - m_sub), fast_exp2(t[1] - m_sub));
-                __nv_bfloat162 p23 = __floats2bfloat162_rn(fast_exp2(t[2] - m_sub), fast_exp2(t[3] - m_sub));
-                // the row sum uses the rounded weights the MMA will use
-                l_run = l_run * alpha + (__low2float(p01) + __high2float(p01)) + (__low2float(p23) + __high2float(p23));
-                const uint32_t pa[4] = {*reinterpret_cast<uint32_t*>(&p01), 0u, *reinterpret_cast<uint32_t*>(&p23), 0u};
+                // P is handed to the tensor cores as bf16 hi + bf16 lo (two MMAs per tile): 8 significant bits
+                // alone put sequences of a few tokens above the 2e-3 tolerance, and the tensor pipe is idle here.
+                const float p0 = fast_exp2(t[0] - m_sub), p1 = fast_exp2(t[1] - m_sub);
+                const float p2 = fast_exp2(t[2] - m_sub), p3 = fast_exp2(t[3] - m_sub);
+                const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
+                const __nv_bfloat162 l01 = __floats2bfloat162_rn(p0 - __low2float(h01), p1 - __high2float(h01));
+                const __nv_bfloat162 l23 = __floats2bfloat162_rn(p2 - __low2float(h23), p3 - __high2float(h23));
+                l_run = l_run * alpha + (p0 + p1) + (p2 + p3);
+                const uint32_t pa[4] = {*reinterpret_cast<const uint32_t*>(&h01), 0u, *reinterpret_cast<const uint32_t*>(&h23), 0u};
+                const uint32_t pl[4] = {*reinterpret_cast<const uint32_t*>(&l01), 0u, *reinterpret_cast<const uint32_t*>(&l23), 0u};
 #pragma unroll
                 for (int nd = 0; nd < D / 8; ++nd) {
                     o[nd][0] *= alpha;
@@ -240,6 +250,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
                     ldmatrix_x4_trans(bfr, addr);
                     mma_bf16_16816(o[2 * ndp], pa, bfr[0], bfr[1]);
                     mma_bf16_16816(o[2 * ndp + 1], pa, bfr[2], bfr[3]);
+                    mma_bf16_16816(o[2 * ndp], pl, bfr[0], bfr[1]);
+                    mma_bf16_16816(o[2 * ndp + 1], pl, bfr[2], bfr[3]);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty + slot);

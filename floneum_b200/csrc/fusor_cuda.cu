@@ -37,6 +37,11 @@ struct fusor_cuda_ctx {
     size_t scratch_bytes = 0;
     void* pinned = nullptr;
     size_t pinned_bytes = 0;
+    // f16 copy of V for the tensor-core prefill kernel, and the ring of overflow flags its pre-pass writes
+    void* v16 = nullptr;
+    size_t v16_bytes = 0;
+    int* d_flags = nullptr;  // [256]
+    unsigned flag_counter = 0;
 };
 
 static thread_local std::string g_last_error;
@@ -119,7 +124,8 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
         }
         ctx->owns_stream = true;
     }
-    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&ctx->d_flags, 256 * sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_flags, 0, 256 * sizeof(int)) != cudaSuccess) {
         delete ctx;
         return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cannot allocate the device error word");
     }
@@ -131,8 +137,7 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
     }
     ctx->encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
     // opt in to large dynamic shared memory once per context
-    cudaFuncSetAttribute(prefill_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
-    cudaFuncSetAttribute(prefill_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
+    cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
     cudaFuncSetAttribute(decode_splitkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024);
     cudaFuncSetAttribute(decode_splitkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024);
     cudaFuncSetAttribute(general_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -152,6 +157,8 @@ extern "C" int32_t fusor_cuda_ctx_destroy(fusor_cuda_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    if (ctx->v16) cudaFree(ctx->v16);
+    if (ctx->d_flags) cudaFree(ctx->d_flags);
     if (ctx->d_err) cudaFree(ctx->d_err);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -330,7 +337,8 @@ static int32_t launch_general(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
 }
 
 // [B,H,S,D] view -> 4-D tensor map {D, S, H, B}, box {64, box_rows, 1, 1}, 128-byte swizzle, zero fill.
-static int32_t make_tmap_bhsd(fusor_cuda_ctx* ctx, CUtensorMap* tm, const fusor_cuda_tensor4* t, int box_rows) {
+static int32_t make_tmap_bhsd(fusor_cuda_ctx* ctx, CUtensorMap* tm, const fusor_cuda_tensor4* t, int box_rows,
+                              CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
     cuuint64_t dims[4] = {(cuuint64_t)t->shape[3], (cuuint64_t)t->shape[2], (cuuint64_t)t->shape[1], (cuuint64_t)t->shape[0]};
     cuuint64_t strides[3] = {(cuuint64_t)t->stride[2] * 2, (cuuint64_t)t->stride[1] * 2, (cuuint64_t)t->stride[0] * 2};
     // an extent-1 axis may carry any stride; give the encoder a legal one
@@ -338,13 +346,14 @@ static int32_t make_tmap_bhsd(fusor_cuda_ctx* ctx, CUtensorMap* tm, const fusor_
         if (dims[i + 1] == 1) strides[i] = (i == 0 ? dims[0] * 2 : strides[i - 1] * dims[i]);
     cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = ctx->encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t->data, dims, strides, box, estr,
+    CUresult r = ctx->encode(tm, dt, 4, t->data, dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "cuTensorMapEncodeTiled failed with %d", (int)r);
     return FUSOR_CUDA_OK;
 }
 
+static void set_contiguous(fusor_cuda_tensor4* t);
 static bool tma_view_ok(const fusor_cuda_tensor4* t) {
     if (t->dtype != FUSOR_CUDA_BF16) return false;
     if (reinterpret_cast<uintptr_t>(t->data) % 16) return false;
@@ -352,8 +361,6 @@ static bool tma_view_ok(const fusor_cuda_tensor4* t) {
         if (t->shape[i] > 1 && (t->stride[i] % 8 != 0 || t->stride[i] <= 0)) return false;
     return true;
 }
-
-static int g_prefill_p_format = 0;  // 0 = f16 P (default), 1 = bf16 P
 
 static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
                              const fusor_cuda_tensor4* v, float scale, int32_t mask_kind, const fusor_cuda_tensor4* out) {
@@ -368,13 +375,41 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
     return true;
 }
 
+// p_mode: 0 = f16 P with an f16 copy of V (falls back to bf16 on the device when V overflows f16), 1 = bf16 P.
 static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
                               const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
-                              const fusor_cuda_tensor4* out, float* debug) {
-    CUtensorMap tmQ, tmK, tmV;
+                              const fusor_cuda_tensor4* out, float* debug, int p_mode) {
+    CUtensorMap tmQ, tmK, tmV, tmV16;
     TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM));
     TRY(make_tmap_bhsd(ctx, &tmK, k, PF_BN));
     TRY(make_tmap_bhsd(ctx, &tmV, v, PF_BN));
+    tmV16 = tmV;
+    const int* flag = nullptr;
+    if (p_mode == 0) {
+        const size_t n = (size_t)S.B * S.Hkv * S.Skv * S.D;
+        if (ctx->v16_bytes < n * 2) {
+            CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            if (ctx->v16) CUDA_TRY(ctx, cudaFree(ctx->v16));
+            ctx->v16 = nullptr;
+            ctx->v16_bytes = 0;
+            CUDA_TRY(ctx, cudaMalloc(&ctx->v16, n * 2));
+            ctx->v16_bytes = n * 2;
+        }
+        const unsigned slot = ctx->flag_counter++ % 256;
+        CastVParams C;
+        C.src = (const __nv_bfloat16*)v->data; C.dst = (__half*)ctx->v16;
+        C.s0 = v->stride[0]; C.s1 = v->stride[1]; C.s2 = v->stride[2];
+        C.H = S.Hkv; C.S = S.Skv; C.D = S.D; C.n_vec = (long long)(n / 8);
+        C.overflow = ctx->d_flags + slot; C.clear_slot = ctx->d_flags + (slot + 128) % 256;
+        const int blocks = (int)std::min<long long>((C.n_vec + 255) / 256, (long long)ctx->num_sms * 8);
+        cast_v_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>(C);
+        TRY(launch_check(ctx, "cast_v_to_f16_kernel"));
+        fusor_cuda_tensor4 v16 = *v;
+        v16.data = ctx->v16;
+        set_contiguous(&v16);
+        TRY(make_tmap_bhsd(ctx, &tmV16, &v16, PF_BN, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
+        flag = ctx->d_flags + slot;
+    }
     PrefillParams P;
     P.out = out->data; P.out_dtype = out->dtype;
     for (int i = 0; i < 3; ++i) P.os[i] = out->stride[i];
@@ -384,12 +419,10 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
     P.err = ctx->d_err;
     P.debug = debug;
+    P.v_f16_overflow = flag;
     const long long grid = (long long)P.n_q_tiles * S.Hq * S.B;
     if (grid > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "grid too large");
-    if (g_prefill_p_format == 0)
-        prefill_sm100_kernel<0><<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, P);
-    else
-        prefill_sm100_kernel<1><<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, P);
+    prefill_sm100_kernel<<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, P);
     return launch_check(ctx, "prefill_sm100_kernel");
 }
 
@@ -399,7 +432,7 @@ extern "C" int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_c
     AttnShape S;
     TRY(validate_attention(ctx, q, k, v, mask, mask_kind, window, out, &S));
     DeviceGuard g(ctx->device);
-    if (prefill_eligible(S, q, k, v, scale, mask_kind, out)) return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, nullptr);
+    if (prefill_eligible(S, q, k, v, scale, mask_kind, out)) return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, nullptr, 0);
     return launch_general(ctx, S, q, k, v, scale, mask, mask_kind, window, out);
 }
 
@@ -423,11 +456,7 @@ extern "C" int32_t fusor_cuda_prefill_probe(fusor_cuda_ctx* ctx, const fusor_cud
     DeviceGuard g(ctx->device);
     if (!prefill_eligible(S, q, k, v, scale, mask_kind, out))
         return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "arguments are not eligible for the tensor-core prefill kernel");
-    const int saved = g_prefill_p_format;
-    g_prefill_p_format = p_format ? 1 : 0;
-    int32_t rc = launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, debug_device);
-    g_prefill_p_format = saved;
-    return rc;
+    return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, debug_device, p_format ? 1 : 0);
 }
 
 // --------------------------------------------------------------------------- host-memory variants

@@ -43,15 +43,20 @@ struct PrefillParams {
     int n_q_tiles;
     int* err;
     float* debug;              // optional [128][128 + 128 + 2] dump from CTA 0: raw S of tile 0, un-normalised O, m, l
+    const int* v_f16_overflow; // written by the V pre-pass: non-zero when some |v| does not fit f16; null = no f16 copy
 };
 
 constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_TILE_BYTES * (1 + 2 * PF_STAGES) + 256;
 
-// kPFormat: 0 = P stored as f16, 1 = P stored as bf16 (V is always bf16).
-template <int kPFormat>
+// P (the softmax weights handed to the second MMA) and V must have the same 16-bit type: kind::f16 rejects a
+// mixed f16 / bf16 operand pair.  bf16 weights (8 significant bits) put rows with few keys above the 2e-3
+// tolerance, so the host converts V to f16 once per call (cast_v_to_f16_kernel) and the kernel keeps P in f16
+// (11 bits).  When some |v| exceeds the f16 range the pre-pass raises a flag and every CTA falls back to bf16
+// P with the original bf16 V: the choice is a uniform runtime branch (descriptor bits and the tensor map).
 __global__ void __launch_bounds__(PF_THREADS, 1)
     prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmV, const PrefillParams P) {
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmV16,
+                         const PrefillParams P) {
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_sm = base;
@@ -70,6 +75,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool use_f16 = P.v_f16_overflow != nullptr && *P.v_f16_overflow == 0;
 
     // ---- which tile: heavy (late) query tiles first; consecutive CTAs share a kv head
     const int heads_total = P.Hq * P.B;
@@ -99,7 +105,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
         mbar_fence_init();
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
-        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(use_f16 ? &tmV16 : &tmV);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, PF_TMEM_COLS);
@@ -124,8 +130,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 tma_load_4d(k_sm + s * PF_TILE_BYTES + PF_HALF_BYTES, &tmK, k_full + s, 64, j * PF_BN, hk, b);
                 if (use > 0 && !mbar_wait(v_empty + s, (use - 1) & 1, abort_flag, P.err)) break;
                 mbar_arrive_expect_tx(v_full + s, PF_TILE_BYTES);
-                tma_load_4d(v_sm + s * PF_TILE_BYTES, &tmV, v_full + s, 0, j * PF_BN, hk, b);
-                tma_load_4d(v_sm + s * PF_TILE_BYTES + PF_HALF_BYTES, &tmV, v_full + s, 64, j * PF_BN, hk, b);
+                const CUtensorMap* tv = use_f16 ? &tmV16 : &tmV;
+                tma_load_4d(v_sm + s * PF_TILE_BYTES, tv, v_full + s, 0, j * PF_BN, hk, b);
+                tma_load_4d(v_sm + s * PF_TILE_BYTES + PF_HALF_BYTES, tv, v_full + s, 64, j * PF_BN, hk, b);
             }
         }
     } else if (warp == 1) {
@@ -134,7 +141,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
             // S = Q K^T : A, B bf16, both K-major, M = N = 128
             constexpr uint32_t idesc_qk = make_idesc_f16(1, 1, 0, 0, PF_BM, PF_BN);
             // O += P V  : A = P (TMEM, K-major), B = V bf16 MN-major, M = 128, N = D
-            constexpr uint32_t idesc_pv = make_idesc_f16(kPFormat, 1, 0, 1, PF_BM, PF_D);
+            const uint32_t idesc_pv = use_f16 ? make_idesc_f16(0, 0, 0, 1, PF_BM, PF_D) : make_idesc_f16(1, 1, 0, 1, PF_BM, PF_D);
             const uint32_t q_addr = smem_u32(q_sm);
             auto issue_qk = [&](int j) {
                 const uint32_t k_addr = smem_u32(k_sm + (j % PF_STAGES) * PF_TILE_BYTES);
@@ -229,7 +236,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                     const float p0 = fast_exp2(__uint_as_float(sr[c][2 * i]) - m_ref);
                     const float p1 = fast_exp2(__uint_as_float(sr[c][2 * i + 1]) - m_ref);
                     psum += p0 + p1;
-                    pk[i] = kPFormat == 0 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+                    pk[i] = use_f16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
                 }
                 tmem_st16(p_tmem + c * 16, pk);
             }
@@ -305,6 +312,43 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
         tc_fence_after();
         tmem_dealloc(tmem_base, PF_TMEM_COLS);
     }
+}
+
+// V pre-pass: strided bf16 [B,Hkv,Skv,D] view -> contiguous f16 copy; raises *overflow when a value does not
+// fit f16 (|v| > 65504, inf or NaN).  Thread 0 also clears the flag slot a later call will use.
+struct CastVParams {
+    const __nv_bfloat16* src;
+    __half* dst;
+    long long s0, s1, s2;  // element strides of batch, head, row
+    int H, S, D;           // D is a multiple of 8
+    long long n_vec;       // B*H*S*D / 8
+    int* overflow;
+    int* clear_slot;
+};
+
+__global__ void cast_v_to_f16_kernel(const CastVParams P) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) *P.clear_slot = 0;
+    const int vec_per_row = P.D / 8;
+    bool bad = false;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < P.n_vec; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % vec_per_row);
+        const long long row = i / vec_per_row;
+        const int s = (int)(row % P.S);
+        const int h = (int)((row / P.S) % P.H);
+        const long long b = row / ((long long)P.S * P.H);
+        const uint4 in = *reinterpret_cast<const uint4*>(P.src + b * P.s0 + h * P.s1 + s * P.s2 + c * 8);
+        const __nv_bfloat162* iv = reinterpret_cast<const __nv_bfloat162*>(&in);
+        uint4 out;
+        __half2* ov = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(iv[e]);
+            bad |= !(fabsf(f.x) <= 65504.0f) || !(fabsf(f.y) <= 65504.0f);
+            ov[e] = __floats2half2_rn(f.x, f.y);
+        }
+        *reinterpret_cast<uint4*>(P.dst + i * 8) = out;
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(P.overflow, 1);
 }
 
 }  // namespace fusor

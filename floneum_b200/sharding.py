@@ -1,0 +1,69 @@
+"""Multi-GPU partitioning of the attention path: one process per GPU.
+
+Two partitions, both defined by the benchmark configurations (the reference has no multi-GPU code):
+  * KV heads (prefill and batched decode): rank r owns kv heads [r*Hkv/N, (r+1)*Hkv/N) and the query
+    heads that read them.  Inputs arrive sharded, outputs stay sharded: no collective.
+  * KV-sequence chunks (long-context decode): rank r owns keys [r*Skv/N, (r+1)*Skv/N); each rank emits
+    a partial {m, l, O} per query head, the partials are all-gathered (NCCL over NVLink on GPUs, gloo in
+    the CPU tests) and merged by log-sum-exp on every rank.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+
+def kv_head_range(num_kv_heads: int, rank: int, world: int) -> Tuple[int, int]:
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world {world}")
+    if num_kv_heads % world != 0:
+        raise ValueError(f"{num_kv_heads} kv heads do not split evenly over {world} ranks")
+    per = num_kv_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def q_head_range(num_q_heads: int, num_kv_heads: int, rank: int, world: int) -> Tuple[int, int]:
+    """Query heads that read the kv heads of `rank` (query head h reads kv head h // (Hq/Hkv))."""
+    if num_q_heads % num_kv_heads != 0:
+        raise ValueError(f"Number of Q heads ({num_q_heads}) must be divisible by number of K/V heads ({num_kv_heads})")
+    g = num_q_heads // num_kv_heads
+    lo, hi = kv_head_range(num_kv_heads, rank, world)
+    return lo * g, hi * g
+
+
+def kv_chunk_range(kv_len: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous key range of `rank`; ranges tile [0, kv_len) and differ in size by at most one."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world {world}")
+    return rank * kv_len // world, (rank + 1) * kv_len // world
+
+
+def all_gather_partials(partial, group=None):
+    """partial: torch tensor [rows..., D+2] on this rank -> [world, rows..., D+2] on every rank."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    out = torch.empty((world,) + tuple(partial.shape), dtype=partial.dtype, device=partial.device)
+    if partial.is_cuda:
+        dist.all_gather_into_tensor(out, partial.contiguous(), group=group)
+    else:
+        chunks = list(out.unbind(0))
+        dist.all_gather(chunks, partial.contiguous(), group=group)
+    return out
+
+
+def decode_kv_chunks(device, cache, q, scale: float, group=None):
+    """Long-context decode over KV chunks: local split-KV partial -> all-gather -> log-sum-exp merge.
+
+    `cache` holds this rank's chunk of the keys, `q` [B,Hq,1,D] is replicated.  Returns a torch tensor
+    [B,Hq,D] f32 on this rank's GPU (every rank gets the full result).  The collective runs on torch's current
+    stream, which must be the stream the Device was created on."""
+    import torch
+    from .cache import lse_combine
+    from .tensor import F32, Tensor
+    B, Hq, _, D = q.shape()
+    partial = torch.empty((B, Hq, D + 2), dtype=torch.float32, device=f"cuda:{device.ordinal}")
+    cache.decode_partial(q, scale, Tensor.from_torch(device, partial))
+    gathered = all_gather_partials(partial, group)
+    out = torch.empty((B, Hq, D), dtype=torch.float32, device=partial.device)
+    lse_combine(device, Tensor.from_torch(device, gathered), Tensor.from_torch(device, out))
+    return out

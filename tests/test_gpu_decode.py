@@ -118,12 +118,13 @@ def test_kv_cache_append_reset_like_the_reference(device):
     fb = _fb()
     D = 128
     cache = fb.KvCache.new(2, 64)
+    # values exactly representable in bf16: the cache stores bf16
     k1 = np.arange(D, dtype=np.float32).reshape(1, 1, 1, D)
-    v1 = k1 + 300
+    v1 = k1 * np.float32(0.5)
     k, v = cache.append(device, fb.Tensor.from_slice(device, k1.shape, k1), fb.Tensor.from_slice(device, v1.shape, v1))
     assert k.shape() == (1, 1, 1, D) and v.shape() == (1, 1, 1, D)
     assert np.array_equal(k.as_slice(), k1) and np.array_equal(v.as_slice(), v1)
-    k2, v2 = k1 + 1000, v1 + 1000
+    k2, v2 = k1 + 128, v1 + 64
     k, v = cache.append(device, fb.Tensor.from_slice(device, k2.shape, k2), fb.Tensor.from_slice(device, v2.shape, v2))
     assert k.shape() == (1, 1, 2, D) and cache.current_seq_len() == 2
     assert np.array_equal(k.as_slice(), np.concatenate([k1, k2], 2)) and np.array_equal(v.as_slice(), np.concatenate([v1, v2], 2))
