@@ -1042,3 +1042,115 @@ extern "C" int32_t fusor_cuda_flash_attention_decode_host(fusor_cuda_ctx* ctx, f
     CUDA_TRY(ctx, cudaMemcpyAsync(out->data, dout.data, ob, cudaMemcpyDeviceToHost, ctx->stream));
     return check_device_error(ctx);
 }
+
+// =============================================================================== attention without allocation
+// Scratch for fusor_cuda_flash_attention_noalloc: a 256-byte header (word 0 = device error word, word 1 = the
+// "V does not fit f16" flag) followed by the f16 copy of V.  Every device that loads the library holds these
+// 8 MiB + 256 B until the process exits.
+static constexpr size_t kNoallocMaxVElems = 4u * 1024u * 1024u;  // B * Hkv * Skv * 128 <= 4 Mi elements
+static constexpr size_t kNoallocHeaderBytes = 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoallocHeaderBytes + kNoallocMaxVElems * 2];
+
+struct NoallocDevice {
+    bool ready = false;
+    unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+    PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+};
+static NoallocDevice g_noalloc[64];
+static std::mutex g_noalloc_mutex;
+
+extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                                      const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
+                                                      const fusor_cuda_tensor4* out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return fail(nullptr, FUSOR_CUDA_NO_DEVICE, "no current CUDA device");
+    }
+    // A throw-away context object on the stack carries the stream and the encoder into the shared helpers;
+    // nothing in it is allocated and it owns nothing.
+    fusor_cuda_ctx local;
+    local.device = dev;
+    local.stream = static_cast<cudaStream_t>(stream);
+    AttnShape S;
+    TRY(validate_attention(&local, q, k, v, nullptr, mask_kind, 0, out, &S));
+    if (!prefill_eligible(S, q, k, v, scale, mask_kind, out))
+        return fail(nullptr, FUSOR_CUDA_UNSUPPORTED,
+                    "the allocation-free entry point takes bf16 q/k/v with head_dim 128, 16-byte aligned rows, "
+                    "mask NONE or CAUSAL and a positive scale");
+    const size_t v_elems = (size_t)S.B * S.Hkv * S.Skv * S.D;
+    if (v_elems > kNoallocMaxVElems)
+        return fail(nullptr, FUSOR_CUDA_UNSUPPORTED,
+                    "V has %zu elements; the static scratch of the allocation-free entry point holds at most %zu "
+                    "(B * Hkv * Skv * 128 <= 4194304)", v_elems, kNoallocMaxVElems);
+    const long long grid = (long long)((S.Sq + PF_BM - 1) / PF_BM) * S.Hq * S.B;
+    if (grid > 0x7fffffffLL) return fail(nullptr, FUSOR_CUDA_UNSUPPORTED, "grid too large");
+
+    NoallocDevice& nd = g_noalloc[dev];
+    {
+        // One-time set-up per device, with that device current: resolve the DEVICE address of the static array
+        // (its name is only a host-side handle here), the tensor-map encoder, and the kernel's shared-memory opt-in.
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!nd.ready) {
+            cudaDeviceProp prop;
+            CUDA_TRY(nullptr, cudaGetDeviceProperties(&prop, dev));
+            if (prop.major != 10)
+                return fail(nullptr, FUSOR_CUDA_NO_DEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only", dev,
+                            prop.major, prop.minor);
+            void* p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || !p)
+                return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
+                return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cuTensorMapEncodeTiled is not available in this driver");
+            CUDA_TRY(nullptr, cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES));
+            nd.scratch = static_cast<unsigned char*>(p);
+            nd.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+            nd.ready = true;
+        }
+    }
+    local.encode = nd.encode;
+    int* d_err = reinterpret_cast<int*>(nd.scratch);
+    int* d_overflow = d_err + 1;
+    __half* v16 = reinterpret_cast<__half*>(nd.scratch + kNoallocHeaderBytes);
+    // The array keeps the previous call's contents: the two status words must start at zero.
+    CUDA_TRY(nullptr, cudaMemsetAsync(nd.scratch, 0, kNoallocHeaderBytes, local.stream));
+
+    CastVParams C;
+    C.src = (const __nv_bfloat16*)v->data; C.dst = v16;
+    C.s0 = v->stride[0]; C.s1 = v->stride[1]; C.s2 = v->stride[2];
+    C.H = S.Hkv; C.S = S.Skv; C.D = S.D; C.n_vec = (long long)(v_elems / 8);
+    C.overflow = d_overflow; C.clear_slot = d_err + 2;  // an unused header word
+    const int blocks = (int)std::min<long long>((C.n_vec + 255) / 256, 148LL * 8);
+    cast_v_to_f16_kernel<<<blocks, 256, 0, local.stream>>>(C);
+    TRY(launch_check(&local, "cast_v_to_f16_kernel"));
+
+    CUtensorMap tmQ, tmK, tmV, tmV16;
+    TRY(make_tmap_bhsd(&local, &tmQ, q, PF_BM));
+    TRY(make_tmap_bhsd(&local, &tmK, k, PF_BN));
+    TRY(make_tmap_bhsd(&local, &tmV, v, PF_BN));
+    fusor_cuda_tensor4 v16t = *v;
+    v16t.data = v16;
+    set_contiguous(&v16t);
+    TRY(make_tmap_bhsd(&local, &tmV16, &v16t, PF_BN, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
+    PrefillParams P;
+    P.out = out->data; P.out_dtype = out->dtype;
+    for (int i = 0; i < 3; ++i) P.os[i] = out->stride[i];
+    P.B = S.B; P.Hq = S.Hq; P.Hkv = S.Hkv; P.Sq = S.Sq; P.Skv = S.Skv;
+    P.causal = mask_kind == FUSOR_CUDA_MASK_CAUSAL;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
+    P.err = d_err;
+    P.debug = nullptr;
+    P.v_f16_overflow = d_overflow;
+    prefill_sm100_kernel<<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, local.stream>>>(tmQ, tmK, tmV, tmV16, P);
+    TRY(launch_check(&local, "prefill_sm100_kernel"));
+    // Synchronous: wait for the result and report a device-side timeout of this call.
+    int h_err = 0;
+    CUDA_TRY(nullptr, cudaMemcpyAsync(&h_err, d_err, sizeof(int), cudaMemcpyDeviceToHost, local.stream));
+    CUDA_TRY(nullptr, cudaStreamSynchronize(local.stream));
+    if (h_err != 0) return fail(nullptr, FUSOR_CUDA_TIMEOUT, "a bounded device-side wait ran out (kernel unwound, result invalid)");
+    return FUSOR_CUDA_OK;
+}

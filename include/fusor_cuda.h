@@ -122,6 +122,30 @@ int32_t fusor_cuda_flash_attention_general(fusor_cuda_ctx* ctx, const fusor_cuda
                                            const fusor_cuda_tensor2* mask, int32_t mask_kind, int32_t window,
                                            const fusor_cuda_tensor4* out);
 
+/* Causal / full prefill attention that allocates nothing (no counterpart in the reference).
+ * Meant for callers that cannot let a library allocate device memory: a serving process that has handed the
+ * whole GPU to its own memory pool at start-up, where a cudaMalloc from inside this library would fail, or a
+ * latency-critical loop that cannot afford the device-wide synchronisation cudaMalloc and cudaFree imply.
+ * fusor_cuda_flash_attention grows a context-owned f16 copy of V with cudaMalloc when a larger V arrives; this
+ * variant runs the same two kernels (V pre-pass + tensor-core prefill) with that copy in a fixed array inside
+ * the library image (8 MiB + 256 bytes per GPU, held by every GPU that loads the library until the process exits).
+ *   - Needs no context: it runs on the CURRENT device, on `stream` (NULL = the default stream).
+ *   - Accepts what the tensor-core kernel accepts: bf16 q, k, v with head_dim 128, rows 16-byte aligned,
+ *     mask_kind NONE or CAUSAL, scale > 0, out f32 or bf16; anything else returns FUSOR_CUDA_UNSUPPORTED.
+ *   - Limit: B * Hkv * Skv * 128 <= 4 194 304 elements of V (for example 8 kv heads x 4096 keys); larger inputs
+ *     return FUSOR_CUDA_UNSUPPORTED with a message naming the limit.
+ *   - Calls no cudaMalloc / cudaFree / allocating library routine.  The first call on each device resolves the
+ *     array's device address and opts the kernel in to large shared memory; make that first call before any
+ *     stream capture begins.
+ *   - Synchronous: it returns after the result is complete, and reports FUSOR_CUDA_TIMEOUT if a bounded
+ *     device-side wait ran out.  Errors are read with fusor_cuda_last_error(NULL).
+ *   - All calls on a device share the one array (it keeps the previous call's contents; the status words are
+ *     cleared at the start of each call).  Two calls that overlap on the same GPU, from different streams,
+ *     threads or processes sharing the context, race on it: serialise them. */
+int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
+                                           const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
+                                           const fusor_cuda_tensor4* out);
+
 /* Diagnostic (no reference counterpart): runs the tensor-core prefill kernel with the softmax weights kept as f16 against an
  * f16 copy of V (p_format 0, the production setting) or as bf16 against the bf16 V (p_format 1) and copies out of the first CTA, into debug_device f32 [128][258], the raw scores of its
  * first key tile [0,128), its un-normalised O [128,256), the running max in log2 units [256] and the row sum [257].
