@@ -184,6 +184,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--no-extras", action="store_true", help="skip the decode line and the CPU baseline")
+    ap.add_argument("--quick", action="store_true", help="for profiler captures: no clock-settling loop, no e2e, no extras")
+    ap.add_argument("--small", action="store_true", help="for profiler captures: a scaled-down case of the workload "
+                    "(prefill B1 Hq8 Hkv2 S4096; decode B16)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -259,7 +262,7 @@ def main():
             torch.cuda.synchronize()
             # keep the GPU busy with untimed steps until the clocks have been under load for 0.5 s
             i = args.warmup
-            while time.time() - t_busy0 < 0.5:
+            while not args.quick and time.time() - t_busy0 < 0.5:
                 for _ in range(20):
                     step(i)
                     i += 1
@@ -293,9 +296,9 @@ def main():
         def e2e_step():
             _lib.check(L.fusor_cuda_flash_attention_host(dev.handle, ctypes.byref(eq), ctypes.byref(ek), ctypes.byref(evv),
                                                          ctypes.c_float(w.scale), None, _lib.MASK_CAUSAL, 0, ctypes.byref(eo)), dev.handle)
-        e2e_steps = max(3, min(args.steps, 10))
+        e2e_steps = 1 if args.quick else max(3, min(args.steps, 10))
         with torch.cuda.stream(stream):
-            for _ in range(2):
+            for _ in range(0 if args.quick else 2):
                 e2e_step()
             barrier()
             t0 = time.perf_counter()
@@ -382,8 +385,11 @@ def main():
     from oracle import oracle as O  # checker + CPU baseline only
     extras = {}
     if args.workload in ("cfg2", "cfg5"):
-        w = W.cfg2() if args.workload == "cfg2" else W.cfg5()
-        r = run_prefill(w, args.workload)
+        if args.small:
+            w = W.cfg2(B=1, Hq=8, Hkv=2) if args.workload == "cfg2" else W.cfg5(S=8192, Hq=8, Hkv=2)
+        else:
+            w = W.cfg2() if args.workload == "cfg2" else W.cfg5()
+        r = run_prefill(w, args.workload + (" (scaled down)" if args.small else ""))
         q, k, v = r.pop("_slice")
         got = r.pop("_got")
         rows = np.unique(np.random.default_rng(0).integers(0, q.shape[0] * q.shape[1] * q.shape[2], 400))
@@ -392,7 +398,7 @@ def main():
         r["parity"] = {"max_abs": float(err.max()), "mean_abs": float(err.mean()), "rows_checked": int(rows.size),
                        "tolerance": "max 2e-3, mean 2e-4"}
         dtype = "bf16"
-        if rank == 0 and world == 1 and not args.no_extras:
+        if rank == 0 and world == 1 and not args.no_extras and not args.quick:
             fn, flops, desc = cpu_prefill_sample(w)
             sec = time_cpu(fn, 3, 1)
             r["cpu_baseline"] = {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
@@ -407,8 +413,8 @@ def main():
                 extras["decode"] = d
     else:
         if args.workload == "cfg3":
-            w = W.cfg3()
-            r = run_decode(w, "cfg3")
+            w = W.cfg3(B=16) if args.small else W.cfg3()
+            r = run_decode(w, "cfg3" + (" (scaled down)" if args.small else ""))
         else:
             w = W.cfg4(rank=rank, world=world)
             r = run_decode(w, "cfg4", shard_heads=False, chunked=True)

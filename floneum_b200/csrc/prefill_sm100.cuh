@@ -1,17 +1,17 @@
 // Causal / full flash-attention prefill on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
-// One CTA owns a 128-row query tile of one (batch, query head) and walks the 128-key tiles
-// it can see (causal tile skip).  Roles, by warp:
-//   warp 0      TMA producer: Q once, then K and V tiles into two 3-slot shared-memory rings
-//               (128-byte swizzle; no multicast).
+// One CTA owns a 128-row query tile of one (batch, query head) and walks the 128-key tiles it can see
+// (causal tile skip).  Two CTAs are resident per SM (256 TMEM columns and ~98 KB of shared memory each), so
+// the softmax of one overlaps the tensor work, prologue and epilogue of the other.  Roles, by warp:
+//   warp 0      TMA producer: Q once, then one K tile and one V tile at a time (128-byte swizzle, no multicast).
 //   warp 1      allocates TMEM and issues every tcgen05.mma from one thread:
 //               S_j = Q K_j^T   (SS: both operands in shared memory, K-major),
-//               O  += P_j V_j   (TS: P read from TMEM, V from shared memory, MN-major).
-//               S is double-buffered in TMEM so S_{j+1} is computed while the softmax of tile j runs.
-//   warps 4-7   softmax: one thread per query row reads its S row from TMEM, keeps the running
-//               max / sum, writes P (16-bit) back over S, rescales O in TMEM only when the row
-//               max has grown by more than 2^8 (lazy rescale), and finally writes O / l.
-// TMEM columns: [0,128) S0/P0, [128,256) S1/P1, [256,384) O.
+//               O  += P_j V_j   (TS: P read from TMEM, V from shared memory, MN-major),
+//               and S_{j+1} straight after O += P_j V_j, so the tensor pipe runs them back to back.
+//   warps 2-5   softmax: one thread per query row reads its S row from TMEM, keeps the running max / sum,
+//               writes P (16-bit) back over S, rescales O in TMEM only when the row max has grown by more
+//               than 2^8 (lazy rescale), and finally writes O / l.
+// TMEM columns: [0,128) S / P, [128,256) O.
 // All waits are bounded (ptx_sm100.cuh); on a timeout the CTA unwinds and frees its TMEM.
 //
 // Replaces the reference's fused kernel for Sq > 1
@@ -25,12 +25,12 @@
 namespace fusor {
 
 constexpr int PF_BM = 128, PF_BN = 128, PF_D = 128;
-constexpr int PF_STAGES = 3;
-constexpr int PF_THREADS = 256;
+constexpr int PF_THREADS = 192;
+constexpr int PF_SOFTMAX_WARP0 = 2;           // warps 2..5: warp % 4 covers the four TMEM lane quadrants
 constexpr int PF_TILE_BYTES = 128 * 128 * 2;  // one 128x128 16-bit tile = two [128][64] halves
 constexpr int PF_HALF_BYTES = PF_TILE_BYTES / 2;
-constexpr uint32_t PF_TMEM_COLS = 512;
-constexpr uint32_t PF_COL_S0 = 0, PF_COL_S1 = 128, PF_COL_O = 256;
+constexpr uint32_t PF_TMEM_COLS = 256;
+constexpr uint32_t PF_COL_S = 0, PF_COL_O = 128;
 constexpr float PF_RESCALE_THRESHOLD = 8.0f;  // in log2 units
 
 struct PrefillParams {
@@ -46,14 +46,14 @@ struct PrefillParams {
     const int* v_f16_overflow; // written by the V pre-pass: non-zero when some |v| does not fit f16; null = no f16 copy
 };
 
-constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_TILE_BYTES * (1 + 2 * PF_STAGES) + 256;
+constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_TILE_BYTES * 3 + 256;
 
 // P (the softmax weights handed to the second MMA) and V must have the same 16-bit type: kind::f16 rejects a
 // mixed f16 / bf16 operand pair.  bf16 weights (8 significant bits) put rows with few keys above the 2e-3
 // tolerance, so the host converts V to f16 once per call (cast_v_to_f16_kernel) and the kernel keeps P in f16
 // (11 bits).  When some |v| exceeds the f16 range the pre-pass raises a flag and every CTA falls back to bf16
 // P with the original bf16 V: the choice is a uniform runtime branch (descriptor bits and the tensor map).
-__global__ void __launch_bounds__(PF_THREADS, 1)
+__global__ void __launch_bounds__(PF_THREADS, 2)
     prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmV16,
                          const PrefillParams P) {
@@ -61,17 +61,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_sm = base;
     uint8_t* k_sm = q_sm + PF_TILE_BYTES;
-    uint8_t* v_sm = k_sm + PF_STAGES * PF_TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + PF_STAGES * PF_TILE_BYTES);
-    uint64_t* q_full = bars;                    // 1
-    uint64_t* k_full = bars + 1;                // STAGES
-    uint64_t* k_empty = k_full + PF_STAGES;     // STAGES
-    uint64_t* v_full = k_empty + PF_STAGES;     // STAGES
-    uint64_t* v_empty = v_full + PF_STAGES;     // STAGES
-    uint64_t* s_full = v_empty + PF_STAGES;     // 2
-    uint64_t* p_full = s_full + 2;              // 2
-    uint64_t* pv_done = p_full + 2;             // 1
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    uint8_t* v_sm = k_sm + PF_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + PF_TILE_BYTES);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = bars + 2;
+    uint64_t* v_full = bars + 3;
+    uint64_t* v_empty = bars + 4;
+    uint64_t* s_full = bars + 5;
+    uint64_t* p_full = bars + 6;
+    uint64_t* pv_done = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -90,16 +90,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
 
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int i = 0; i < PF_STAGES; ++i) {
-            mbar_init(k_full + i, 1);
-            mbar_init(k_empty + i, 1);
-            mbar_init(v_full + i, 1);
-            mbar_init(v_empty + i, 1);
-        }
-        mbar_init(s_full + 0, 1);
-        mbar_init(s_full + 1, 1);
-        mbar_init(p_full + 0, 128);
-        mbar_init(p_full + 1, 128);
+        mbar_init(k_full, 1);
+        mbar_init(k_empty, 1);
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 128);
         mbar_init(pv_done, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -119,20 +115,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            const CUtensorMap* tv = use_f16 ? &tmV16 : &tmV;
             mbar_arrive_expect_tx(q_full, PF_TILE_BYTES);
             tma_load_4d(q_sm, &tmQ, q_full, 0, q0, h, b);
             tma_load_4d(q_sm + PF_HALF_BYTES, &tmQ, q_full, 64, q0, h, b);
             for (int j = 0; j < n_kv; ++j) {
-                const int s = j % PF_STAGES, use = j / PF_STAGES;
-                if (use > 0 && !mbar_wait(k_empty + s, (use - 1) & 1, abort_flag, P.err)) break;
-                mbar_arrive_expect_tx(k_full + s, PF_TILE_BYTES);
-                tma_load_4d(k_sm + s * PF_TILE_BYTES, &tmK, k_full + s, 0, j * PF_BN, hk, b);
-                tma_load_4d(k_sm + s * PF_TILE_BYTES + PF_HALF_BYTES, &tmK, k_full + s, 64, j * PF_BN, hk, b);
-                if (use > 0 && !mbar_wait(v_empty + s, (use - 1) & 1, abort_flag, P.err)) break;
-                mbar_arrive_expect_tx(v_full + s, PF_TILE_BYTES);
-                const CUtensorMap* tv = use_f16 ? &tmV16 : &tmV;
-                tma_load_4d(v_sm + s * PF_TILE_BYTES, tv, v_full + s, 0, j * PF_BN, hk, b);
-                tma_load_4d(v_sm + s * PF_TILE_BYTES + PF_HALF_BYTES, tv, v_full + s, 64, j * PF_BN, hk, b);
+                if (j > 0 && !mbar_wait(k_empty, (j - 1) & 1, abort_flag, P.err)) break;
+                mbar_arrive_expect_tx(k_full, PF_TILE_BYTES);
+                tma_load_4d(k_sm, &tmK, k_full, 0, j * PF_BN, hk, b);
+                tma_load_4d(k_sm + PF_HALF_BYTES, &tmK, k_full, 64, j * PF_BN, hk, b);
+                if (j > 0 && !mbar_wait(v_empty, (j - 1) & 1, abort_flag, P.err)) break;
+                mbar_arrive_expect_tx(v_full, PF_TILE_BYTES);
+                tma_load_4d(v_sm, tv, v_full, 0, j * PF_BN, hk, b);
+                tma_load_4d(v_sm + PF_HALF_BYTES, tv, v_full, 64, j * PF_BN, hk, b);
             }
         }
     } else if (warp == 1) {
@@ -140,107 +135,112 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
         if (lane == 0) {
             // S = Q K^T : A, B bf16, both K-major, M = N = 128
             constexpr uint32_t idesc_qk = make_idesc_f16(1, 1, 0, 0, PF_BM, PF_BN);
-            // O += P V  : A = P (TMEM, K-major), B = V bf16 MN-major, M = 128, N = D
+            // O += P V  : A = P (TMEM, K-major), B = V MN-major, M = 128, N = D; both f16 or both bf16
             const uint32_t idesc_pv = use_f16 ? make_idesc_f16(0, 0, 0, 1, PF_BM, PF_D) : make_idesc_f16(1, 1, 0, 1, PF_BM, PF_D);
-            const uint32_t q_addr = smem_u32(q_sm);
-            auto issue_qk = [&](int j) {
-                const uint32_t k_addr = smem_u32(k_sm + (j % PF_STAGES) * PF_TILE_BYTES);
-                const uint32_t d_tmem = tmem_base + ((j & 1) ? PF_COL_S1 : PF_COL_S0);
+            const uint32_t q_addr = smem_u32(q_sm), k_addr = smem_u32(k_sm), v_addr = smem_u32(v_sm);
+            auto issue_qk = [&]() {
 #pragma unroll
                 for (int kk = 0; kk < PF_D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * PF_HALF_BYTES + (kk & 3) * 32;
-                    tc_mma_ss(d_tmem, make_smem_desc_sw128(q_addr + off, 16, 1024),
+                    tc_mma_ss(tmem_base + PF_COL_S, make_smem_desc_sw128(q_addr + off, 16, 1024),
                               make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0);
                 }
-                tc_commit(s_full + (j & 1));
-                tc_commit(k_empty + (j % PF_STAGES));
+                tc_commit(s_full);
+                tc_commit(k_empty);
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag, P.err);
-            ok = ok && mbar_wait(k_full + 0, 0, abort_flag, P.err);
+            bool ok = mbar_wait(q_full, 0, abort_flag, P.err) && mbar_wait(k_full, 0, abort_flag, P.err);
             if (ok) {
                 tc_fence_after();
-                issue_qk(0);
+                issue_qk();
             }
             for (int j = 0; j < n_kv && ok; ++j) {
-                if (j + 1 < n_kv) {
-                    ok = mbar_wait(k_full + (j + 1) % PF_STAGES, ((j + 1) / PF_STAGES) & 1, abort_flag, P.err);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_qk(j + 1);
-                }
-                ok = mbar_wait(p_full + (j & 1), (j >> 1) & 1, abort_flag, P.err) &&
-                     mbar_wait(v_full + j % PF_STAGES, (j / PF_STAGES) & 1, abort_flag, P.err);
+                ok = mbar_wait(p_full, j & 1, abort_flag, P.err) && mbar_wait(v_full, j & 1, abort_flag, P.err);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(v_sm + (j % PF_STAGES) * PF_TILE_BYTES);
-                const uint32_t p_tmem = tmem_base + ((j & 1) ? PF_COL_S1 : PF_COL_S0);
 #pragma unroll
                 for (int kk = 0; kk < PF_BN / 16; ++kk) {
                     // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2 KB) of the V tile
-                    tc_mma_ts(tmem_base + PF_COL_O, p_tmem + kk * 8,
+                    tc_mma_ts(tmem_base + PF_COL_O, tmem_base + PF_COL_S + kk * 8,
                               make_smem_desc_sw128(v_addr + kk * 2048, PF_HALF_BYTES, 1024), idesc_pv,
                               (j > 0 || kk > 0));
                 }
-                tc_commit(v_empty + (j % PF_STAGES));
+                tc_commit(v_empty);
                 tc_commit(pv_done);
+                if (j + 1 < n_kv) {
+                    // S_{j+1} overwrites the columns P_j is being read from: the tensor pipe executes in issue order
+                    ok = mbar_wait(k_full, (j + 1) & 1, abort_flag, P.err);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk();
+                }
             }
         }
-    } else if (warp >= 4) {
+    } else {
         // ------------------------------------------------------------------ softmax / correction / epilogue
-        const int row = tid - 128;                                   // 0..127 = TMEM lane
+        const int row = (warp & 3) * 32 + lane;                        // 0..127 = TMEM lane = query row of the tile
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lane quadrant
         const int qi = q0 + row;
         const int k_limit = P.causal ? min(P.Skv - 1, qi + offset) : P.Skv - 1;  // last key this row may see
+        const float c = P.scale_log2;
+        const uint32_t s_tmem = tmem_base + lane_base + PF_COL_S;
+        const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
-            ok = mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag, P.err);
+            ok = mbar_wait(s_full, j & 1, abort_flag, P.err);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t s_tmem = tmem_base + lane_base + ((j & 1) ? PF_COL_S1 : PF_COL_S0);
-            uint32_t sr[4][32];
+            float s[128];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, sr[c]);
+            for (int cc = 0; cc < 4; ++cc) tmem_ld32(s_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
             tc_wait_ld();
             if (P.debug && blockIdx.x == 0 && j == 0) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) P.debug[row * 258 + c * 32 + i] = __uint_as_float(sr[c][i]);
+                for (int i = 0; i < 128; ++i) P.debug[row * 258 + i] = s[i];
             }
             const int k0 = j * PF_BN;
-            const bool need_mask = k0 + PF_BN - 1 > k_limit;
-            float tmax = -INFINITY;
+            if (k0 + PF_BN - 1 > k_limit) {  // diagonal or ragged tile: mask in the raw domain
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+                for (int i = 0; i < 128; ++i)
+                    if (k0 + i > k_limit) s[i] = -INFINITY;
+            }
+            float mx0 = fmax3(s[0], s[1], s[2]), mx1 = fmax3(s[3], s[4], s[5]);
+            float mx2 = fmax3(s[6], s[7], s[8]), mx3 = fmax3(s[9], s[10], s[11]);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float t = __uint_as_float(sr[c][i]) * P.scale_log2;
-                    if (need_mask && k0 + c * 32 + i > k_limit) t = -INFINITY;
-                    sr[c][i] = __float_as_uint(t);
-                    tmax = fmaxf(tmax, t);
-                }
+            for (int i = 12; i < 124; i += 8) {
+                mx0 = fmax3(mx0, s[i], s[i + 1]);
+                mx1 = fmax3(mx1, s[i + 2], s[i + 3]);
+                mx2 = fmax3(mx2, s[i + 4], s[i + 5]);
+                mx3 = fmax3(mx3, s[i + 6], s[i + 7]);
+            }
+            mx0 = fmax3(mx0, s[124], s[125]);
+            mx1 = fmax3(mx1, s[126], s[127]);
+            const float tmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // scale > 0
             // lazy rescale: keep the reference max until the true max has moved by more than the threshold
             float alpha = 1.0f;
             if (tmax > m_ref + PF_RESCALE_THRESHOLD) {  // also true on the first tile (m_ref = -inf)
                 alpha = fast_exp2(m_ref - tmax);        // 0 on the first tile
                 m_ref = tmax;
             }
-            float psum = 0.0f;
-            const uint32_t p_tmem = s_tmem;  // P overwrites the first 64 columns of this S buffer
+            const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_ref, -m_ref);
+            float2 ps0 = make_float2(0.0f, 0.0f), ps1 = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int cc = 0; cc < 4; ++cc) {
                 uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float p0 = fast_exp2(__uint_as_float(sr[c][2 * i]) - m_ref);
-                    const float p1 = fast_exp2(__uint_as_float(sr[c][2 * i + 1]) - m_ref);
-                    psum += p0 + p1;
-                    pk[i] = use_f16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
+                for (int i = 0; i < 16; i += 2) {
+                    const float2 t0 = ffma2(make_float2(s[cc * 32 + 2 * i], s[cc * 32 + 2 * i + 1]), c2, nm2);
+                    const float2 t1 = ffma2(make_float2(s[cc * 32 + 2 * i + 2], s[cc * 32 + 2 * i + 3]), c2, nm2);
+                    const float2 p0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
+                    const float2 p1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
+                    ps0 = fadd2(ps0, p0);
+                    ps1 = fadd2(ps1, p1);
+                    pk[i] = use_f16 ? pack_f16(p0.x, p0.y) : pack_bf16(p0.x, p0.y);
+                    pk[i + 1] = use_f16 ? pack_f16(p1.x, p1.y) : pack_bf16(p1.x, p1.y);
                 }
-                tmem_st16(p_tmem + c * 16, pk);
+                tmem_st16(s_tmem + cc * 16, pk);  // P overwrites the first 64 columns of S
             }
-            l = l * alpha + psum;
+            l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
             tc_wait_st();
             if (j > 0) {
                 // O must be complete up to tile j-1 before it is rescaled and before P_j is handed over
@@ -248,58 +248,59 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 if (!ok) break;
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-                    const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O;
+                    const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t orr[32];
-                        tmem_ld32(o_tmem + c * 32, orr);
+                    for (int cc = 0; cc < 4; ++cc) {
+                        float orr[32];
+                        tmem_ld32(o_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[0]));
                         tc_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-                        tmem_st32(o_tmem + c * 32, orr);
+                        for (int i = 0; i < 32; i += 2) {
+                            const float2 r = fmul2(make_float2(orr[i], orr[i + 1]), a2);
+                            orr[i] = r.x;
+                            orr[i + 1] = r.y;
+                        }
+                        tmem_st32(o_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[0]));
                     }
                     tc_wait_st();
                 }
             }
             tc_fence_before();
-            mbar_arrive(p_full + (j & 1));
+            mbar_arrive(p_full);
         }
         if (ok) ok = mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, P.err);
         if (ok) {
             tc_fence_after();
-            const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O;
             const float inv_l = 1.0f / l;
             const long long obase = (long long)b * P.os[0] + (long long)h * P.os[1] + (long long)qi * P.os[2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t orr[32];
-                tmem_ld32(o_tmem + c * 32, orr);
+            for (int cc = 0; cc < 4; ++cc) {
+                float orr[32];
+                tmem_ld32(o_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[0]));
                 tc_wait_ld();
                 if (P.debug && blockIdx.x == 0) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) P.debug[row * 258 + 128 + c * 32 + i] = __uint_as_float(orr[i]);
-                    if (c == 0) {
+                    for (int i = 0; i < 32; ++i) P.debug[row * 258 + 128 + cc * 32 + i] = orr[i];
+                    if (cc == 0) {
                         P.debug[row * 258 + 256] = m_ref;
                         P.debug[row * 258 + 257] = l;
                     }
                 }
                 if (qi < P.Sq) {
                     if (P.out_dtype == 0) {
-                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + obase + c * 32);
+                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + obase + cc * 32);
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
-                            dst[i] = make_float4(__uint_as_float(orr[4 * i]) * inv_l, __uint_as_float(orr[4 * i + 1]) * inv_l,
-                                                 __uint_as_float(orr[4 * i + 2]) * inv_l,
-                                                 __uint_as_float(orr[4 * i + 3]) * inv_l);
+                            dst[i] = make_float4(orr[4 * i] * inv_l, orr[4 * i + 1] * inv_l, orr[4 * i + 2] * inv_l,
+                                                 orr[4 * i + 3] * inv_l);
                     } else {
-                        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(P.out) + obase + c * 32);
+                        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(P.out) + obase + cc * 32);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
-                            dst[i] = make_uint4(
-                                pack_bf16(__uint_as_float(orr[8 * i]) * inv_l, __uint_as_float(orr[8 * i + 1]) * inv_l),
-                                pack_bf16(__uint_as_float(orr[8 * i + 2]) * inv_l, __uint_as_float(orr[8 * i + 3]) * inv_l),
-                                pack_bf16(__uint_as_float(orr[8 * i + 4]) * inv_l, __uint_as_float(orr[8 * i + 5]) * inv_l),
-                                pack_bf16(__uint_as_float(orr[8 * i + 6]) * inv_l, __uint_as_float(orr[8 * i + 7]) * inv_l));
+                            dst[i] = make_uint4(pack_bf16(orr[8 * i] * inv_l, orr[8 * i + 1] * inv_l),
+                                                pack_bf16(orr[8 * i + 2] * inv_l, orr[8 * i + 3] * inv_l),
+                                                pack_bf16(orr[8 * i + 4] * inv_l, orr[8 * i + 5] * inv_l),
+                                                pack_bf16(orr[8 * i + 6] * inv_l, orr[8 * i + 7] * inv_l));
                     }
                 }
             }
