@@ -186,7 +186,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the decode line and the CPU baseline")
     ap.add_argument("--quick", action="store_true", help="for profiler captures: no clock-settling loop, no e2e, no extras")
     ap.add_argument("--small", action="store_true", help="for profiler captures: a scaled-down case of the workload "
-                    "(prefill B1 Hq8 Hkv2 S4096; decode B16)")
+                    "(prefill B2 Hq16 Hkv4 S4096; decode B16)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -386,7 +386,7 @@ def main():
     extras = {}
     if args.workload in ("cfg2", "cfg5"):
         if args.small:
-            w = W.cfg2(B=1, Hq=8, Hkv=2) if args.workload == "cfg2" else W.cfg5(S=8192, Hq=8, Hkv=2)
+            w = W.cfg2(B=2, Hq=16, Hkv=4) if args.workload == "cfg2" else W.cfg5(S=8192, Hq=8, Hkv=2)
         else:
             w = W.cfg2() if args.workload == "cfg2" else W.cfg5()
         r = run_prefill(w, args.workload + (" (scaled down)" if args.small else ""))

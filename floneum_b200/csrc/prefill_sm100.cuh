@@ -1,17 +1,18 @@
 // Causal / full flash-attention prefill on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
-// One CTA owns a 128-row query tile of one (batch, query head) and walks the 128-key tiles it can see
-// (causal tile skip).  Two CTAs are resident per SM (256 TMEM columns and ~98 KB of shared memory each), so
+// One CTA owns a 128-row query tile of one (batch, query head) and walks the 64-key tiles it can see
+// (causal tile skip).  Two CTAs are resident per SM (256 TMEM columns and ~97 KB of shared memory each), so
 // the softmax of one overlaps the tensor work, prologue and epilogue of the other.  Roles, by warp:
-//   warp 0      TMA producer: Q once, then one K tile and one V tile at a time (128-byte swizzle, no multicast).
+//   warp 0      TMA producer: Q once, then K and V tiles into two 2-slot rings (128-byte swizzle, no multicast).
 //   warp 1      allocates TMEM and issues every tcgen05.mma from one thread:
-//               S_j = Q K_j^T   (SS: both operands in shared memory, K-major),
-//               O  += P_j V_j   (TS: P read from TMEM, V from shared memory, MN-major),
-//               and S_{j+1} straight after O += P_j V_j, so the tensor pipe runs them back to back.
+//               S_j = Q K_j^T   (SS: both operands in shared memory, K-major, N = 64),
+//               O  += P_j V_j   (TS: P read from TMEM, V from shared memory, MN-major, N = 128).
+//               S is double-buffered: S_{j+1} is ready before the softmax of tile j ends, and S_{j+2} is
+//               issued straight after O += P_j V_j into the buffer P_j is read from (the pipe runs in order).
 //   warps 2-5   softmax: one thread per query row reads its S row from TMEM, keeps the running max / sum,
 //               writes P (16-bit) back over S, rescales O in TMEM only when the row max has grown by more
 //               than 2^8 (lazy rescale), and finally writes O / l.
-// TMEM columns: [0,128) S / P, [128,256) O.
+// TMEM columns: [0,64) S0 / P0, [64,128) S1 / P1, [128,256) O.
 // All waits are bounded (ptx_sm100.cuh); on a timeout the CTA unwinds and frees its TMEM.
 //
 // Replaces the reference's fused kernel for Sq > 1
@@ -24,14 +25,16 @@
 
 namespace fusor {
 
-constexpr int PF_BM = 128, PF_BN = 128, PF_D = 128;
-constexpr int PF_THREADS = 192;
-constexpr int PF_SOFTMAX_WARP0 = 2;           // warps 2..5: warp % 4 covers the four TMEM lane quadrants
-constexpr int PF_TILE_BYTES = 128 * 128 * 2;  // one 128x128 16-bit tile = two [128][64] halves
-constexpr int PF_HALF_BYTES = PF_TILE_BYTES / 2;
+constexpr int PF_BM = 128, PF_BN = 64, PF_D = 128;
+constexpr int PF_THREADS = 192;               // warp 0 TMA, warp 1 MMA, warps 2..5 softmax (warp % 4 = TMEM lane quadrant)
+constexpr int PF_Q_BYTES = PF_BM * PF_D * 2;  // 32 KB = two [128][64] halves
+constexpr int PF_Q_HALF = PF_Q_BYTES / 2;
+constexpr int PF_KV_BYTES = PF_BN * PF_D * 2;  // 16 KB = two [64][64] halves
+constexpr int PF_KV_HALF = PF_KV_BYTES / 2;
 constexpr uint32_t PF_TMEM_COLS = 256;
-constexpr uint32_t PF_COL_S = 0, PF_COL_O = 128;
-constexpr float PF_RESCALE_THRESHOLD = 8.0f;  // in log2 units
+constexpr uint32_t PF_COL_S = 0, PF_COL_O = 128;  // S buffer b at PF_COL_S + 64 b
+constexpr float PF_RESCALE_THRESHOLD = 8.0f;      // in log2 units
+constexpr int PF_DEBUG_ROW = 258;                 // debug dump: per row 64 raw scores, pad, 128 O values at [128,256), m, l
 
 struct PrefillParams {
     void* out;
@@ -42,11 +45,11 @@ struct PrefillParams {
     float scale_log2;
     int n_q_tiles;
     int* err;
-    float* debug;              // optional [128][128 + 128 + 2] dump from CTA 0: raw S of tile 0, un-normalised O, m, l
+    float* debug;              // optional diagnostic dump from CTA 0 (see fusor_cuda_prefill_probe)
     const int* v_f16_overflow; // written by the V pre-pass: non-zero when some |v| does not fit f16; null = no f16 copy
 };
 
-constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_TILE_BYTES * 3 + 256;
+constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_Q_BYTES + 4 * (size_t)PF_KV_BYTES + 256;
 
 // P (the softmax weights handed to the second MMA) and V must have the same 16-bit type: kind::f16 rejects a
 // mixed f16 / bf16 operand pair.  bf16 weights (8 significant bits) put rows with few keys above the 2e-3
@@ -60,21 +63,27 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_sm = base;
-    uint8_t* k_sm = q_sm + PF_TILE_BYTES;
-    uint8_t* v_sm = k_sm + PF_TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + PF_TILE_BYTES);
+    uint8_t* k_sm = q_sm + PF_Q_BYTES;       // 2 slots
+    uint8_t* v_sm = k_sm + 2 * PF_KV_BYTES;  // 2 slots
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + 2 * PF_KV_BYTES);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;
-    uint64_t* k_empty = bars + 2;
-    uint64_t* v_full = bars + 3;
-    uint64_t* v_empty = bars + 4;
-    uint64_t* s_full = bars + 5;
-    uint64_t* p_full = bars + 6;
-    uint64_t* pv_done = bars + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* k_full = bars + 1;    // [2]
+    uint64_t* k_empty = bars + 3;   // [2]
+    uint64_t* v_full = bars + 5;    // [2]
+    uint64_t* v_empty = bars + 7;   // [2]
+    uint64_t* s_full = bars + 9;    // [2]
+    uint64_t* p_full = bars + 11;   // [2]
+    uint64_t* pv_done = bars + 13;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // diagnostic timeline (probe entry point only): cycle stamps of CTA 0 after the [128][258] value dump
+    const long long t_start = clock64();
+    const bool trace = P.debug != nullptr && blockIdx.x == 0;
+    auto stamp = [&](int slot) {
+        if (trace) P.debug[128 * PF_DEBUG_ROW + slot] = (float)(clock64() - t_start);
+    };
     const bool use_f16 = P.v_f16_overflow != nullptr && *P.v_f16_overflow == 0;
 
     // ---- which tile: heavy (late) query tiles first; consecutive CTAs share a kv head
@@ -90,12 +99,14 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
 
     if (tid == 0) {
         mbar_init(q_full, 1);
-        mbar_init(k_full, 1);
-        mbar_init(k_empty, 1);
-        mbar_init(v_full, 1);
-        mbar_init(v_empty, 1);
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 128);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + i, 1);
+            mbar_init(k_empty + i, 1);
+            mbar_init(v_full + i, 1);
+            mbar_init(v_empty + i, 1);
+            mbar_init(s_full + i, 1);
+            mbar_init(p_full + i, 128);
+        }
         mbar_init(pv_done, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -116,62 +127,76 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             const CUtensorMap* tv = use_f16 ? &tmV16 : &tmV;
-            mbar_arrive_expect_tx(q_full, PF_TILE_BYTES);
+            mbar_arrive_expect_tx(q_full, PF_Q_BYTES);
             tma_load_4d(q_sm, &tmQ, q_full, 0, q0, h, b);
-            tma_load_4d(q_sm + PF_HALF_BYTES, &tmQ, q_full, 64, q0, h, b);
+            tma_load_4d(q_sm + PF_Q_HALF, &tmQ, q_full, 64, q0, h, b);
             for (int j = 0; j < n_kv; ++j) {
-                if (j > 0 && !mbar_wait(k_empty, (j - 1) & 1, abort_flag, P.err)) break;
-                mbar_arrive_expect_tx(k_full, PF_TILE_BYTES);
-                tma_load_4d(k_sm, &tmK, k_full, 0, j * PF_BN, hk, b);
-                tma_load_4d(k_sm + PF_HALF_BYTES, &tmK, k_full, 64, j * PF_BN, hk, b);
-                if (j > 0 && !mbar_wait(v_empty, (j - 1) & 1, abort_flag, P.err)) break;
-                mbar_arrive_expect_tx(v_full, PF_TILE_BYTES);
-                tma_load_4d(v_sm, tv, v_full, 0, j * PF_BN, hk, b);
-                tma_load_4d(v_sm + PF_HALF_BYTES, tv, v_full, 64, j * PF_BN, hk, b);
+                const int st = j & 1, use = j >> 1;
+                if (use > 0 && !mbar_wait(k_empty + st, (use - 1) & 1, abort_flag, P.err)) break;
+                mbar_arrive_expect_tx(k_full + st, PF_KV_BYTES);
+                tma_load_4d(k_sm + st * PF_KV_BYTES, &tmK, k_full + st, 0, j * PF_BN, hk, b);
+                tma_load_4d(k_sm + st * PF_KV_BYTES + PF_KV_HALF, &tmK, k_full + st, 64, j * PF_BN, hk, b);
+                if (use > 0 && !mbar_wait(v_empty + st, (use - 1) & 1, abort_flag, P.err)) break;
+                mbar_arrive_expect_tx(v_full + st, PF_KV_BYTES);
+                tma_load_4d(v_sm + st * PF_KV_BYTES, tv, v_full + st, 0, j * PF_BN, hk, b);
+                tma_load_4d(v_sm + st * PF_KV_BYTES + PF_KV_HALF, tv, v_full + st, 64, j * PF_BN, hk, b);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            // S = Q K^T : A, B bf16, both K-major, M = N = 128
+            // S = Q K^T : A, B bf16, both K-major, M = 128, N = 64
             constexpr uint32_t idesc_qk = make_idesc_f16(1, 1, 0, 0, PF_BM, PF_BN);
             // O += P V  : A = P (TMEM, K-major), B = V MN-major, M = 128, N = D; both f16 or both bf16
             const uint32_t idesc_pv = use_f16 ? make_idesc_f16(0, 0, 0, 1, PF_BM, PF_D) : make_idesc_f16(1, 1, 0, 1, PF_BM, PF_D);
-            const uint32_t q_addr = smem_u32(q_sm), k_addr = smem_u32(k_sm), v_addr = smem_u32(v_sm);
-            auto issue_qk = [&]() {
+            const uint32_t q_addr = smem_u32(q_sm), k_addr0 = smem_u32(k_sm), v_addr0 = smem_u32(v_sm);
+            auto issue_qk = [&](int j) {  // K tile j (ring slot j & 1) -> S buffer j & 1
+                const uint32_t k_addr = k_addr0 + (j & 1) * PF_KV_BYTES;
+                const uint32_t d_tmem = tmem_base + PF_COL_S + (j & 1) * PF_BN;
 #pragma unroll
                 for (int kk = 0; kk < PF_D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * PF_HALF_BYTES + (kk & 3) * 32;
-                    tc_mma_ss(tmem_base + PF_COL_S, make_smem_desc_sw128(q_addr + off, 16, 1024),
-                              make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0);
+                    tc_mma_ss(d_tmem, make_smem_desc_sw128(q_addr + (kk >> 2) * PF_Q_HALF + (kk & 3) * 32, 16, 1024),
+                              make_smem_desc_sw128(k_addr + (kk >> 2) * PF_KV_HALF + (kk & 3) * 32, 16, 1024), idesc_qk, kk > 0);
                 }
-                tc_commit(s_full);
-                tc_commit(k_empty);
+                tc_commit(s_full + (j & 1));
+                tc_commit(k_empty + (j & 1));
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag, P.err) && mbar_wait(k_full, 0, abort_flag, P.err);
+            bool ok = mbar_wait(q_full, 0, abort_flag, P.err) && mbar_wait(k_full + 0, 0, abort_flag, P.err);
             if (ok) {
                 tc_fence_after();
-                issue_qk();
+                issue_qk(0);
+            }
+            if (ok && n_kv > 1) {
+                ok = mbar_wait(k_full + 1, 0, abort_flag, P.err);
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk(1);
+                }
             }
             for (int j = 0; j < n_kv && ok; ++j) {
-                ok = mbar_wait(p_full, j & 1, abort_flag, P.err) && mbar_wait(v_full, j & 1, abort_flag, P.err);
+                const int st = j & 1, ph = (j >> 1) & 1;
+                if (j < 32) stamp(256 + j * 4 + 0);
+                ok = mbar_wait(p_full + st, ph, abort_flag, P.err) && mbar_wait(v_full + st, ph, abort_flag, P.err);
                 if (!ok) break;
                 tc_fence_after();
+                if (j < 32) stamp(256 + j * 4 + 1);
+                const uint32_t v_addr = v_addr0 + st * PF_KV_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < PF_BN / 16; ++kk) {
                     // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2 KB) of the V tile
-                    tc_mma_ts(tmem_base + PF_COL_O, tmem_base + PF_COL_S + kk * 8,
-                              make_smem_desc_sw128(v_addr + kk * 2048, PF_HALF_BYTES, 1024), idesc_pv,
-                              (j > 0 || kk > 0));
+                    tc_mma_ts(tmem_base + PF_COL_O, tmem_base + PF_COL_S + st * PF_BN + kk * 8,
+                              make_smem_desc_sw128(v_addr + kk * 2048, PF_KV_HALF, 1024), idesc_pv, (j > 0 || kk > 0));
                 }
-                tc_commit(v_empty);
+                tc_commit(v_empty + st);
                 tc_commit(pv_done);
-                if (j + 1 < n_kv) {
-                    // S_{j+1} overwrites the columns P_j is being read from: the tensor pipe executes in issue order
-                    ok = mbar_wait(k_full, (j + 1) & 1, abort_flag, P.err);
+                if (j + 2 < n_kv) {
+                    // S_{j+2} overwrites the columns P_j is being read from: the tensor pipe executes in issue order
+                    ok = mbar_wait(k_full + st, ((j + 2) >> 1) & 1, abort_flag, P.err);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_qk();
+                    if (j < 32) stamp(256 + j * 4 + 2);
+                    issue_qk(j + 2);
+                    if (j < 32) stamp(256 + j * 4 + 3);
                 }
             }
         }
@@ -182,50 +207,54 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
         const int qi = q0 + row;
         const int k_limit = P.causal ? min(P.Skv - 1, qi + offset) : P.Skv - 1;  // last key this row may see
         const float c = P.scale_log2;
-        const uint32_t s_tmem = tmem_base + lane_base + PF_COL_S;
         const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
+        const bool tr = row == 0;
         for (int j = 0; j < n_kv && ok; ++j) {
-            ok = mbar_wait(s_full, j & 1, abort_flag, P.err);
+            const int st = j & 1;
+            const uint32_t s_tmem = tmem_base + lane_base + PF_COL_S + st * PF_BN;
+            if (tr && j < 32) stamp(j * 8 + 0);
+            ok = mbar_wait(s_full + st, (j >> 1) & 1, abort_flag, P.err);
             if (!ok) break;
             tc_fence_after();
-            float s[128];
-#pragma unroll
-            for (int cc = 0; cc < 4; ++cc) tmem_ld32(s_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
+            if (tr && j < 32) stamp(j * 8 + 1);
+            float s[PF_BN];
+            tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
             tc_wait_ld();
+            if (tr && j < 32) stamp(j * 8 + 2);
             if (P.debug && blockIdx.x == 0 && j == 0) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i) P.debug[row * 258 + i] = s[i];
+                for (int i = 0; i < PF_BN; ++i) P.debug[row * PF_DEBUG_ROW + i] = s[i];
             }
             const int k0 = j * PF_BN;
             if (k0 + PF_BN - 1 > k_limit) {  // diagonal or ragged tile: mask in the raw domain
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
+                for (int i = 0; i < PF_BN; ++i)
                     if (k0 + i > k_limit) s[i] = -INFINITY;
             }
-            float mx0 = fmax3(s[0], s[1], s[2]), mx1 = fmax3(s[3], s[4], s[5]);
-            float mx2 = fmax3(s[6], s[7], s[8]), mx3 = fmax3(s[9], s[10], s[11]);
+            float mx[8];
 #pragma unroll
-            for (int i = 12; i < 124; i += 8) {
-                mx0 = fmax3(mx0, s[i], s[i + 1]);
-                mx1 = fmax3(mx1, s[i + 2], s[i + 3]);
-                mx2 = fmax3(mx2, s[i + 4], s[i + 5]);
-                mx3 = fmax3(mx3, s[i + 6], s[i + 7]);
-            }
-            mx0 = fmax3(mx0, s[124], s[125]);
-            mx1 = fmax3(mx1, s[126], s[127]);
-            const float tmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // scale > 0
+            for (int a = 0; a < 8; ++a) mx[a] = fmax3(s[8 * a], s[8 * a + 1], s[8 * a + 2]);
+#pragma unroll
+            for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[8 * a + 3], s[8 * a + 4]);
+#pragma unroll
+            for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[8 * a + 5], s[8 * a + 6]);
+#pragma unroll
+            for (int a = 0; a < 8; a += 2) mx[a] = fmax3(mx[a], s[8 * a + 7], fmaxf(mx[a + 1], s[8 * a + 15]));
+            const float tmax = fmaxf(fmaxf(mx[0], mx[2]), fmaxf(mx[4], mx[6])) * c;  // scale > 0
             // lazy rescale: keep the reference max until the true max has moved by more than the threshold
             float alpha = 1.0f;
             if (tmax > m_ref + PF_RESCALE_THRESHOLD) {  // also true on the first tile (m_ref = -inf)
                 alpha = fast_exp2(m_ref - tmax);        // 0 on the first tile
                 m_ref = tmax;
             }
+            if (tr && j < 32) stamp(j * 8 + 3);
             const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_ref, -m_ref);
             float2 ps0 = make_float2(0.0f, 0.0f), ps1 = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = 0; cc < PF_BN / 32; ++cc) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
@@ -238,10 +267,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                     pk[i] = use_f16 ? pack_f16(p0.x, p0.y) : pack_bf16(p0.x, p0.y);
                     pk[i + 1] = use_f16 ? pack_f16(p1.x, p1.y) : pack_bf16(p1.x, p1.y);
                 }
-                tmem_st16(s_tmem + cc * 16, pk);  // P overwrites the first 64 columns of S
+                tmem_st16(s_tmem + cc * 16, pk);  // P overwrites the first 32 columns of this S buffer
             }
             l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
+            if (tr && j < 32) stamp(j * 8 + 4);
             tc_wait_st();
+            if (tr && j < 32) stamp(j * 8 + 5);
             if (j > 0) {
                 // O must be complete up to tile j-1 before it is rescaled and before P_j is handed over
                 ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, P.err);
@@ -266,7 +297,8 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 }
             }
             tc_fence_before();
-            mbar_arrive(p_full);
+            mbar_arrive(p_full + st);
+            if (tr && j < 32) stamp(j * 8 + 6);
         }
         if (ok) ok = mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, P.err);
         if (ok) {
@@ -280,10 +312,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 tc_wait_ld();
                 if (P.debug && blockIdx.x == 0) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) P.debug[row * 258 + 128 + cc * 32 + i] = orr[i];
+                    for (int i = 0; i < 32; ++i) P.debug[row * PF_DEBUG_ROW + 128 + cc * 32 + i] = orr[i];
                     if (cc == 0) {
-                        P.debug[row * 258 + 256] = m_ref;
-                        P.debug[row * 258 + 257] = l;
+                        P.debug[row * PF_DEBUG_ROW + 256] = m_ref;
+                        P.debug[row * PF_DEBUG_ROW + 257] = l;
                     }
                 }
                 if (qi < P.Sq) {
