@@ -86,8 +86,9 @@ def load(path: str | None = None):
     global _lib
     if _lib is not None:
         return _lib
-    path = path or _build.LIB_PATH
-    if _build.needs_build() and os.path.exists(os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")):
+    override = path or os.environ.get("FUSOR_CUDA_LIB")  # a differently tuned build of the same sources
+    path = override or _build.LIB_PATH
+    if not override and _build.needs_build() and os.path.exists(os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")):
         _build.build()
     if not os.path.exists(path):
         raise ImportError(

@@ -336,15 +336,16 @@ static int32_t launch_general(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     return launch_check(ctx, "general_attention_kernel");
 }
 
-// [B,H,S,D] view -> 4-D tensor map {D, S, H, B}, box {64, box_rows, 1, 1}, 128-byte swizzle, zero fill.
+// [B,H,S,D] view -> 4-D tensor map {D, S, H, B}, box {128 bytes of D, box_rows, 1, 1}, 128-byte swizzle, zero fill.
 static int32_t make_tmap_bhsd(fusor_cuda_ctx* ctx, CUtensorMap* tm, const fusor_cuda_tensor4* t, int box_rows,
                               CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
+    const cuuint64_t esz = dt == CU_TENSOR_MAP_DATA_TYPE_FLOAT32 ? 4 : 2;
     cuuint64_t dims[4] = {(cuuint64_t)t->shape[3], (cuuint64_t)t->shape[2], (cuuint64_t)t->shape[1], (cuuint64_t)t->shape[0]};
-    cuuint64_t strides[3] = {(cuuint64_t)t->stride[2] * 2, (cuuint64_t)t->stride[1] * 2, (cuuint64_t)t->stride[0] * 2};
+    cuuint64_t strides[3] = {(cuuint64_t)t->stride[2] * esz, (cuuint64_t)t->stride[1] * esz, (cuuint64_t)t->stride[0] * esz};
     // an extent-1 axis may carry any stride; give the encoder a legal one
     for (int i = 0; i < 3; ++i)
-        if (dims[i + 1] == 1) strides[i] = (i == 0 ? dims[0] * 2 : strides[i - 1] * dims[i]);
-    cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+        if (dims[i + 1] == 1) strides[i] = (i == 0 ? dims[0] * esz : strides[i - 1] * dims[i]);
+    cuuint32_t box[4] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = ctx->encode(tm, dt, 4, t->data, dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -379,13 +380,14 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
 static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
                               const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
                               const fusor_cuda_tensor4* out, float* debug, int p_mode) {
-    CUtensorMap tmQ, tmK, tmV, tmV16;
+    CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
     TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM));
     TRY(make_tmap_bhsd(ctx, &tmK, k, PF_BN));
     TRY(make_tmap_bhsd(ctx, &tmV, v, PF_BN));
+    TRY(make_tmap_bhsd(ctx, &tmO, out, PF_BM, out->dtype == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16));
     tmV16 = tmV;
     const int* flag = nullptr;
-    if (p_mode == 0) {
+    if ((p_mode & 1) == 0) {
         const size_t n = (size_t)S.B * S.Hkv * S.Skv * S.D;
         if (ctx->v16_bytes < n * 2) {
             CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
@@ -419,10 +421,12 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
     P.err = ctx->d_err;
     P.debug = debug;
+    P.debug_values = (p_mode & 2) ? 0 : 1;
+    P.debug_cta = p_mode >> 8;
     P.v_f16_overflow = flag;
     const long long grid = (long long)P.n_q_tiles * S.Hq * S.B;
     if (grid > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "grid too large");
-    prefill_sm100_kernel<<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, P);
+    prefill_sm100_kernel<<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
     return launch_check(ctx, "prefill_sm100_kernel");
 }
 
@@ -456,7 +460,7 @@ extern "C" int32_t fusor_cuda_prefill_probe(fusor_cuda_ctx* ctx, const fusor_cud
     DeviceGuard g(ctx->device);
     if (!prefill_eligible(S, q, k, v, scale, mask_kind, out))
         return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "arguments are not eligible for the tensor-core prefill kernel");
-    return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, debug_device, p_format ? 1 : 0);
+    return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, debug_device, p_format);
 }
 
 // --------------------------------------------------------------------------- host-memory variants
@@ -1127,7 +1131,8 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
     cast_v_to_f16_kernel<<<blocks, 256, 0, local.stream>>>(C);
     TRY(launch_check(&local, "cast_v_to_f16_kernel"));
 
-    CUtensorMap tmQ, tmK, tmV, tmV16;
+    CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
+    TRY(make_tmap_bhsd(&local, &tmO, out, PF_BM, out->dtype == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16));
     TRY(make_tmap_bhsd(&local, &tmQ, q, PF_BM));
     TRY(make_tmap_bhsd(&local, &tmK, k, PF_BN));
     TRY(make_tmap_bhsd(&local, &tmV, v, PF_BN));
@@ -1144,8 +1149,10 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
     P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
     P.err = d_err;
     P.debug = nullptr;
+    P.debug_values = 0;
+    P.debug_cta = 0;
     P.v_f16_overflow = d_overflow;
-    prefill_sm100_kernel<<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, local.stream>>>(tmQ, tmK, tmV, tmV16, P);
+    prefill_sm100_kernel<<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, local.stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
     TRY(launch_check(&local, "prefill_sm100_kernel"));
     // Synchronous: wait for the result and report a device-side timeout of this call.
     int h_err = 0;

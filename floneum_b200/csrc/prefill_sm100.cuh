@@ -1,18 +1,18 @@
 // Causal / full flash-attention prefill on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
-// One CTA owns a 128-row query tile of one (batch, query head) and walks the 64-key tiles it can see
-// (causal tile skip).  Two CTAs are resident per SM (256 TMEM columns and ~97 KB of shared memory each), so
-// the softmax of one overlaps the tensor work, prologue and epilogue of the other.  Roles, by warp:
-//   warp 0      TMA producer: Q once, then K and V tiles into two 2-slot rings (128-byte swizzle, no multicast).
+// One CTA owns a 128-row query tile of one (batch, query head) and walks the PF_BN-key tiles it can see
+// (causal tile skip).  Two CTAs are resident per SM (256 TMEM columns and <= 113 KB of shared memory each),
+// so the softmax of one overlaps the tensor work, prologue and epilogue of the other.  Roles, by warp:
+//   warp 0      TMA producer: Q once, then K and V tiles into PF_SBUF-slot rings (128-byte swizzle, no multicast).
 //   warp 1      allocates TMEM and issues every tcgen05.mma from one thread:
-//               S_j = Q K_j^T   (SS: both operands in shared memory, K-major, N = 64),
-//               O  += P_j V_j   (TS: P read from TMEM, V from shared memory, MN-major, N = 128).
-//               S is double-buffered: S_{j+1} is ready before the softmax of tile j ends, and S_{j+2} is
-//               issued straight after O += P_j V_j into the buffer P_j is read from (the pipe runs in order).
-//   warps 2-5   softmax: one thread per query row reads its S row from TMEM, keeps the running max / sum,
-//               writes P (16-bit) back over S, rescales O in TMEM only when the row max has grown by more
-//               than 2^8 (lazy rescale), and finally writes O / l.
-// TMEM columns: [0,64) S0 / P0, [64,128) S1 / P1, [128,256) O.
+//               S_j = Q K_j^T   (SS: both operands in shared memory, K-major, N = PF_BN),
+//               O  += P_j V_j   (TS: P read from TMEM, V from shared memory, MN-major, N = 128),
+//               and the next S into the buffer P_j is read from straight after (the pipe runs in issue order).
+//   warps 2..   softmax: PF_TPR threads per query row read S from TMEM, keep the running max / sum, write P
+//               (16-bit) back over S, rescale O in TMEM only when the row max has grown by more than 2^8
+//               (lazy rescale), and finally write O / l.  With two threads per row the two warps that share a
+//               TMEM lane quadrant swap their partial row maxima through shared memory.
+// TMEM columns: S / P buffers from column 0 (PF_SBUF x PF_BN <= 128), O in [128,256).
 // All waits are bounded (ptx_sm100.cuh); on a timeout the CTA unwinds and frees its TMEM.
 //
 // Replaces the reference's fused kernel for Sq > 1
@@ -25,16 +25,29 @@
 
 namespace fusor {
 
-constexpr int PF_BM = 128, PF_BN = 64, PF_D = 128;
-constexpr int PF_THREADS = 192;               // warp 0 TMA, warp 1 MMA, warps 2..5 softmax (warp % 4 = TMEM lane quadrant)
-constexpr int PF_Q_BYTES = PF_BM * PF_D * 2;  // 32 KB = two [128][64] halves
+#ifndef PF_BN_CFG
+#define PF_BN_CFG 64
+#endif
+#ifndef PF_SBUF_CFG
+#define PF_SBUF_CFG 2
+#endif
+#ifndef PF_TPR_CFG
+#define PF_TPR_CFG 1
+#endif
+constexpr int PF_BM = 128, PF_BN = PF_BN_CFG, PF_D = 128;
+constexpr int PF_SBUF = PF_SBUF_CFG;           // S buffers in TMEM = K / V ring slots
+constexpr int PF_TPR = PF_TPR_CFG;             // softmax threads per query row
+constexpr int PF_CPT = PF_BN / PF_TPR;         // key columns per softmax thread
+constexpr int PF_THREADS = 64 + 128 * PF_TPR;  // warp 0 TMA, warp 1 MMA, then softmax warps (warp % 4 = TMEM lane quadrant)
+constexpr int PF_Q_BYTES = PF_BM * PF_D * 2;   // two [128][64] halves
 constexpr int PF_Q_HALF = PF_Q_BYTES / 2;
-constexpr int PF_KV_BYTES = PF_BN * PF_D * 2;  // 16 KB = two [64][64] halves
+constexpr int PF_KV_BYTES = PF_BN * PF_D * 2;  // two [PF_BN][64] halves
 constexpr int PF_KV_HALF = PF_KV_BYTES / 2;
 constexpr uint32_t PF_TMEM_COLS = 256;
-constexpr uint32_t PF_COL_S = 0, PF_COL_O = 128;  // S buffer b at PF_COL_S + 64 b
+constexpr uint32_t PF_COL_S = 0, PF_COL_O = 128;  // S buffer b at PF_COL_S + PF_BN b
 constexpr float PF_RESCALE_THRESHOLD = 8.0f;      // in log2 units
-constexpr int PF_DEBUG_ROW = 258;                 // debug dump: per row 64 raw scores, pad, 128 O values at [128,256), m, l
+constexpr int PF_DEBUG_ROW = 258;                 // debug dump: per row raw scores [0,PF_BN), O at [128,256), m, l
+static_assert(PF_SBUF * PF_BN <= 128 && PF_CPT % 32 == 0 && (PF_TPR == 1 || PF_TPR == 2), "tile configuration");
 
 struct PrefillParams {
     void* out;
@@ -46,10 +59,12 @@ struct PrefillParams {
     int n_q_tiles;
     int* err;
     float* debug;              // optional diagnostic dump from CTA 0 (see fusor_cuda_prefill_probe)
+    int debug_values;          // dump S / O / m / l values as well as the cycle stamps
+    int debug_cta;             // which CTA is traced
     const int* v_f16_overflow; // written by the V pre-pass: non-zero when some |v| does not fit f16; null = no f16 copy
 };
 
-constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_Q_BYTES + 4 * (size_t)PF_KV_BYTES + 256;
+constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_Q_BYTES + 2 * PF_SBUF * (size_t)PF_KV_BYTES + 512 + 6 * 128 * 4;
 
 // P (the softmax weights handed to the second MMA) and V must have the same 16-bit type: kind::f16 rejects a
 // mixed f16 / bf16 operand pair.  bf16 weights (8 significant bits) put rows with few keys above the 2e-3
@@ -59,13 +74,13 @@ constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_Q_BYTES + 4 * (size_t)PF_KV_B
 __global__ void __launch_bounds__(PF_THREADS, 2)
     prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmV16,
-                         const PrefillParams P) {
+                         const __grid_constant__ CUtensorMap tmO, const PrefillParams P) {
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_sm = base;
-    uint8_t* k_sm = q_sm + PF_Q_BYTES;       // 2 slots
-    uint8_t* v_sm = k_sm + 2 * PF_KV_BYTES;  // 2 slots
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + 2 * PF_KV_BYTES);
+    uint8_t* k_sm = q_sm + PF_Q_BYTES;             // PF_SBUF slots
+    uint8_t* v_sm = k_sm + PF_SBUF * PF_KV_BYTES;  // PF_SBUF slots
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + PF_SBUF * PF_KV_BYTES);
     uint64_t* q_full = bars + 0;
     uint64_t* k_full = bars + 1;    // [2]
     uint64_t* k_empty = bars + 3;   // [2]
@@ -74,15 +89,24 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
     uint64_t* s_full = bars + 9;    // [2]
     uint64_t* p_full = bars + 11;   // [2]
     uint64_t* pv_done = bars + 13;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t* xch_bar = bars + 14;  // [4] one per TMEM lane quadrant: the two softmax warps of a quadrant meet here
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(bars + 32);  // [3][2 halves][128 rows]: partial maxima (2 buffers), row sums
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // diagnostic timeline (probe entry point only): cycle stamps of CTA 0 after the [128][258] value dump
     const long long t_start = clock64();
-    const bool trace = P.debug != nullptr && blockIdx.x == 0;
+    const bool trace = P.debug != nullptr && blockIdx.x == P.debug_cta;
     auto stamp = [&](int slot) {
         if (trace) P.debug[128 * PF_DEBUG_ROW + slot] = (float)(clock64() - t_start);
+    };
+    auto stamp_ns = [&](int slot) {  // low 24 bits of the nanosecond wall clock
+        if (trace) {
+            unsigned long long ns;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+            P.debug[128 * PF_DEBUG_ROW + slot] = (float)(ns & 0xFFFFFFull);
+        }
     };
     const bool use_f16 = P.v_f16_overflow != nullptr && *P.v_f16_overflow == 0;
 
@@ -105,9 +129,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             mbar_init(v_full + i, 1);
             mbar_init(v_empty + i, 1);
             mbar_init(s_full + i, 1);
-            mbar_init(p_full + i, 128);
+            mbar_init(p_full + i, 128 * PF_TPR);
         }
         mbar_init(pv_done, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(xch_bar + i, 64);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmQ);
@@ -131,7 +156,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             tma_load_4d(q_sm, &tmQ, q_full, 0, q0, h, b);
             tma_load_4d(q_sm + PF_Q_HALF, &tmQ, q_full, 64, q0, h, b);
             for (int j = 0; j < n_kv; ++j) {
-                const int st = j & 1, use = j >> 1;
+                const int st = j % PF_SBUF, use = j / PF_SBUF;
                 if (use > 0 && !mbar_wait(k_empty + st, (use - 1) & 1, abort_flag, P.err)) break;
                 mbar_arrive_expect_tx(k_full + st, PF_KV_BYTES);
                 tma_load_4d(k_sm + st * PF_KV_BYTES, &tmK, k_full + st, 0, j * PF_BN, hk, b);
@@ -145,36 +170,33 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            // S = Q K^T : A, B bf16, both K-major, M = 128, N = 64
+            // S = Q K^T : A, B bf16, both K-major, M = 128, N = PF_BN
             constexpr uint32_t idesc_qk = make_idesc_f16(1, 1, 0, 0, PF_BM, PF_BN);
             // O += P V  : A = P (TMEM, K-major), B = V MN-major, M = 128, N = D; both f16 or both bf16
             const uint32_t idesc_pv = use_f16 ? make_idesc_f16(0, 0, 0, 1, PF_BM, PF_D) : make_idesc_f16(1, 1, 0, 1, PF_BM, PF_D);
             const uint32_t q_addr = smem_u32(q_sm), k_addr0 = smem_u32(k_sm), v_addr0 = smem_u32(v_sm);
-            auto issue_qk = [&](int j) {  // K tile j (ring slot j & 1) -> S buffer j & 1
-                const uint32_t k_addr = k_addr0 + (j & 1) * PF_KV_BYTES;
-                const uint32_t d_tmem = tmem_base + PF_COL_S + (j & 1) * PF_BN;
+            auto issue_qk = [&](int j) {  // K tile j (ring slot j % PF_SBUF) -> S buffer j % PF_SBUF
+                const int st = j % PF_SBUF;
+                const uint32_t k_addr = k_addr0 + st * PF_KV_BYTES;
+                const uint32_t d_tmem = tmem_base + PF_COL_S + st * PF_BN;
 #pragma unroll
                 for (int kk = 0; kk < PF_D / 16; ++kk) {
                     tc_mma_ss(d_tmem, make_smem_desc_sw128(q_addr + (kk >> 2) * PF_Q_HALF + (kk & 3) * 32, 16, 1024),
                               make_smem_desc_sw128(k_addr + (kk >> 2) * PF_KV_HALF + (kk & 3) * 32, 16, 1024), idesc_qk, kk > 0);
                 }
-                tc_commit(s_full + (j & 1));
-                tc_commit(k_empty + (j & 1));
+                tc_commit(s_full + st);
+                tc_commit(k_empty + st);
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag, P.err) && mbar_wait(k_full + 0, 0, abort_flag, P.err);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0);
-            }
-            if (ok && n_kv > 1) {
-                ok = mbar_wait(k_full + 1, 0, abort_flag, P.err);
+            bool ok = mbar_wait(q_full, 0, abort_flag, P.err);
+            for (int t = 0; t < PF_SBUF && t < n_kv && ok; ++t) {
+                ok = mbar_wait(k_full + t, 0, abort_flag, P.err);
                 if (ok) {
                     tc_fence_after();
-                    issue_qk(1);
+                    issue_qk(t);
                 }
             }
             for (int j = 0; j < n_kv && ok; ++j) {
-                const int st = j & 1, ph = (j >> 1) & 1;
+                const int st = j % PF_SBUF, ph = (j / PF_SBUF) & 1;
                 if (j < 32) stamp(256 + j * 4 + 0);
                 ok = mbar_wait(p_full + st, ph, abort_flag, P.err) && mbar_wait(v_full + st, ph, abort_flag, P.err);
                 if (!ok) break;
@@ -189,72 +211,89 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 }
                 tc_commit(v_empty + st);
                 tc_commit(pv_done);
-                if (j + 2 < n_kv) {
-                    // S_{j+2} overwrites the columns P_j is being read from: the tensor pipe executes in issue order
-                    ok = mbar_wait(k_full + st, ((j + 2) >> 1) & 1, abort_flag, P.err);
+                if (j + PF_SBUF < n_kv) {
+                    // the next S for this buffer overwrites the columns P_j is being read from: issue order = execution order
+                    ok = mbar_wait(k_full + st, ((j + PF_SBUF) / PF_SBUF) & 1, abort_flag, P.err);
                     if (!ok) break;
                     tc_fence_after();
                     if (j < 32) stamp(256 + j * 4 + 2);
-                    issue_qk(j + 2);
+                    issue_qk(j + PF_SBUF);
                     if (j < 32) stamp(256 + j * 4 + 3);
                 }
             }
         }
     } else {
         // ------------------------------------------------------------------ softmax / correction / epilogue
-        const int row = (warp & 3) * 32 + lane;                        // 0..127 = TMEM lane = query row of the tile
-        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lane quadrant
+        // PF_TPR threads per query row; thread `half` owns key columns [half*PF_CPT, (half+1)*PF_CPT) of each
+        // S tile and output columns [half*128/PF_TPR, ...).
+        const int half = (warp - 2) >> 2;
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;                        // 0..127 = TMEM lane = query row of the tile
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;  // this warp's TMEM lane quadrant
         const int qi = q0 + row;
         const int k_limit = P.causal ? min(P.Skv - 1, qi + offset) : P.Skv - 1;  // last key this row may see
         const float c = P.scale_log2;
-        const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O;
+        constexpr int OC = 128 / PF_TPR;  // output columns per thread
+        const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O + half * OC;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
-        const bool tr = row == 0;
+        const bool tr = row == 0 && half == 0;
+        if (tr) {
+            stamp(499);
+            stamp_ns(502);
+        }
         for (int j = 0; j < n_kv && ok; ++j) {
-            const int st = j & 1;
+            const int st = j % PF_SBUF;
             const uint32_t s_tmem = tmem_base + lane_base + PF_COL_S + st * PF_BN;
             if (tr && j < 32) stamp(j * 8 + 0);
-            ok = mbar_wait(s_full + st, (j >> 1) & 1, abort_flag, P.err);
+            ok = mbar_wait(s_full + st, (j / PF_SBUF) & 1, abort_flag, P.err);
             if (!ok) break;
             tc_fence_after();
             if (tr && j < 32) stamp(j * 8 + 1);
-            float s[PF_BN];
-            tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+            float s[PF_CPT];
+#pragma unroll
+            for (int cc = 0; cc < PF_CPT / 32; ++cc)
+                tmem_ld32(s_tmem + half * PF_CPT + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
             tc_wait_ld();
             if (tr && j < 32) stamp(j * 8 + 2);
-            if (P.debug && blockIdx.x == 0 && j == 0) {
+            if (trace && P.debug_values && j == 0) {
 #pragma unroll
-                for (int i = 0; i < PF_BN; ++i) P.debug[row * PF_DEBUG_ROW + i] = s[i];
+                for (int i = 0; i < PF_CPT; ++i) P.debug[row * PF_DEBUG_ROW + half * PF_CPT + i] = s[i];
             }
-            const int k0 = j * PF_BN;
-            if (k0 + PF_BN - 1 > k_limit) {  // diagonal or ragged tile: mask in the raw domain
+            const int k0 = j * PF_BN + half * PF_CPT;
+            if (k0 + PF_CPT - 1 > k_limit) {  // diagonal or ragged tile: mask in the raw domain
 #pragma unroll
-                for (int i = 0; i < PF_BN; ++i)
+                for (int i = 0; i < PF_CPT; ++i)
                     if (k0 + i > k_limit) s[i] = -INFINITY;
             }
             float mx[8];
 #pragma unroll
-            for (int a = 0; a < 8; ++a) mx[a] = fmax3(s[8 * a], s[8 * a + 1], s[8 * a + 2]);
+            for (int a = 0; a < 8; ++a) mx[a] = fmaxf(s[4 * a], s[4 * a + 1]);
 #pragma unroll
-            for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[8 * a + 3], s[8 * a + 4]);
+            for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[4 * a + 2], s[4 * a + 3]);
 #pragma unroll
-            for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[8 * a + 5], s[8 * a + 6]);
+            for (int i = 32; i < PF_CPT; i += 16)
 #pragma unroll
-            for (int a = 0; a < 8; a += 2) mx[a] = fmax3(mx[a], s[8 * a + 7], fmaxf(mx[a + 1], s[8 * a + 15]));
-            const float tmax = fmaxf(fmaxf(mx[0], mx[2]), fmaxf(mx[4], mx[6])) * c;  // scale > 0
-            // lazy rescale: keep the reference max until the true max has moved by more than the threshold
-            float alpha = 1.0f;
-            if (tmax > m_ref + PF_RESCALE_THRESHOLD) {  // also true on the first tile (m_ref = -inf)
-                alpha = fast_exp2(m_ref - tmax);        // 0 on the first tile
-                m_ref = tmax;
+                for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[i + 2 * a], s[i + 2 * a + 1]);
+            float pmax = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+            if (PF_TPR == 2) {
+                // swap partial maxima with the thread that owns the other columns of this row
+                xch[((j & 1) * 2 + half) * 128 + row] = pmax;
+                mbar_arrive(xch_bar + quad);
+                ok = mbar_wait(xch_bar + quad, j & 1, abort_flag, P.err);
+                if (!ok) break;
+                pmax = fmaxf(pmax, xch[((j & 1) * 2 + (half ^ 1)) * 128 + row]);
             }
+            const float tmax = pmax * c;  // scale > 0
+            // lazy rescale: keep the reference max until the true max has moved by more than the threshold
+            const float m_new = (tmax > m_ref + PF_RESCALE_THRESHOLD) ? tmax : m_ref;  // also taken on the first tile
+            const float alpha = fast_exp2(m_ref - m_new);                              // 1 when unchanged, 0 on the first tile
+            m_ref = m_new;
             if (tr && j < 32) stamp(j * 8 + 3);
             const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_ref, -m_ref);
             float2 ps0 = make_float2(0.0f, 0.0f), ps1 = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int cc = 0; cc < PF_BN / 32; ++cc) {
+            for (int cc = 0; cc < PF_CPT / 32; ++cc) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
@@ -267,7 +306,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                     pk[i] = use_f16 ? pack_f16(p0.x, p0.y) : pack_bf16(p0.x, p0.y);
                     pk[i + 1] = use_f16 ? pack_f16(p1.x, p1.y) : pack_bf16(p1.x, p1.y);
                 }
-                tmem_st16(s_tmem + cc * 16, pk);  // P overwrites the first 32 columns of this S buffer
+                tmem_st16(s_tmem + (half * PF_CPT) / 2 + cc * 16, pk);  // P overwrites the first PF_BN/2 columns of this S buffer
             }
             l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
             if (tr && j < 32) stamp(j * 8 + 4);
@@ -281,7 +320,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
                     const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
+                    for (int cc = 0; cc < OC / 32; ++cc) {
                         float orr[32];
                         tmem_ld32(o_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[0]));
                         tc_wait_ld();
@@ -300,47 +339,77 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             mbar_arrive(p_full + st);
             if (tr && j < 32) stamp(j * 8 + 6);
         }
+        // the row sum is the sum over the row's threads (they used the same sequence of reference maxima)
+        if (PF_TPR == 2 && ok) {
+            xch[(2 * 2 + half) * 128 + row] = l;
+            mbar_arrive(xch_bar + quad);
+            ok = mbar_wait(xch_bar + quad, n_kv & 1, abort_flag, P.err);
+            if (ok) l += xch[(2 * 2 + (half ^ 1)) * 128 + row];
+        }
         if (ok) ok = mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, P.err);
+        if (tr) stamp(500);
+        // Epilogue: O / l goes through shared memory (the Q / K / V buffers are idle once the last MMA has
+        // completed) in the 128-byte-swizzled layout of the output tensor map, then out with TMA stores:
+        // full 128-byte lines instead of one 16-byte piece per row per instruction.  Rows past Sq are clipped.
+        constexpr int BLK_BYTES = 128 * 128;  // one [128 rows][128 bytes] column block
         if (ok) {
             tc_fence_after();
             const float inv_l = 1.0f / l;
-            const long long obase = (long long)b * P.os[0] + (long long)h * P.os[1] + (long long)qi * P.os[2];
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = 0; cc < OC / 32; ++cc) {
                 float orr[32];
                 tmem_ld32(o_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[0]));
                 tc_wait_ld();
-                if (P.debug && blockIdx.x == 0) {
+                if (trace && P.debug_values) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) P.debug[row * PF_DEBUG_ROW + 128 + cc * 32 + i] = orr[i];
-                    if (cc == 0) {
+                    for (int i = 0; i < 32; ++i) P.debug[row * PF_DEBUG_ROW + 128 + half * OC + cc * 32 + i] = orr[i];
+                    if (cc == 0 && half == 0) {
                         P.debug[row * PF_DEBUG_ROW + 256] = m_ref;
                         P.debug[row * PF_DEBUG_ROW + 257] = l;
                     }
                 }
-                if (qi < P.Sq) {
-                    if (P.out_dtype == 0) {
-                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + obase + cc * 32);
+                const int col0 = half * OC + cc * 32;  // first output column of this chunk
+                if (P.out_dtype == 0) {
+                    // f32: 32 columns = one 128-byte block row = 8 chunks of 16 bytes
+                    uint8_t* blk = base + (col0 / 32) * BLK_BYTES + row * 128;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            dst[i] = make_float4(orr[4 * i] * inv_l, orr[4 * i + 1] * inv_l, orr[4 * i + 2] * inv_l,
-                                                 orr[4 * i + 3] * inv_l);
-                    } else {
-                        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(P.out) + obase + cc * 32);
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4*>(blk + ((i ^ (row & 7)) << 4)) =
+                            make_float4(orr[4 * i] * inv_l, orr[4 * i + 1] * inv_l, orr[4 * i + 2] * inv_l, orr[4 * i + 3] * inv_l);
+                } else {
+                    // bf16: 32 columns = half of a 128-byte block row = 4 chunks of 16 bytes
+                    uint8_t* blk = base + (col0 / 64) * BLK_BYTES + row * 128;
+                    const int ch0 = (col0 % 64) / 8;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            dst[i] = make_uint4(pack_bf16(orr[8 * i] * inv_l, orr[8 * i + 1] * inv_l),
-                                                pack_bf16(orr[8 * i + 2] * inv_l, orr[8 * i + 3] * inv_l),
-                                                pack_bf16(orr[8 * i + 4] * inv_l, orr[8 * i + 5] * inv_l),
-                                                pack_bf16(orr[8 * i + 6] * inv_l, orr[8 * i + 7] * inv_l));
-                    }
+                    for (int i = 0; i < 4; ++i)
+                        *reinterpret_cast<uint4*>(blk + (((ch0 + i) ^ (row & 7)) << 4)) =
+                            make_uint4(pack_bf16(orr[8 * i] * inv_l, orr[8 * i + 1] * inv_l),
+                                       pack_bf16(orr[8 * i + 2] * inv_l, orr[8 * i + 3] * inv_l),
+                                       pack_bf16(orr[8 * i + 4] * inv_l, orr[8 * i + 5] * inv_l),
+                                       pack_bf16(orr[8 * i + 6] * inv_l, orr[8 * i + 7] * inv_l));
                 }
             }
+            fence_proxy_async_smem();
+        }
+        // every softmax thread reaches this barrier, also after a timeout (then nothing is stored)
+        const int any_failed = named_bar_or(1, 128 * PF_TPR, ok ? 0 : 1);
+        if (!any_failed && warp == 2 && lane == 0) {
+            const int n_blk = P.out_dtype == 0 ? 4 : 2, blk_cols = P.out_dtype == 0 ? 32 : 64;
+            for (int kb = 0; kb < n_blk; ++kb) tma_store_4d(&tmO, base + kb * BLK_BYTES, kb * blk_cols, q0, h, b);
+            tma_store_commit_and_wait_read();
+        }
+        if (tr) {
+            stamp(501);
+            stamp_ns(503);
         }
     }
     // ---- teardown: every role falls through to here, also after a timeout
     tc_fence_before();
     __syncthreads();
+    if (P.debug != nullptr && tid == 0) {  // diagnostic: sum of CTA lifetimes in cycles, and their number
+        atomicAdd(&P.debug[128 * PF_DEBUG_ROW + 504], (float)(clock64() - t_start));
+        atomicAdd(&P.debug[128 * PF_DEBUG_ROW + 505], 1.0f);
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, PF_TMEM_COLS);

@@ -149,7 +149,8 @@ int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_cuda_tensor
 /* Diagnostic (no reference counterpart): runs the tensor-core prefill kernel with the softmax weights kept as f16 against an
  * f16 copy of V (p_format 0, the production setting) or as bf16 against the bf16 V (p_format 1) and copies out of the first CTA, into debug_device (f32, 128*258 + 512 values), per row the raw scores of its
  * first key tile [0,128), its un-normalised O [128,256), the running max in log2 units [256] and the row sum [257],
- * followed by 512 cycle stamps of that CTA's softmax and MMA loops (a timeline for tuning).
+ * followed by 512 cycle stamps of that CTA's softmax and MMA loops (a timeline for tuning).  p_format + 2 writes
+ * the cycle stamps only; bits 8 and up select the traced CTA (default 0).
  * Fails with FUSOR_CUDA_UNSUPPORTED when the arguments are not eligible for that kernel. */
 int32_t fusor_cuda_prefill_probe(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
                                  const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
