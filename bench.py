@@ -308,12 +308,16 @@ def main():
             e2e_s = max_over_ranks(time.perf_counter() - t0)
         e2e_val = flops_all * e2e_steps / e2e_s / 1e12
         e2e_ok = bool(np.array_equal(hout.numpy(), got))
-        peak = peaks["tensor_burst"]
+        # K launches back to back after a 0.5 s busy loop run under the power cap: the sustained cuBLAS figure is the
+        # denominator; the fraction of the burst figure is given beside it.
+        peak = peaks["tensor_sustained"]
         return {
             "value": value, "unit": "TFLOP/s", "ms_per_step": total_ms / args.steps, "gpu_launches": launches,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": f"{peaks['source']} (cuBLAS bf16 burst)",
-                         "frac_of_nominal_2250": achieved / 2250.0},
+                         "traffic": None, "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
+                         "frac_of_burst_peak": achieved / peaks["tensor_burst"], "burst_peak": peaks["tensor_burst"],
+                         "frac_of_nominal_2250": achieved / 2250.0,
+                         "note": "achieved counts the V pre-pass kernel's time as well (both kernels of a step)"},
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": int(in_bytes * world),
                     "d2h_bytes_per_step": int(out.numel() * 4 * world), "matches_device_path": e2e_ok},
             "clocks": clocks,

@@ -3,7 +3,7 @@
 // One CTA owns a 128-row query tile of one (batch, query head) and walks the PF_BN-key tiles it can see
 // (causal tile skip).  Two CTAs are resident per SM (256 TMEM columns and <= 113 KB of shared memory each),
 // so the softmax of one overlaps the tensor work, prologue and epilogue of the other.  Roles, by warp:
-//   warp 0      TMA producer: Q once, then K and V tiles into PF_SBUF-slot rings (128-byte swizzle, no multicast).
+//   warp 0      TMA producer: Q once, then K and V tiles into PF_SBUF-slot rings (128-byte swizzle, CTA-local loads).
 //   warp 1      allocates TMEM and issues every tcgen05.mma from one thread:
 //               S_j = Q K_j^T   (SS: both operands in shared memory, K-major, N = PF_BN),
 //               O  += P_j V_j   (TS: P read from TMEM, V from shared memory, MN-major, N = 128),

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, no multicast anywhere), tcgen05 (TMEM alloc,
+// mbarrier, TMA (cp.async.bulk.tensor, every load addressed to this CTA only), tcgen05 (TMEM alloc,
 // MMA, commit, ld/st), ldmatrix and mma.sync.  Every wait is bounded: a wait that runs
 // out records a code in a global error word and returns false so the kernel can unwind.
 #pragma once
@@ -70,7 +70,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// ----------------------------------------------------------------------------- TMA (tiled, no multicast)
+// ----------------------------------------------------------------------------- TMA (tiled, CTA-local destination)
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
