@@ -21,8 +21,15 @@
 
 namespace fusor {
 
-constexpr int DEC_PT = 16;  // tokens per page
-constexpr int DEC_NW = 4;   // consumer warps
+#ifndef DEC_CTAS_CFG
+#define DEC_CTAS_CFG 4
+#endif
+#ifndef DEC_NW_CFG
+#define DEC_NW_CFG 3
+#endif
+constexpr int DEC_PT = 16;              // tokens per page
+constexpr int DEC_NW = DEC_NW_CFG;      // consumer warps
+constexpr int DEC_CTAS = DEC_CTAS_CFG;  // resident CTAs per SM the kernel is sized for
 constexpr int DEC_THREADS = (DEC_NW + 1) * 32;
 constexpr int DEC_GP = 8;   // query heads per kv head are padded to 8 rows (g <= 8)
 
@@ -62,7 +69,7 @@ struct DecodeSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK,
                                                                      const __grid_constant__ CUtensorMap tmV,
                                                                      const DecodeParams P) {
     constexpr int PAGE_BYTES = DecodeSmem<D>::PAGE_BYTES;
@@ -82,7 +89,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
     if (tid == 0) {
         for (int i = 0; i < R; ++i) {
             mbar_init(full + i, 1);
-            mbar_init(empty + i, 1);
+            mbar_init(empty + i, DEC_NW);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -96,7 +103,11 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
 
     if (warp == DEC_NW) {
         // ------------------------------------------------------------------ producer warp
-        int i = 0;
+        // Lane 0 owns the ring bookkeeping; the 2*(D/64) TMA copies of a page (K and V, 64 columns each) are
+        // issued by as many lanes in one warp instruction.
+        constexpr int NOPS = 2 * (D / 64);
+        int slot = 0, phase = 0;  // ring position of the next page; `phase` flips each time the ring wraps
+        bool wrapped = false;
         bool ok = true;
         for (int sg = seg_begin; sg < seg_end && ok; ++sg) {
             const DecodeSegment S = P.segs[sg];
@@ -107,29 +118,31 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
                 const int my_phys = next_phys;
                 // page ids of the next batch are fetched before this batch is issued
                 next_phys = (p0 + 32 + lane < S.page_end) ? pt[p0 + 32 + lane] : 0;
-                for (int j = 0; j < n && ok; ++j, ++i) {
+                for (int j = 0; j < n && ok; ++j) {
                     int phys = __shfl_sync(0xffffffffu, my_phys, j);
+                    if (phys < 0 || phys >= P.num_pages) {  // record and read page 0 instead
+                        if (lane == 0) atomicExch(P.err, kErrBadPage);
+                        phys = 0;
+                    }
                     int good = 1;
                     if (lane == 0) {
-                        const int slot = i % R, use = i / R;
-                        if (use > 0) good = mbar_wait(empty + slot, (use - 1) & 1, abort_flag, P.err) ? 1 : 0;
-                        if (good) {
-                            if (phys < 0 || phys >= P.num_pages) {  // record and read page 0 instead
-                                atomicExch(P.err, kErrBadPage);
-                                phys = 0;
-                            }
-                            const int row = (phys * P.Hkv + S.hk) * DEC_PT;
-                            mbar_arrive_expect_tx(full + slot, 2 * PAGE_BYTES);
-#pragma unroll
-                            for (int hf = 0; hf < D / 64; ++hf) {
-                                tma_load_2d(ksm + (size_t)slot * PAGE_BYTES + hf * HALF_BYTES, &tmK, full + slot,
-                                            hf * 64, row);
-                                tma_load_2d(vsm + (size_t)slot * PAGE_BYTES + hf * HALF_BYTES, &tmV, full + slot,
-                                            hf * 64, row);
-                            }
-                        }
+                        if (wrapped) good = mbar_wait(empty + slot, phase ^ 1, abort_flag, P.err, 1) ? 1 : 0;
+                        if (good) mbar_arrive_expect_tx(full + slot, 2 * PAGE_BYTES);
                     }
                     ok = __shfl_sync(0xffffffffu, good, 0) != 0;
+                    if (ok && lane < NOPS) {
+                        // lanes 0, 2 copy the K halves, lanes 1, 3 the V halves (the tensor map is named statically)
+                        const int row = (phys * P.Hkv + S.hk) * DEC_PT;
+                        const int hf = lane >> 1;
+                        const size_t off = (size_t)slot * PAGE_BYTES + hf * HALF_BYTES;
+                        if (lane & 1) tma_load_2d(vsm + off, &tmV, full + slot, hf * 64, row);
+                        else tma_load_2d(ksm + off, &tmK, full + slot, hf * 64, row);
+                    }
+                    if (++slot == R) {
+                        slot = 0;
+                        phase ^= 1;
+                        wrapped = true;
+                    }
                 }
             }
         }
@@ -139,6 +152,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
         const int cq = (lane & 3) * 2;    // column pair inside an 8-wide tile
         const bool row_valid = r < P.g;
         bool aborted = false;
+        int cslot = 0, cphase = 0;  // ring position of the next page of the CTA's stream
         // ldmatrix lane geometry
         const int lm_j = lane >> 3, lm_r = lane & 7;
         const uint32_t ksm_u = smem_u32(ksm), vsm_u = smem_u32(vsm);
@@ -174,18 +188,26 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_splitkv_kernel(const __gri
             for (int nd = 0; nd < D / 8; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.0f;
 
             const int n_pages = S.page_end - S.page_begin;
-            // Every consumer warp waits for every page of the CTA's stream in order, so that it observes each
-            // phase of each ring slot's barrier (a warp that skipped the pages of other warps could meet a slot
-            // two phases later, which a parity wait cannot tell from "ready"); only the owner processes a page.
+            // Every consumer warp waits for every page of the CTA's stream in order and releases the slot once it
+            // has seen it (the owner: once it has used it).  The producer refills a slot only after all DEC_NW
+            // releases, so no warp can meet a slot's barrier two phases later, which a parity wait cannot tell
+            // from "ready".
             for (int i = S.cta_page_off; i < S.cta_page_off + n_pages; ++i) {
                 if (aborted) break;
-                const int slot = i % R;
-                const bool got = mbar_wait(full + slot, (i / R) & 1, abort_flag, P.err);
+                const int slot = cslot;
+                const bool got = mbar_wait(full + slot, cphase, abort_flag, P.err, 2 + (i % DEC_NW == warp ? 1 : 0));
                 if (!__all_sync(0xffffffffu, got)) {
                     aborted = true;
                     break;
                 }
-                if (i % DEC_NW != warp) continue;
+                if (++cslot == R) {
+                    cslot = 0;
+                    cphase ^= 1;
+                }
+                if (i % DEC_NW != warp) {
+                    if (lane == 0) mbar_arrive(empty + slot);
+                    continue;
+                }
                 const int tok0 = (S.page_begin + (i - S.cta_page_off)) * DEC_PT;
                 const uint32_t kb = ksm_u + slot * PAGE_BYTES, vb = vsm_u + slot * PAGE_BYTES;
 

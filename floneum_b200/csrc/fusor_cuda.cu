@@ -138,8 +138,8 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
     ctx->encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
     // opt in to large dynamic shared memory once per context
     cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
-    cudaFuncSetAttribute(decode_splitkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024);
-    cudaFuncSetAttribute(decode_splitkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024);
+    cudaFuncSetAttribute(decode_splitkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(decode_splitkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(general_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)general_smem_bytes(GEN_MAX_D));
     cudaError_t e = cudaGetLastError();
@@ -190,8 +190,8 @@ static int32_t check_device_error(fusor_cuda_ctx* ctx) {
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     if (h != 0) {
         cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream);
-        if (h == kErrWaitTimeout)
-            return fail(ctx, FUSOR_CUDA_TIMEOUT, "a bounded device-side wait ran out (kernel unwound, result invalid)");
+        if ((h & 0xff) == kErrWaitTimeout)
+            return fail(ctx, FUSOR_CUDA_TIMEOUT, "a bounded device-side wait ran out at wait site %d (kernel unwound, result invalid)", h >> 8);
         if (h == kErrBadPage)
             return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "page table holds a page index outside the pool");
         return fail(ctx, FUSOR_CUDA_INTERNAL, "device error word = %d", h);
@@ -576,7 +576,7 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
     c->ctx = ctx; c->max_batch = max_batch; c->Hkv = num_kv_heads; c->D = head_dim; c->PT = page_tokens;
     c->num_pages = num_pages; c->max_pages = max_pages_per_seq;
     const size_t pool_bytes = (size_t)num_pages * num_kv_heads * DEC_PT * head_dim * 2;
-    c->max_grid = 2 * ctx->num_sms;
+    c->max_grid = DEC_CTAS * ctx->num_sms;
     c->max_slots = max_batch * num_kv_heads + c->max_grid;
     bool ok = cudaMalloc(&c->k_pages, pool_bytes) == cudaSuccess && cudaMalloc(&c->v_pages, pool_bytes) == cudaSuccess &&
               cudaMalloc(&c->d_page_table, (size_t)max_batch * max_pages_per_seq * 4) == cudaSuccess &&
@@ -618,9 +618,10 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
     }
     // ring depth: two CTAs per SM, each within 113 KB of dynamic shared memory
     const int page_bytes = DEC_PT * head_dim * 2;
-    c->ring = head_dim == 128 ? 10 : 20;
+    // ring depth: DEC_CTAS CTAs per SM within ~227 KB of shared memory
+    const int budget = (227 * 1024) / DEC_CTAS - 1024 - 1024 - DEC_NW * DEC_GP * (head_dim + 2) * 4 - 1024;
+    c->ring = std::min(24, budget / (2 * page_bytes + 16));
     c->smem = head_dim == 128 ? DecodeSmem<128>::bytes(c->ring) : DecodeSmem<64>::bytes(c->ring);
-    (void)page_bytes;
     *out = c;
     return FUSOR_CUDA_OK;
 }

@@ -52,7 +52,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #ifndef FUSOR_WAIT_LIMIT_CYCLES
 #define FUSOR_WAIT_LIMIT_CYCLES 2000000000ll
 #endif
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err_word) {
+// `site` identifies the wait in the kernel; the first wait that runs out records it in bits 8.. of the error word.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err_word,
+                                          int site = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
@@ -60,7 +62,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (*abort_flag) return false;
         if (clock64() - t0 > FUSOR_WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
-            atomicExch(err_word, kErrWaitTimeout);
+            atomicCAS(err_word, 0, kErrWaitTimeout | (site << 8));
             return false;
         }
     }
