@@ -314,7 +314,10 @@ def main():
         return {
             "value": value, "unit": "TFLOP/s", "ms_per_step": total_ms / args.steps, "gpu_launches": launches,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
+                         # dram read+write of one launch, scaled by (batch, head) pairs from the ncu capture of the
+                         # B2 Hq16 case (68.8 MB for 32 pairs; profiles/prefill_sm100_kernel_cfg2.md)
+                         "traffic": 68.8e6 * (B * (q1 - q0)) / 32.0 if D == 128 and S == 4096 else None,
+                         "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
                          "frac_of_burst_peak": achieved / peaks["tensor_burst"], "burst_peak": peaks["tensor_burst"],
                          "frac_of_nominal_2250": achieved / 2250.0,
                          "note": "achieved counts the V pre-pass kernel's time as well (both kernels of a step)"},
@@ -373,12 +376,30 @@ def main():
             dev.synchronize()
         ms = [a.elapsed_time(b) for a, b in evs]
         mean_ms = max_over_ranks(statistics.mean(ms))
+        # e2e: the host-buffer entry point (q up, result down; the KV cache is the library's device-resident object)
+        e2e = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+        if not (chunked and world > 1) and not args.quick:
+            qh = np.ascontiguousarray(qn, dtype=np.float32)
+            for _ in range(2):
+                cache.decode_host(qh, w.scale)
+            barrier()
+            t0 = time.perf_counter()
+            n_e2e = max(3, min(args.steps, 20))
+            for _ in range(n_e2e):
+                host_out = cache.decode_host(qh, w.scale)
+            e2e_s = max_over_ranks(time.perf_counter() - t0)
+            e2e = {"unit": "GB/s", "h2d_bytes_per_step": int(qh.nbytes * world), "d2h_bytes_per_step": int(host_out.nbytes * world)}
         bytes_rank = kv_bytes_rank + B * (q1 - q0) * D * 6 + 4 * float(np.sum((w.kv_len + 15) // 16))
         bytes_all = bytes_rank * world
         achieved = bytes_rank / (statistics.mean(ms) * 1e-3) / 1e9
-        return {"value": bytes_all / (mean_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": mean_ms, "gpu_launches": launches,
+        if "value" not in e2e:
+            e2e["value"] = bytes_all * n_e2e / e2e_s / 1e9
+        return {"value": bytes_all / (mean_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": mean_ms, "gpu_launches": launches, "e2e": e2e,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                             "frac": achieved / peaks["hbm"], "traffic": None, "peak_source": f"{peaks['source']} (device copy)",
+                             "frac": achieved / peaks["hbm"],
+                             # ncu capture of the B16 case: dram read+write = 1.02 x the algorithmic bytes, scaled by bytes
+                             # (profiles/decode_splitkv_kernel_cfg3.md)
+                             "traffic": bytes_rank * 1.02, "peak_source": f"{peaks['source']} (device copy)",
                              "frac_of_nominal_8000": achieved / 8000.0},
                 "config": {"workload": f"{tag}: paged GQA decode B{B} Hq{Hq} Hkv{Hkv_all} D{D}, 16-token pages, "
                            f"kv tokens {int(np.sum(w.kv_len))}", "bytes_per_step": bytes_all,
@@ -425,9 +446,24 @@ def main():
             if world > 1:
                 r["config"]["sharding"] = f"KV sequence split into {world} contiguous chunks, partials all-gathered over NCCL"
                 r["value"] = r["value"]  # bytes_all already counts every rank's chunk
-        got = r.pop("_got"); r.pop("_q"); r.pop("_krange")
+        got = r.pop("_got"); qn = r.pop("_q"); k0, k1 = r.pop("_krange")
         r["parity"] = {"finite": bool(np.isfinite(got).all())}
-        r["e2e"] = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+        if rank == 0 and not args.quick:
+            if args.workload == "cfg3":
+                nb = min(8, qn.shape[0])
+                want = np.stack([O.flash_attention(qn[b:b + 1], w.k_dense[b][None, k0:k1], w.v_dense[b][None, k0:k1], w.scale)[0]
+                                 for b in range(nb)])
+                err = np.abs(got[:nb] - want)
+            else:
+                wf = w if world == 1 else W.cfg4()  # rank 0 rebuilds the whole sequence for the check
+                want = O.flash_attention(wf.q, wf.k_dense[0][None], wf.v_dense[0][None], wf.scale)
+                err = np.abs(got.reshape(want.shape) - want)
+            r["parity"].update(max_abs=float(err.max()), mean_abs=float(err.mean()), tolerance="max 2e-3, mean 2e-4")
+            if world == 1:
+                fn, nbytes, desc = cpu_decode_sample(w, 4 if args.workload == "cfg3" else 1)
+                sec = time_cpu(fn, 2, 1)
+                r["cpu_baseline"] = {"value": nbytes / sec / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+                                     "sample": desc, "seconds_per_sample": sec}
         dtype = "bf16"
 
     if rank == 0:
