@@ -144,12 +144,16 @@ def reference_arm(args, rank):
         w = W.cfg2() if args.workload == "cfg2" else W.cfg5()
         fn, work, desc = cpu_prefill_sample(w)
         unit, scale_div = "TFLOP/s", 1e12
-        cfg = {"workload": f"{args.workload}: causal prefill B{w.q.shape[0]} S{w.q.shape[2]} Hq{w.q.shape[1]} Hkv{w.k.shape[1]} D128"}
+        cfg = {"workload": f"{args.workload}: causal flash-attention prefill B{w.q.shape[0]} S{w.q.shape[2]} Hq{w.q.shape[1]} "
+                           f"Hkv{w.k.shape[1]} D128, bf16 in, f32 out", "flops_per_step": w.flops,
+               "note": "CPU arm: each step is the bounded sample named in cpu_baseline.sample"}
     else:
         w = W.cfg3() if args.workload == "cfg3" else W.cfg4()
         fn, work, desc = cpu_decode_sample(w)
         unit, scale_div = "GB/s", 1e9
-        cfg = {"workload": f"{args.workload}: paged GQA decode"}
+        cfg = {"workload": f"{args.workload}: paged GQA decode B{w.q.shape[0]} Hq{w.q.shape[1]} Hkv{w.k_pages.shape[1]} D128, "
+                           f"16-token pages, kv tokens {int(np.sum(w.kv_len))}", "bytes_per_step": w.bytes,
+               "note": "CPU arm: each step is the bounded sample named in cpu_baseline.sample"}
     sec = time_cpu(fn, args.steps, min(args.warmup, 1))
     val = work / sec / scale_div
     cores = O.num_threads()
