@@ -188,6 +188,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--no-extras", action="store_true", help="skip the decode line and the CPU baseline")
+    ap.add_argument("--shard-of", type=int, default=0, help="for profiler captures on one GPU: run rank 0's shard of an "
+                    "N-rank job (no process group; the line is marked as a shard)")
     ap.add_argument("--quick", action="store_true", help="for profiler captures: no clock-settling loop, no e2e, no extras")
     ap.add_argument("--small", action="store_true", help="for profiler captures: a scaled-down case of the workload "
                     "(prefill B2 Hq16 Hkv4 S4096; decode B16)")
@@ -196,6 +198,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    fake_world = args.shard_of if (world == 1 and args.shard_of > 1) else 0
     if args.impl == "reference":
         reference_arm(args, rank)
         return
@@ -209,18 +212,21 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    use_dist = world > 1
+    if fake_world:
+        world = fake_world  # shard sizes as in an N-rank job; no collectives, no cross-rank reductions
     stream = torch.cuda.Stream()
     dev = fb.Device.gpu(local_rank, stream.cuda_stream)
     peaks = load_peaks()
     cuda = torch.device(f"cuda:{local_rank}")
 
     def barrier():
-        if world > 1:
+        if use_dist:
             dist.barrier()
         torch.cuda.synchronize()
 
     def max_over_ranks(x: float) -> float:
-        if world == 1:
+        if not use_dist:
             return x
         t = torch.tensor([x], dtype=torch.float64, device=cuda)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -355,7 +361,7 @@ def main():
         flush = torch.empty(int(300e6), dtype=torch.uint8, device=cuda) if kv_bytes_rank < 400e6 else None
 
         def step():
-            if chunked and world > 1:
+            if chunked and use_dist:
                 return sharding.decode_kv_chunks(dev, cache, tq, w.scale)
             cache.decode(tq, w.scale, to)
             return out
@@ -382,7 +388,7 @@ def main():
         mean_ms = max_over_ranks(statistics.mean(ms))
         # e2e: the host-buffer entry point (q up, result down; the KV cache is the library's device-resident object)
         e2e = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
-        if not (chunked and world > 1) and not args.quick:
+        if not (chunked and use_dist) and not args.quick:
             qh = np.ascontiguousarray(qn, dtype=np.float32)
             for _ in range(2):
                 cache.decode_host(qh, w.scale)
@@ -459,7 +465,7 @@ def main():
                                  for b in range(nb)])
                 err = np.abs(got[:nb] - want)
             else:
-                wf = w if world == 1 else W.cfg4()  # rank 0 rebuilds the whole sequence for the check
+                wf = w if (world == 1 or fake_world) else W.cfg4()  # rank 0 rebuilds the whole sequence for the check
                 want = O.flash_attention(wf.q, wf.k_dense[0][None], wf.v_dense[0][None], wf.scale)
                 err = np.abs(got.reshape(want.shape) - want)
             r["parity"].update(max_abs=float(err.max()), mean_abs=float(err.mean()), tolerance="max 2e-3, mean 2e-4")
@@ -471,7 +477,9 @@ def main():
         dtype = "bf16"
 
     if rank == 0:
-        line = {"metric": METRIC, "value": r["value"], "unit": r["unit"], "n_gpus": world, "steps": args.steps,
+        if fake_world:
+            r["config"]["shard_of"] = f"rank 0 of a {fake_world}-rank job on one GPU: value is extrapolated as {fake_world} x this shard"
+        line = {"metric": METRIC, "value": r["value"], "unit": r["unit"], "n_gpus": 1 if fake_world else world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": dtype, "data": "synthetic (seeded N(0,1) rounded to bf16; random values, no weights)",
                 "config": r["config"], "roofline": r["roofline"], "e2e": r.get("e2e"), "clocks": r.get("clocks"),
@@ -480,7 +488,7 @@ def main():
             line["cpu_baseline"] = r["cpu_baseline"]
         line.update(extras)
         print(json.dumps(line))
-    if world > 1:
+    if use_dist:
         dist.destroy_process_group()
 
 

@@ -337,18 +337,19 @@ __global__ void decode_combine_kernel(const CombineParams P) {
     const int h = blockIdx.x, b = blockIdx.y;
     const int seq = b * P.Hkv + h / P.g, rr = h % P.g;
     const int s0 = P.seq_slot_begin[seq], s1 = P.seq_slot_begin[seq + 1];
-    float M = -INFINITY;
-    for (int s = s0; s < s1; ++s) M = fmaxf(M, P.part_ml[((long long)s * DEC_GP + rr) * 2]);
-    float L = 0.0f;
-    for (int s = s0; s < s1; ++s) {
-        const float mw = P.part_ml[((long long)s * DEC_GP + rr) * 2];
-        if (mw != -INFINITY) L += P.part_ml[((long long)s * DEC_GP + rr) * 2 + 1] * fast_exp2(mw - M);
-    }
+    // one pass with an online rescale: the loads of all records are independent of the arithmetic
     for (int d = threadIdx.x; d < P.D; d += blockDim.x) {
-        float acc = 0.0f;
+        float M = -INFINITY, L = 0.0f, acc = 0.0f;
+#pragma unroll 4
         for (int s = s0; s < s1; ++s) {
-            const float mw = P.part_ml[((long long)s * DEC_GP + rr) * 2];
-            if (mw != -INFINITY) acc += P.part_o[((long long)s * DEC_GP + rr) * P.D + d] * fast_exp2(mw - M);
+            const float2 ml = *reinterpret_cast<const float2*>(P.part_ml + ((long long)s * DEC_GP + rr) * 2);
+            const float o = P.part_o[((long long)s * DEC_GP + rr) * P.D + d];
+            if (ml.x == -INFINITY) continue;
+            const float Mn = fmaxf(M, ml.x);
+            const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
+            L = L * a0 + ml.y * a1;
+            acc = acc * a0 + o * a1;
+            M = Mn;
         }
         if (P.mode == 0) {
             const long long idx = (long long)b * P.o_sb + (long long)h * P.o_sh + d;
