@@ -31,6 +31,9 @@ namespace fusor {
 #ifndef PF_SBUF_CFG
 #define PF_SBUF_CFG 2
 #endif
+#ifndef PF_WHATIF
+#define PF_WHATIF 0  // timing experiments only (wrong results): 1 no ex2, 2 no row max, 3 no PV MMAs, 4 softmax skeleton
+#endif
 #ifndef PF_TPR_CFG
 #define PF_TPR_CFG 1
 #endif
@@ -150,7 +153,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (elect_one_sync()) {
             const CUtensorMap* tv = use_f16 ? &tmV16 : &tmV;
             mbar_arrive_expect_tx(q_full, PF_Q_BYTES);
             tma_load_4d(q_sm, &tmQ, q_full, 0, q0, h, b);
@@ -169,20 +172,23 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (elect_one_sync()) {
             // S = Q K^T : A, B bf16, both K-major, M = 128, N = PF_BN
             constexpr uint32_t idesc_qk = make_idesc_f16(1, 1, 0, 0, PF_BM, PF_BN);
             // O += P V  : A = P (TMEM, K-major), B = V MN-major, M = 128, N = D; both f16 or both bf16
             const uint32_t idesc_pv = use_f16 ? make_idesc_f16(0, 0, 0, 1, PF_BM, PF_D) : make_idesc_f16(1, 1, 0, 1, PF_BM, PF_D);
-            const uint32_t q_addr = smem_u32(q_sm), k_addr0 = smem_u32(k_sm), v_addr0 = smem_u32(v_sm);
+            // descriptors are built once; a k-step or a ring slot only moves the start-address field (units of 16 bytes)
+            const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(q_sm), 16, 1024);
+            const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(k_sm), 16, 1024);
+            const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(v_sm), PF_KV_HALF, 1024);
             auto issue_qk = [&](int j) {  // K tile j (ring slot j % PF_SBUF) -> S buffer j % PF_SBUF
                 const int st = j % PF_SBUF;
-                const uint32_t k_addr = k_addr0 + st * PF_KV_BYTES;
+                const uint64_t k_desc = k_desc0 + (uint64_t)((st * PF_KV_BYTES) >> 4);
                 const uint32_t d_tmem = tmem_base + PF_COL_S + st * PF_BN;
 #pragma unroll
                 for (int kk = 0; kk < PF_D / 16; ++kk) {
-                    tc_mma_ss(d_tmem, make_smem_desc_sw128(q_addr + (kk >> 2) * PF_Q_HALF + (kk & 3) * 32, 16, 1024),
-                              make_smem_desc_sw128(k_addr + (kk >> 2) * PF_KV_HALF + (kk & 3) * 32, 16, 1024), idesc_qk, kk > 0);
+                    tc_mma_ss(d_tmem, q_desc0 + (uint64_t)(((kk >> 2) * PF_Q_HALF + (kk & 3) * 32) >> 4),
+                              k_desc + (uint64_t)(((kk >> 2) * PF_KV_HALF + (kk & 3) * 32) >> 4), idesc_qk, kk > 0);
                 }
                 tc_commit(s_full + st);
                 tc_commit(k_empty + st);
@@ -192,7 +198,9 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 ok = mbar_wait(k_full + t, 0, abort_flag, P.err);
                 if (ok) {
                     tc_fence_after();
+                    stamp(400 + 2 * t);
                     issue_qk(t);
+                    stamp(401 + 2 * t);
                 }
             }
             for (int j = 0; j < n_kv && ok; ++j) {
@@ -202,12 +210,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 if (!ok) break;
                 tc_fence_after();
                 if (j < 32) stamp(256 + j * 4 + 1);
-                const uint32_t v_addr = v_addr0 + st * PF_KV_BYTES;
+                const uint64_t v_desc = v_desc0 + (uint64_t)((st * PF_KV_BYTES) >> 4);
 #pragma unroll
-                for (int kk = 0; kk < PF_BN / 16; ++kk) {
+                for (int kk = 0; kk < (PF_WHATIF == 3 ? 1 : PF_BN / 16); ++kk) {
                     // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2 KB) of the V tile
                     tc_mma_ts(tmem_base + PF_COL_O, tmem_base + PF_COL_S + st * PF_BN + kk * 8,
-                              make_smem_desc_sw128(v_addr + kk * 2048, PF_KV_HALF, 1024), idesc_pv, (j > 0 || kk > 0));
+                              v_desc + (uint64_t)((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0));
                 }
                 tc_commit(v_empty + st);
                 tc_commit(pv_done);
@@ -275,7 +283,11 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             for (int i = 32; i < PF_CPT; i += 16)
 #pragma unroll
                 for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[i + 2 * a], s[i + 2 * a + 1]);
+#if PF_WHATIF == 2 || PF_WHATIF == 4
+            float pmax = s[0];
+#else
             float pmax = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+#endif
             if (PF_TPR == 2) {
                 // swap partial maxima with the thread that owns the other columns of this row
                 xch[((j & 1) * 2 + half) * 128 + row] = pmax;
@@ -299,10 +311,19 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 for (int i = 0; i < 16; i += 2) {
                     const float2 t0 = ffma2(make_float2(s[cc * 32 + 2 * i], s[cc * 32 + 2 * i + 1]), c2, nm2);
                     const float2 t1 = ffma2(make_float2(s[cc * 32 + 2 * i + 2], s[cc * 32 + 2 * i + 3]), c2, nm2);
+#if PF_WHATIF == 1
+                    const float2 p0 = t0, p1 = t1;
+#elif PF_WHATIF == 4
+                    const float2 p0 = make_float2(s[cc * 32 + 2 * i], s[cc * 32 + 2 * i + 1]);
+                    const float2 p1 = make_float2(s[cc * 32 + 2 * i + 2], s[cc * 32 + 2 * i + 3]);
+#else
                     const float2 p0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
                     const float2 p1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
+#endif
+#if PF_WHATIF != 4
                     ps0 = fadd2(ps0, p0);
                     ps1 = fadd2(ps1, p1);
+#endif
                     pk[i] = use_f16 ? pack_f16(p0.x, p0.y) : pack_bf16(p0.x, p0.y);
                     pk[i + 1] = use_f16 ? pack_f16(p1.x, p1.y) : pack_bf16(p1.x, p1.y);
                 }
