@@ -57,6 +57,7 @@ SIGNATURES = {
     "fusor_cuda_flash_attention_host": (c_int32, [c_void_p, _T4, _T4, _T4, c_float, _T2, c_int32, c_int32, _T4]),
     "fusor_cuda_flash_attention_general": (c_int32, [c_void_p, _T4, _T4, _T4, c_float, _T2, c_int32, c_int32, _T4]),
     "fusor_cuda_flash_attention_noalloc": (c_int32, [c_void_p, _T4, _T4, _T4, c_float, c_int32, _T4]),
+    "fusor_cuda_selftest_wait_limit": (c_int32, [c_void_p]),
     "fusor_cuda_prefill_probe": (c_int32, [c_void_p, _T4, _T4, _T4, c_float, c_int32, _T4, c_int32, c_void_p]),
     "fusor_cuda_kvcache_create": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                             POINTER(c_void_p)]),

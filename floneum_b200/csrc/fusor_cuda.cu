@@ -366,7 +366,7 @@ static bool tma_view_ok(const fusor_cuda_tensor4* t) {
 static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
                              const fusor_cuda_tensor4* v, float scale, int32_t mask_kind, const fusor_cuda_tensor4* out) {
     if (S.D != PF_D) return false;
-    if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL)) return false;
+    if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL || mask_kind == FUSOR_CUDA_MASK_SLIDING)) return false;
     if (!tma_view_ok(q) || !tma_view_ok(k) || !tma_view_ok(v)) return false;
     if (!(scale > 0.0f) || !std::isfinite(scale)) return false;
     const int al = out->dtype == FUSOR_CUDA_F32 ? 4 : 8;
@@ -379,7 +379,7 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
 // p_mode: 0 = f16 P with an f16 copy of V (falls back to bf16 on the device when V overflows f16), 1 = bf16 P.
 static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
                               const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
-                              const fusor_cuda_tensor4* out, float* debug, int p_mode) {
+                              const fusor_cuda_tensor4* out, float* debug, int p_mode, int window = 0) {
     CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
     TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM));
     TRY(make_tmap_bhsd(ctx, &tmK, k, PF_BN));
@@ -416,7 +416,8 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.out = out->data; P.out_dtype = out->dtype;
     for (int i = 0; i < 3; ++i) P.os[i] = out->stride[i];
     P.B = S.B; P.Hq = S.Hq; P.Hkv = S.Hkv; P.Sq = S.Sq; P.Skv = S.Skv;
-    P.causal = mask_kind == FUSOR_CUDA_MASK_CAUSAL;
+    P.causal = mask_kind == FUSOR_CUDA_MASK_CAUSAL || mask_kind == FUSOR_CUDA_MASK_SLIDING;
+    P.window = mask_kind == FUSOR_CUDA_MASK_SLIDING ? window : 0;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
     P.err = ctx->d_err;
@@ -436,7 +437,7 @@ extern "C" int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_c
     AttnShape S;
     TRY(validate_attention(ctx, q, k, v, mask, mask_kind, window, out, &S));
     DeviceGuard g(ctx->device);
-    if (prefill_eligible(S, q, k, v, scale, mask_kind, out)) return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, nullptr, 0);
+    if (prefill_eligible(S, q, k, v, scale, mask_kind, out)) return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, nullptr, 0, window);
     return launch_general(ctx, S, q, k, v, scale, mask, mask_kind, window, out);
 }
 
@@ -1048,6 +1049,29 @@ extern "C" int32_t fusor_cuda_flash_attention_decode_host(fusor_cuda_ctx* ctx, f
     return check_device_error(ctx);
 }
 
+// =============================================================================== wait-limit self test
+// One CTA waits on an mbarrier that nothing ever arrives on.  The bounded wait runs out after about a second,
+// records wait site 99 in the error word and the kernel returns normally: no trap, no endless spin.
+__global__ void wait_limit_selftest_kernel(int* err) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    mbar_wait(&bar, 0, &abort_flag, err, 99);
+}
+
+extern "C" int32_t fusor_cuda_selftest_wait_limit(fusor_cuda_ctx* ctx) {
+    if (!ctx) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "ctx is null");
+    DeviceGuard g(ctx->device);
+    wait_limit_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_err);
+    TRY(launch_check(ctx, "wait_limit_selftest_kernel"));
+    return check_device_error(ctx);
+}
+
 // =============================================================================== attention without allocation
 // Scratch for fusor_cuda_flash_attention_noalloc: a 256-byte header (word 0 = device error word, word 1 = the
 // "V does not fit f16" flag) followed by the f16 copy of V.  Every device that loads the library holds these
@@ -1079,7 +1103,7 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
     local.stream = static_cast<cudaStream_t>(stream);
     AttnShape S;
     TRY(validate_attention(&local, q, k, v, nullptr, mask_kind, 0, out, &S));
-    if (!prefill_eligible(S, q, k, v, scale, mask_kind, out))
+    if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL) || !prefill_eligible(S, q, k, v, scale, mask_kind, out))
         return fail(nullptr, FUSOR_CUDA_UNSUPPORTED,
                     "the allocation-free entry point takes bf16 q/k/v with head_dim 128, 16-byte aligned rows, "
                     "mask NONE or CAUSAL and a positive scale");
@@ -1146,6 +1170,7 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
     for (int i = 0; i < 3; ++i) P.os[i] = out->stride[i];
     P.B = S.B; P.Hq = S.Hq; P.Hkv = S.Hkv; P.Sq = S.Sq; P.Skv = S.Skv;
     P.causal = mask_kind == FUSOR_CUDA_MASK_CAUSAL;
+    P.window = 0;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
     P.err = d_err;

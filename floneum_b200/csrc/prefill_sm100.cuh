@@ -58,6 +58,7 @@ struct PrefillParams {
     long long os[3];           // element strides of batch, head, row
     int B, Hq, Hkv, Sq, Skv;
     int causal;
+    int window;                // > 0: sliding window on top of causal (key k allowed iff q + off - window < k <= q + off)
     float scale_log2;
     int n_q_tiles;
     int* err;
@@ -121,8 +122,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
     const int hk = h / (P.Hq / P.Hkv);
     const int q0 = qt * PF_BM;
     const int offset = P.Skv - P.Sq;
-    int n_kv = (P.Skv + PF_BN - 1) / PF_BN;
+    int n_kv = (P.Skv + PF_BN - 1) / PF_BN;  // becomes the number of key tiles this CTA visits, starting at tile j_begin
     if (P.causal) n_kv = min(n_kv, (q0 + PF_BM - 1 + offset) / PF_BN + 1);
+    const int j_begin = P.window > 0 ? max(0, q0 + offset - P.window + 1) / PF_BN : 0;
+    n_kv -= j_begin;
 
     if (tid == 0) {
         mbar_init(q_full, 1);
@@ -162,12 +165,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 const int st = j % PF_SBUF, use = j / PF_SBUF;
                 if (use > 0 && !mbar_wait(k_empty + st, (use - 1) & 1, abort_flag, P.err)) break;
                 mbar_arrive_expect_tx(k_full + st, PF_KV_BYTES);
-                tma_load_4d(k_sm + st * PF_KV_BYTES, &tmK, k_full + st, 0, j * PF_BN, hk, b);
-                tma_load_4d(k_sm + st * PF_KV_BYTES + PF_KV_HALF, &tmK, k_full + st, 64, j * PF_BN, hk, b);
+                tma_load_4d(k_sm + st * PF_KV_BYTES, &tmK, k_full + st, 0, (j_begin + j) * PF_BN, hk, b);
+                tma_load_4d(k_sm + st * PF_KV_BYTES + PF_KV_HALF, &tmK, k_full + st, 64, (j_begin + j) * PF_BN, hk, b);
                 if (use > 0 && !mbar_wait(v_empty + st, (use - 1) & 1, abort_flag, P.err)) break;
                 mbar_arrive_expect_tx(v_full + st, PF_KV_BYTES);
-                tma_load_4d(v_sm + st * PF_KV_BYTES, tv, v_full + st, 0, j * PF_BN, hk, b);
-                tma_load_4d(v_sm + st * PF_KV_BYTES + PF_KV_HALF, tv, v_full + st, 64, j * PF_BN, hk, b);
+                tma_load_4d(v_sm + st * PF_KV_BYTES, tv, v_full + st, 0, (j_begin + j) * PF_BN, hk, b);
+                tma_load_4d(v_sm + st * PF_KV_BYTES + PF_KV_HALF, tv, v_full + st, 64, (j_begin + j) * PF_BN, hk, b);
             }
         }
     } else if (warp == 1) {
@@ -240,6 +243,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;  // this warp's TMEM lane quadrant
         const int qi = q0 + row;
         const int k_limit = P.causal ? min(P.Skv - 1, qi + offset) : P.Skv - 1;  // last key this row may see
+        const int k_first = P.window > 0 ? qi + offset - P.window + 1 : 0;      // first key this row may see
         const float c = P.scale_log2;
         constexpr int OC = 128 / PF_TPR;  // output columns per thread
         const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O + half * OC;
@@ -268,11 +272,11 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
 #pragma unroll
                 for (int i = 0; i < PF_CPT; ++i) P.debug[row * PF_DEBUG_ROW + half * PF_CPT + i] = s[i];
             }
-            const int k0 = j * PF_BN + half * PF_CPT;
-            if (k0 + PF_CPT - 1 > k_limit) {  // diagonal or ragged tile: mask in the raw domain
+            const int k0 = (j_begin + j) * PF_BN + half * PF_CPT;
+            if (k0 + PF_CPT - 1 > k_limit || k0 < k_first) {  // diagonal, ragged or window-edge tile: mask in the raw domain
 #pragma unroll
                 for (int i = 0; i < PF_CPT; ++i)
-                    if (k0 + i > k_limit) s[i] = -INFINITY;
+                    if (k0 + i > k_limit || k0 + i < k_first) s[i] = -INFINITY;
             }
             float mx[8];
 #pragma unroll
@@ -299,10 +303,13 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             const float tmax = pmax * c;  // scale > 0
             // lazy rescale: keep the reference max until the true max has moved by more than the threshold
             const float m_new = (tmax > m_ref + PF_RESCALE_THRESHOLD) ? tmax : m_ref;  // also taken on the first tile
-            const float alpha = fast_exp2(m_ref - m_new);                              // 1 when unchanged, 0 on the first tile
+            // A row whose keys so far are all outside its window keeps m = -inf: its weights are exp2(-inf - 0) = 0
+            // and its O row stays 0, without a NaN from (-inf) - (-inf).
+            const float alpha = (m_new == -INFINITY) ? 1.0f : fast_exp2(m_ref - m_new);  // 1 when unchanged, 0 on a row's first tile
             m_ref = m_new;
             if (tr && j < 32) stamp(j * 8 + 3);
-            const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_ref, -m_ref);
+            const float m_sub = (m_ref == -INFINITY) ? 0.0f : m_ref;
+            const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_sub, -m_sub);
             float2 ps0 = make_float2(0.0f, 0.0f), ps1 = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int cc = 0; cc < PF_CPT / 32; ++cc) {

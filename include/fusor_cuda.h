@@ -146,6 +146,12 @@ int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_cuda_tensor
                                            const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
                                            const fusor_cuda_tensor4* out);
 
+/* Self test of the failure path (no reference counterpart): launches one warp that waits on a barrier nothing
+ * ever signals.  The wait is bounded (about a second); the kernel then returns by itself and the call reports
+ * FUSOR_CUDA_TIMEOUT with wait site 99.  The context stays usable: this is how a lost producer / consumer inside
+ * the attention kernels surfaces, instead of a hang. */
+int32_t fusor_cuda_selftest_wait_limit(fusor_cuda_ctx* ctx);
+
 /* Diagnostic (no reference counterpart): runs the tensor-core prefill kernel with the softmax weights kept as f16 against an
  * f16 copy of V (p_format 0, the production setting) or as bf16 against the bf16 V (p_format 1) and copies out of the first CTA, into debug_device (f32, 128*258 + 512 values), per row the raw scores of its
  * first key tile [0,128), its un-normalised O [128,256), the running max in log2 units [256] and the row sum [257],

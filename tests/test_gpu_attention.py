@@ -204,6 +204,20 @@ def test_prefill_tensor_core_shapes(device, B, Hq, Hkv, Sq, Skv, causal):
     assert_close(got, want, what=f"prefill {B}x{Hq}/{Hkv}x{Sq}/{Skv} causal={causal}")
 
 
+@pytest.mark.parametrize("Sq,off,w", [(300, 0, 64), (300, 0, 7), (256, 0, 128), (200, 56, 256), (513, 0, 200), (130, 0, 1000)])
+def test_prefill_sliding_window_tensor_core(device, Sq, off, w):
+    """Sliding-window masks from MaskCache run analytically in the tcgen05 kernel (tiles left of the window are skipped,
+    rows whose first visited tile is entirely outside their window stay exact)."""
+    fb = _mods()
+    eff_off = min(off, max(w - Sq, 0))
+    Skv = Sq + eff_off
+    q, k, v, scale = _bf16_case(7 * Sq + w, 1, 4, 2, Sq, Skv)
+    m = fb.MaskCache().get_mask(Sq, off, w, device)
+    got = _run(device, q, k, v, scale, (m, fb.MaskKind.QKMask), dtype=1)
+    want = O.flash_attention(q, k, v, scale, O.get_mask(Sq, off, w), O.MASK_QK)
+    assert_close(got, want, what=f"sliding window {Sq},{off},{w}")
+
+
 def test_prefill_golden_fixture(device):
     fb = _mods()
     z = np.load(__file__.replace("test_gpu_attention.py", "golden/seeded_bf16_d128_causal.npz"))

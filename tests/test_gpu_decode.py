@@ -198,3 +198,20 @@ def test_cfg3_full_size(device):
     cache = _install(device, w)
     got = cache.decode(fb.Tensor.from_slice(device, w.q.shape, w.q, 1), w.scale).as_slice()
     assert_close(got, _oracle_decode(w), what="cfg3 full")
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(device):
+    """Failure detection without a GPU fault: a wait on a barrier nothing signals runs out (about a second), the
+    kernel returns, the host sees TIMEOUT, and the same context computes correctly afterwards."""
+    import ctypes
+    fb = _fb()
+    from floneum_b200 import _lib
+    L = _lib.load()
+    rc = L.fusor_cuda_selftest_wait_limit(device.handle)
+    assert rc == _lib.TIMEOUT
+    assert b"wait site 99" in L.fusor_cuda_last_error(device.handle)
+    device.synchronize()  # the error word was cleared; the stream is healthy
+    q = np.ones((1, 2, 4, 16), np.float32)
+    out = fb.Tensor.from_slice(device, q.shape, q).flash_attention(fb.Tensor.from_slice(device, q.shape, q),
+                                                                   fb.Tensor.from_slice(device, q.shape, q), 0.25).as_slice()
+    assert np.allclose(out, 1.0, atol=1e-6)
