@@ -190,6 +190,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the decode line and the CPU baseline")
     ap.add_argument("--shard-of", type=int, default=0, help="for profiler captures on one GPU: run rank 0's shard of an "
                     "N-rank job (no process group; the line is marked as a shard)")
+    ap.add_argument("--no-graph", action="store_true", help="decode workloads: time eager launches instead of a CUDA graph replay")
     ap.add_argument("--quick", action="store_true", help="for profiler captures: no clock-settling loop, no e2e, no extras")
     ap.add_argument("--small", action="store_true", help="for profiler captures: a scaled-down case of the workload "
                     "(prefill B2 Hq16 Hkv4 S4096; decode B16)")
@@ -207,6 +208,7 @@ def main():
     import torch.distributed as dist
     import floneum_b200 as fb
     from floneum_b200 import _lib, sharding, workloads as W
+    from floneum_b200.cache import lse_combine
     L = _lib.load()
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -360,9 +362,19 @@ def main():
         kv_bytes_rank = float(np.sum(w.kv_len)) * 2 * (k1 - k0) * D * 2
         flush = torch.empty(int(300e6), dtype=torch.uint8, device=cuda) if kv_bytes_rank < 400e6 else None
 
+        if chunked and use_dist:
+            # fixed buffers so that the step can be captured in a CUDA graph
+            part = torch.empty((B, q1 - q0, D + 2), dtype=torch.float32, device=cuda)
+            gathered = torch.empty((world, B, q1 - q0, D + 2), dtype=torch.float32, device=cuda)
+            out3 = torch.empty((B, q1 - q0, D), dtype=torch.float32, device=cuda)
+            tpart, tgath, tout3 = (fb.Tensor.from_torch(dev, t) for t in (part, gathered, out3))
+
         def step():
             if chunked and use_dist:
-                return sharding.decode_kv_chunks(dev, cache, tq, w.scale)
+                cache.decode_partial(tq, w.scale, tpart)
+                dist.all_gather_into_tensor(gathered, part)
+                lse_combine(dev, tgath, tout3)
+                return out3
             cache.decode(tq, w.scale, to)
             return out
         with torch.cuda.stream(stream):
@@ -371,6 +383,20 @@ def main():
                     flush.zero_()
                 res = step()
             barrier()
+            # A decode step is launch-bound at small shard sizes: capture it once in a CUDA graph and replay it.
+            graph = None
+            if not args.no_graph and not args.quick:
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        res = step()
+                    graph.replay()
+                    torch.cuda.synchronize()
+                except Exception as e:  # capture is an optimisation only
+                    sys.stderr.write(f"CUDA graph capture failed ({e}); timing eager launches\n")
+                    graph = None
+                    torch.cuda.synchronize()
+            barrier()
             launches0 = dev.launch_count()
             evs = []
             for _ in range(args.steps):
@@ -378,11 +404,16 @@ def main():
                     flush.zero_()  # write a buffer larger than L2 between timed launches
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(stream)
-                res = step()
+                if graph is not None:
+                    graph.replay()
+                else:
+                    res = step()
                 b.record(stream)
                 evs.append((a, b))
             barrier()
             launches = dev.launch_count() - launches0
+            if graph is not None:
+                launches = args.steps * (3 if (chunked and use_dist) else 2)  # kernels of ours inside each replay
             dev.synchronize()
         ms = [a.elapsed_time(b) for a, b in evs]
         mean_ms = max_over_ranks(statistics.mean(ms))
@@ -413,6 +444,7 @@ def main():
                              "frac_of_nominal_8000": achieved / 8000.0},
                 "config": {"workload": f"{tag}: paged GQA decode B{B} Hq{Hq} Hkv{Hkv_all} D{D}, 16-token pages, "
                            f"kv tokens {int(np.sum(w.kv_len))}", "bytes_per_step": bytes_all,
+                           "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
                            "l2": "KV working set exceeds L2" if flush is None else "300 MB buffer written between timed launches"},
                 "_got": (res if isinstance(res, torch.Tensor) else out).cpu().numpy(), "_q": qn, "_krange": (k0, k1)}
 

@@ -287,3 +287,43 @@ int oracle_attention_partial_f32(const float* q, const float* k, const float* v,
     }
     return 0;
 }
+
+/*
+ * Rotary position embedding as the reference's CPU composites compute it, f32, contiguous [B,H,S,D]:
+ *   interleaved = 0: Tensor::rope            (fusor-ml/fusor/src/composite/rope.rs:38-68, rotate_half :8-19):
+ *                    out = x * cos + rotate_half(x) * sin, halves (i, i + D/2) share cos/sin[pos][i]
+ *   interleaved = 1: Tensor::rope_interleaved (rope.rs:70-118): pairs (2i, 2i+1):
+ *                    y0 = x0 * c - x1 * s,  y1 = x0 * s + x1 * c
+ * cos, sin: [context_length][D/2]; row start_pos + t is used for sequence position t
+ * (RopeCache::forward narrows the tables at start_pos, rope.rs:232-246).
+ * Each product is rounded before the add / subtract (separate mul_ and add_ ops): contraction is switched off.
+ */
+__attribute__((optimize("fp-contract=off"))) int oracle_rope_f32(const float* x, const float* cos_t, const float* sin_t,
+                                                                 float* out, int B, int H, int S, int D, int start_pos,
+                                                                 int interleaved) {
+    if (D % 2 != 0) return -1;
+    const int half = D / 2;
+    for (long long bh = 0; bh < (long long)B * H; ++bh)
+        for (int t = 0; t < S; ++t) {
+            const float* xr = x + ((size_t)bh * S + t) * D;
+            float* orow = out + ((size_t)bh * S + t) * D;
+            const float* c = cos_t + (size_t)(start_pos + t) * half;
+            const float* s = sin_t + (size_t)(start_pos + t) * half;
+            for (int i = 0; i < half; ++i) {
+                if (interleaved) {
+                    const float x0 = xr[2 * i], x1 = xr[2 * i + 1];
+                    const float a = x0 * c[i], b = x1 * s[i];
+                    const float e = x0 * s[i], f = x1 * c[i];
+                    orow[2 * i] = a - b;
+                    orow[2 * i + 1] = e + f;
+                } else {
+                    const float x1 = xr[i], x2 = xr[i + half];
+                    const float a = x1 * c[i], b = (-x2) * s[i];
+                    const float e = x2 * c[i], f = x1 * s[i];
+                    orow[i] = a + b;
+                    orow[i + half] = e + f;
+                }
+            }
+        }
+    return 0;
+}

@@ -58,6 +58,8 @@ def lib():
                                                                                         ctypes.c_int]
         L.oracle_attention_partial_f32.restype = ctypes.c_int
         L.oracle_num_threads.restype = ctypes.c_int
+        L.oracle_rope_f32.argtypes = [fp, fp, fp, fp] + [ctypes.c_int] * 6
+        L.oracle_rope_f32.restype = ctypes.c_int
         _lib = L
     return _lib
 
@@ -170,6 +172,26 @@ def lse_combine(parts) -> np.ndarray:
     n_rows = int(np.prod(parts.shape[1:-1]))
     out = np.empty(parts.shape[1:-1] + (D,), np.float32)
     lib().oracle_lse_combine(_p(parts), P, n_rows, D, _p(out))
+    return out
+
+
+# --------------------------------------------------------------------------- rotary embedding (next-row F2)
+def rope_tables(head_dim: int, context_length: int, rope_theta: float = 10000.0):
+    """RopeCache::new (fusor-ml/fusor/src/composite/rope.rs:186-219): cos, sin [context_length, head_dim/2] in f32."""
+    inv = np.array([1.0 / np.float32(rope_theta) ** (np.float32(i) / np.float32(head_dim)) for i in range(0, head_dim, 2)],
+                   dtype=np.float32)
+    outer = np.arange(context_length, dtype=np.float32)[:, None] * inv[None, :]
+    return np.cos(outer).astype(np.float32), np.sin(outer).astype(np.float32)
+
+
+def rope(x, cos, sin, start_pos: int = 0, interleaved: bool = False) -> np.ndarray:
+    """Tensor::rope / rope_interleaved on f32 [B,H,S,D] with table rows start_pos .. start_pos+S."""
+    x, cos, sin = _f32(x), _f32(cos), _f32(sin)
+    B, H, S, D = x.shape
+    assert cos.shape == sin.shape and cos.shape[1] == D // 2 and start_pos + S <= cos.shape[0]
+    out = np.empty_like(x)
+    rc = lib().oracle_rope_f32(_p(x), _p(cos), _p(sin), _p(out), B, H, S, D, int(start_pos), int(bool(interleaved)))
+    assert rc == 0
     return out
 
 
