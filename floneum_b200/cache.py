@@ -141,6 +141,20 @@ class PagedKvCache:
         ck, cv = k_new._c4(), v_new._c4()
         self._ck(self._L.fusor_cuda_kvcache_append(self._h, ctypes.byref(ck), ctypes.byref(cv)))
 
+    def rope_append(self, q: Tensor, k_new: Tensor, v_new: Tensor, cos: Tensor, sin: Tensor, start_pos: int = -1,
+                    interleaved: bool = False, out_dtype: Optional[int] = None) -> Tensor:
+        """RoPE of q and k_new plus the append of (rotated k, v) in one kernel; returns rotated q.
+
+        cos, sin: f32 device tensors [context, D/2].  start_pos < 0: each sequence's own length."""
+        assert tuple(cos.shape()) == tuple(sin.shape()) and cos.shape()[1] == self.head_dim // 2
+        assert cos.dtype == F32 and sin.dtype == F32 and cos.is_contiguous() and sin.is_contiguous()
+        q_out = Tensor.empty(self.device, q.shape(), q.dtype if out_dtype is None else out_dtype)
+        cq, ck, cv, co = q._c4(), k_new._c4(), v_new._c4(), q_out._c4()
+        self._ck(self._L.fusor_cuda_kvcache_rope_append(self._h, ctypes.byref(cq), ctypes.byref(ck), ctypes.byref(cv),
+                                                        cos.ptr, sin.ptr, cos.shape()[0], int(start_pos),
+                                                        int(bool(interleaved)), ctypes.byref(co)))
+        return q_out
+
     def truncate_front(self, b: int, keep: int):
         self._ck(self._L.fusor_cuda_kvcache_truncate_front(self._h, b, keep))
 
@@ -287,7 +301,9 @@ class KvCache:
     def v(self) -> Optional[CachedKv]:
         return CachedKv(self, "v") if self.current_seq_len() else None
 
-    def append(self, device: Device, k: Tensor, v: Tensor) -> Tuple[CachedKv, CachedKv]:
+    def _make_room(self, device: Device, k: Tensor, v: Tensor):
+        """Allocation on first use and the eviction rule of TensorCache::append; returns (k, v, rows dropped from the
+        front of the new tensors)."""
         B, Hkv, n, D = k.shape()
         assert tuple(v.shape()) == (B, Hkv, n, D), "k and v shapes differ"
         if self._paged is None or B > self._paged.max_batch or (self._num_kv_heads, self._head_dim) != (Hkv, D):
@@ -295,6 +311,7 @@ class KvCache:
             self._paged = PagedKvCache(device, B, Hkv, D, B * pages_per_seq, pages_per_seq)
             self._num_kv_heads, self._head_dim = Hkv, D
         mx = self.max_sequence_len
+        skip = 0
         if n >= mx:  # only the newest max_sequence_len rows survive
             self._paged.reset()
             skip = n - mx
@@ -303,9 +320,30 @@ class KvCache:
         elif self.current_seq_len() + n > mx:
             for b in range(B):
                 self._paged.truncate_front(b, mx - n)
+        return k, v, skip
+
+    def append(self, device: Device, k: Tensor, v: Tensor) -> Tuple[CachedKv, CachedKv]:
+        k, v, _ = self._make_room(device, k, v)
         self._paged.append(k, v)
-        self._batch = B
+        self._batch = k.shape()[0]
         return CachedKv(self, "k"), CachedKv(self, "v")
+
+    def _append_rotated(self, rope_cache, q: Tensor, k: Tensor, v: Tensor, start_pos: int, interleaved: bool, out_dtype):
+        """`RopeCache.forward(q, k, start_pos)` then `append(k, v)` in one launch (see RopeCache.forward_append)."""
+        if start_pos < 0:
+            start_pos = self.current_seq_len()
+        n = k.shape()[2]
+        k2, v2, skip = self._make_room(q.device, k, v)
+        if skip:  # the rows that do not survive still rotate q; do that with the plain op and append the rest
+            from .rope import rope
+            q_rot = rope(q, rope_cache.cos, rope_cache.sin, start_pos, interleaved, out_dtype)
+            dummy = Tensor(q.device, q.ptr + skip * q.strides[2] * (4 if q.dtype == F32 else 2),
+                           (q.shape()[0], q.shape()[1], n - skip, q.shape()[3]), q.dtype, q.strides, owner=q)
+            self._paged.rope_append(dummy, k2, v2, rope_cache.cos, rope_cache.sin, start_pos + skip, interleaved, out_dtype)
+        else:
+            q_rot = self._paged.rope_append(q, k2, v2, rope_cache.cos, rope_cache.sin, start_pos, interleaved, out_dtype)
+        self._batch = k.shape()[0]
+        return q_rot, CachedKv(self, "k"), CachedKv(self, "v")
 
     def _dense(self, dtype: int) -> Tuple[Tensor, Tensor]:
         return self._paged.gather(self._batch, self.current_seq_len(), dtype)

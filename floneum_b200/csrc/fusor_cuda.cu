@@ -19,6 +19,7 @@
 #include "decode_splitkv.cuh"
 #include "general_attention.cuh"
 #include "prefill_sm100.cuh"
+#include "rope_append.cuh"
 
 using namespace fusor;
 
@@ -661,9 +662,9 @@ static int32_t kv_sync_tables(fusor_cuda_kvcache* c) {
     return FUSOR_CUDA_OK;
 }
 
-extern "C" int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* k_new,
-                                             const fusor_cuda_tensor4* v_new) {
-    if (!c || !k_new || !v_new || !k_new->data || !v_new->data) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+// Argument checks shared by the append entry points, then page allocation on the host: takes pages from the free list
+// for n more tokens per sequence, bumps the lengths and uploads the tables plus each sequence's previous length.
+static int32_t kv_reserve(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* k_new, const fusor_cuda_tensor4* v_new) {
     fusor_cuda_ctx* ctx = c->ctx;
     if (!dtype_ok(k_new->dtype) || !dtype_ok(v_new->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
     for (int i = 0; i < 4; ++i)
@@ -677,7 +678,6 @@ extern "C" int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* c, const fusor_
     if (k_new->stride[3] != 1 || v_new->stride[3] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the head_dim axis must be contiguous");
     if (c->active_B != 0 && c->active_B != B)
         return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "cache holds %d sequences, append brings %d", c->active_B, B);
-    // page allocation on the host
     int need = 0;
     for (int b = 0; b < B; ++b) {
         const int have = (c->h_kv_len[b] + DEC_PT - 1) / DEC_PT, want = (c->h_kv_len[b] + n + DEC_PT - 1) / DEC_PT;
@@ -701,7 +701,16 @@ extern "C" int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* c, const fusor_
     c->table_dirty = true;
     c->plan_dirty = true;
     CUDA_TRY(ctx, cudaMemcpyAsync(c->d_len_before, before.data(), (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
-    TRY(kv_sync_tables(c));
+    return kv_sync_tables(c);
+}
+
+extern "C" int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* k_new,
+                                             const fusor_cuda_tensor4* v_new) {
+    if (!c || !k_new || !v_new || !k_new->data || !v_new->data) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    fusor_cuda_ctx* ctx = c->ctx;
+    TRY(kv_reserve(c, k_new, v_new));
+    DeviceGuard g(ctx->device);
+    const int B = (int)k_new->shape[0], n = (int)k_new->shape[2];
     AppendParams P;
     P.k_new = k_new->data; P.v_new = v_new->data; P.k_dtype = k_new->dtype; P.v_dtype = v_new->dtype;
     for (int i = 0; i < 3; ++i) { P.ks[i] = k_new->stride[i]; P.vs[i] = v_new->stride[i]; }
@@ -711,6 +720,93 @@ extern "C" int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* c, const fusor_
     const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
     kvcache_append_kernel<<<blocks, 256, 0, ctx->stream>>>(P);
     return launch_check(ctx, "kvcache_append_kernel");
+}
+
+// ------------------------------------------------------------------------------------------------ rotary embedding
+static int32_t rope_check(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* x, const fusor_cuda_tensor4* out, const float* cos_t,
+                          const float* sin_t, int32_t context_length, const char* what) {
+    if (!x || !out || !x->data || !out->data || !cos_t || !sin_t) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (!dtype_ok(x->dtype) || !dtype_ok(out->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    for (int i = 0; i < 4; ++i) {
+        if (x->shape[i] <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "%s has an empty axis", what);
+        if (x->shape[i] != out->shape[i]) return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "%s and its output differ in shape", what);
+    }
+    if (x->shape[3] % 2 != 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "head_dim %lld must be even for rope", (long long)x->shape[3]);
+    if (x->stride[3] != 1 || out->stride[3] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the head_dim axis must be contiguous");
+    if (context_length <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "context_length must be positive");
+    return FUSOR_CUDA_OK;
+}
+
+static bool rope_vec_ok(const void* p, int dtype, const long long* stride) {
+    const long long per16 = dtype == FUSOR_CUDA_F32 ? 4 : 8;  // elements per 16 bytes
+    if (reinterpret_cast<uintptr_t>(p) % 16 != 0) return false;
+    for (int i = 0; i < 3; ++i)
+        if (stride[i] % per16 != 0) return false;
+    return true;
+}
+
+// Picks the 8-pairs-per-thread kernel when every tensor allows 16-byte accesses, else the scalar one.
+static int32_t rope_launch(fusor_cuda_ctx* ctx, const RopeParams& P) {
+    const int heads = P.Hq + (P.k_pages ? P.Hkv : 0);
+    bool vec = P.D % 16 == 0 && reinterpret_cast<uintptr_t>(P.cos_t) % 16 == 0 && reinterpret_cast<uintptr_t>(P.sin_t) % 16 == 0 &&
+               rope_vec_ok(P.q, P.q_dtype, P.qs) && rope_vec_ok(P.q_out, P.qo_dtype, P.qos);
+    if (vec && P.k_pages) vec = rope_vec_ok(P.k_new, P.k_dtype, P.ks) && rope_vec_ok(P.v_new, P.v_dtype, P.vs);
+    const long long pairs = (long long)P.B * heads * P.n * (P.D / 2);
+    const long long threads = vec ? pairs / 8 : pairs;
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((threads + 255) / 256, (long long)ctx->num_sms * 16));
+    if (!vec) rope_append_kernel<<<blocks, 256, 0, ctx->stream>>>(P);
+    else if (P.interleaved) rope_append_vec_kernel<true><<<blocks, 256, 0, ctx->stream>>>(P);
+    else rope_append_vec_kernel<false><<<blocks, 256, 0, ctx->stream>>>(P);
+    return launch_check(ctx, "rope_append_kernel");
+}
+
+extern "C" int32_t fusor_cuda_rope(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* x, const float* cos_t, const float* sin_t,
+                                   int32_t context_length, int32_t start_pos, int32_t interleaved,
+                                   const fusor_cuda_tensor4* out) {
+    if (!ctx) return FUSOR_CUDA_INVALID_ARGUMENT;
+    TRY(rope_check(ctx, x, out, cos_t, sin_t, context_length, "x"));
+    const int B = (int)x->shape[0], H = (int)x->shape[1], n = (int)x->shape[2], D = (int)x->shape[3];
+    if (start_pos < 0 || (long long)start_pos + n > context_length)
+        return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "positions %d..%lld are outside the %d-row cos/sin tables", start_pos,
+                    (long long)start_pos + n, context_length);
+    DeviceGuard g(ctx->device);
+    RopeParams P{};
+    P.q = x->data; P.q_out = out->data; P.q_dtype = x->dtype; P.qo_dtype = out->dtype; P.Hq = H;
+    for (int i = 0; i < 3; ++i) { P.qs[i] = x->stride[i]; P.qos[i] = out->stride[i]; }
+    P.cos_t = cos_t; P.sin_t = sin_t; P.B = B; P.n = n; P.D = D; P.start_pos = start_pos; P.interleaved = interleaved ? 1 : 0;
+    return rope_launch(ctx, P);
+}
+
+extern "C" int32_t fusor_cuda_kvcache_rope_append(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* q,
+                                                  const fusor_cuda_tensor4* k_new, const fusor_cuda_tensor4* v_new,
+                                                  const float* cos_t, const float* sin_t, int32_t context_length,
+                                                  int32_t start_pos, int32_t interleaved, const fusor_cuda_tensor4* q_out) {
+    if (!c || !k_new || !v_new || !k_new->data || !v_new->data) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    fusor_cuda_ctx* ctx = c->ctx;
+    TRY(rope_check(ctx, q, q_out, cos_t, sin_t, context_length, "q"));
+    const int B = (int)k_new->shape[0], n = (int)k_new->shape[2];
+    if (q->shape[0] != B || q->shape[2] != n || q->shape[3] != c->D)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "q is [%lld,%lld,%lld,%lld]; k_new brings batch %d, %d tokens, cache head_dim %d",
+                    (long long)q->shape[0], (long long)q->shape[1], (long long)q->shape[2], (long long)q->shape[3], B, n, c->D);
+    // highest table row any sequence reads
+    long long last = (long long)start_pos + n;
+    if (start_pos < 0) {
+        last = 0;
+        for (int b = 0; b < B && b < c->max_batch; ++b) last = std::max<long long>(last, (long long)c->h_kv_len[b] + n);
+    }
+    if (last > context_length)
+        return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "positions up to %lld are outside the %d-row cos/sin tables", last, context_length);
+    TRY(kv_reserve(c, k_new, v_new));
+    DeviceGuard g(ctx->device);
+    RopeParams P{};
+    P.q = q->data; P.q_out = q_out->data; P.q_dtype = q->dtype; P.qo_dtype = q_out->dtype; P.Hq = (int)q->shape[1];
+    for (int i = 0; i < 3; ++i) { P.qs[i] = q->stride[i]; P.qos[i] = q_out->stride[i]; P.ks[i] = k_new->stride[i]; P.vs[i] = v_new->stride[i]; }
+    P.k_new = k_new->data; P.v_new = v_new->data; P.k_dtype = k_new->dtype; P.v_dtype = v_new->dtype;
+    P.k_pages = c->k_pages; P.v_pages = c->v_pages; P.page_table = c->d_page_table; P.len_before = c->d_len_before;
+    P.max_pages = c->max_pages; P.Hkv = c->Hkv;
+    P.cos_t = cos_t; P.sin_t = sin_t; P.B = B; P.n = n; P.D = c->D; P.start_pos = start_pos < 0 ? -1 : start_pos;
+    P.interleaved = interleaved ? 1 : 0;
+    return rope_launch(ctx, P);
 }
 
 extern "C" int32_t fusor_cuda_kvcache_seq_len(fusor_cuda_kvcache* c, int32_t b, int32_t* len) {

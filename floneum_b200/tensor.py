@@ -153,6 +153,20 @@ class Tensor:
             t.stride[i] = self.strides[i]
         return t
 
+    # ------------------------------------------------------------------ rotary embedding
+    def rope(self, cos: "Tensor", sin: "Tensor") -> "Tensor":
+        """Tensor::rope (fusor-ml/fusor/src/composite/rope.rs:38-68): halves (i, i + D/2); cos/sin [seq, D/2]."""
+        from .rope import rope
+        return rope(self, cos, sin, 0, False)
+
+    def rope_interleaved(self, cos: "Tensor", sin: "Tensor") -> "Tensor":
+        """Tensor::rope_interleaved (rope.rs:70-118): adjacent pairs (2i, 2i+1)."""
+        from .rope import rope
+        return rope(self, cos, sin, 0, True)
+
+    rope_normal_fused = rope          # rope.rs:158-175
+    rope_fused = rope_interleaved     # rope.rs:140-156
+
     # ------------------------------------------------------------------ the operator
     def flash_attention(self, k, v, scale: float, mask=None, out_dtype: int = F32) -> "Tensor":
         """softmax(q k^T * scale + mask) v with GQA; self is q [B,Hq,Sq,D].

@@ -180,6 +180,24 @@ int32_t fusor_cuda_kvcache_reset(fusor_cuda_kvcache* cache);
  * 0..B-1; pages are taken from the free list as needed.  Sets the active batch to B. */
 int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* k_new,
                                   const fusor_cuda_tensor4* v_new);
+/* Rotary position embedding: Tensor::rope (interleaved = 0) and Tensor::rope_interleaved (interleaved = 1)
+ * (fusor-ml/fusor/src/composite/rope.rs:38-118; the fused entries Tensor::rope_fused / rope_normal_fused, rope.rs:140-175, and the llama
+ * call site models/kalosm-llama/src/raw/rope.rs:86-111).  x, out [B,H,n,D] (f32 or bf16, device, contiguous head_dim
+ * axis, D even); cos, sin: device f32 [context_length][D/2] as RopeCache::new builds them (rope.rs:186-219); token t
+ * uses table row start_pos + t (RopeCache::forward narrows the tables there, rope.rs:232-246).  Each product is
+ * rounded before the add, as the separate mul / add ops of the composite do: f32 results are bit-identical to it. */
+int32_t fusor_cuda_rope(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* x, const float* cos, const float* sin,
+                        int32_t context_length, int32_t start_pos, int32_t interleaved, const fusor_cuda_tensor4* out);
+/* RopeCache::forward / forward_interleaved on (q, k) followed by KvCache::append(k_rotated, v) in one kernel
+ * (call order of the attention layer, models/kalosm-llama/src/raw/attention_layer.rs:382-408: rope, then cache
+ * append, then attention).  q [B,Hq,n,D] -> q_out (same shape, f32 or bf16); k_new is rotated in f32 and rounded once into the
+ * bf16 pages, v_new is copied into the pages; rotated K never exists as a separate tensor.  start_pos >= 0 is the
+ * reference's scalar index_pos; start_pos < 0 takes each sequence's cache length before the append as its position
+ * (ragged batches).  Checks and page allocation are those of fusor_cuda_kvcache_append. */
+int32_t fusor_cuda_kvcache_rope_append(fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
+                                       const fusor_cuda_tensor4* k_new, const fusor_cuda_tensor4* v_new, const float* cos,
+                                       const float* sin, int32_t context_length, int32_t start_pos, int32_t interleaved,
+                                       const fusor_cuda_tensor4* q_out);
 /* TensorCache eviction (tensor_cache.rs:55-78): keep only the newest `keep` tokens of sequence b. */
 int32_t fusor_cuda_kvcache_truncate_front(fusor_cuda_kvcache* cache, int32_t b, int32_t keep);
 /* KvCache::current_seq_len (kv_cache.rs:65-67) of sequence b. */

@@ -196,3 +196,40 @@ def test_golden_fixture(name):
     mask = z["mask"] if kind in (O.MASK_QK, O.MASK_BATCH_KEY) else None
     out = O.flash_attention(z["q"], z["k"], z["v"], float(z["scale"]), mask, kind)
     assert np.array_equal(out, z["out"]) or np.abs(out - z["out"]).max() < 1e-6
+
+
+# --------------------------------------------------------------------------- rotary embedding
+def test_rope_reference_inputs_shape_and_finite():
+    """fusor-ml/fusor/src/composite/rope.rs:272-352: [1,3,11,64] of sin(i % 64), RopeCache::new(64, 11, 10000)."""
+    x = np.sin((np.arange(3 * 11 * 64) % 64).astype(np.float32)).astype(np.float32).reshape(1, 3, 11, 64)
+    cos, sin = O.rope_tables(64, 11, 10000.0)
+    assert cos.shape == (11, 32) and sin.shape == (11, 32)
+    for interleaved in (False, True):
+        y = O.rope(x, cos, sin, 0, interleaved)
+        assert y.shape == (1, 3, 11, 64) and np.isfinite(y).all()
+        # position 0 has cos = 1, sin = 0: the row is unchanged
+        assert np.array_equal(y[:, :, 0], x[:, :, 0])
+
+
+def test_rope_hand_computed_pairs():
+    """A quarter turn: cos = 0, sin = 1 sends (a, b) to (-b, a) in both pairings (rope.rs:8-19, 52-67, 96-117)."""
+    x = np.array([1.0, 2.0, 3.0, 4.0], np.float32).reshape(1, 1, 1, 4)
+    cos = np.zeros((1, 2), np.float32)
+    sin = np.ones((1, 2), np.float32)
+    assert O.rope(x, cos, sin, 0, False).ravel().tolist() == [-3.0, -4.0, 1.0, 2.0]   # pairs (0,2), (1,3)
+    assert O.rope(x, cos, sin, 0, True).ravel().tolist() == [-2.0, 1.0, -4.0, 3.0]    # pairs (0,1), (2,3)
+    # general angle, against the closed form in float64
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((2, 2, 5, 8)).astype(np.float32)
+    cos, sin = O.rope_tables(8, 16, 10000.0)
+    y = O.rope(x, cos, sin, 7, False).astype(np.float64)
+    c, s = cos[7:12].astype(np.float64), sin[7:12].astype(np.float64)
+    want = np.concatenate([x[..., :4] * c - x[..., 4:] * s, x[..., 4:] * c + x[..., :4] * s], axis=-1)
+    np.testing.assert_allclose(y, want, atol=1e-6)
+
+
+def test_rope_inverse_frequency():
+    """base_inverse_frequency (rope.rs:189-194): 1 / theta^(i/dim), i = 0, 2, .."""
+    cos, sin = O.rope_tables(4, 2, 10000.0)
+    np.testing.assert_allclose(cos[1], np.cos([1.0, 0.01]), rtol=1e-6)
+    np.testing.assert_allclose(sin[1], np.sin([1.0, 0.01]), rtol=1e-6)
