@@ -10,6 +10,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -19,6 +20,7 @@
 #include "decode_splitkv.cuh"
 #include "general_attention.cuh"
 #include "prefill_sm100.cuh"
+#include "prefill2_sm100.cuh"
 #include "rope_append.cuh"
 
 using namespace fusor;
@@ -43,6 +45,7 @@ struct fusor_cuda_ctx {
     size_t v16_bytes = 0;
     int* d_flags = nullptr;  // [256]
     unsigned flag_counter = 0;
+    int prefill_variant = 0;  // 0 = pick by shape, 1 = always the 64-key kernel (set from FUSOR_CUDA_PREFILL_VARIANT, for A/B timing)
 };
 
 static thread_local std::string g_last_error;
@@ -137,8 +140,10 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
         return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cuTensorMapEncodeTiled is not available in this driver");
     }
     ctx->encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    if (const char* pv = std::getenv("FUSOR_CUDA_PREFILL_VARIANT")) ctx->prefill_variant = std::atoi(pv);
     // opt in to large dynamic shared memory once per context
     cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
+    cudaFuncSetAttribute(prefill2_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM_BYTES);
     cudaFuncSetAttribute(decode_splitkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(decode_splitkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(general_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -381,11 +386,15 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
 static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
                               const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
                               const fusor_cuda_tensor4* out, float* debug, int p_mode, int window = 0) {
+    // Two query tiles per CTA with 128-key blocks once a (batch, head) has 256 rows or more; the 64-key kernel with
+    // two CTAs per SM below that (and when asked for: p_mode bit 2, diagnostics).
+    const bool two_tiles = S.Sq >= P2_ROWS && (debug == nullptr || (p_mode & 8)) && (p_mode & 4) == 0 && ctx->prefill_variant != 1;
+    const int kv_rows = two_tiles ? P2_BN : PF_BN;
     CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
     TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM));
-    TRY(make_tmap_bhsd(ctx, &tmK, k, PF_BN));
-    TRY(make_tmap_bhsd(ctx, &tmV, v, PF_BN));
-    TRY(make_tmap_bhsd(ctx, &tmO, out, PF_BM, out->dtype == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16));
+    TRY(make_tmap_bhsd(ctx, &tmK, k, kv_rows));
+    TRY(make_tmap_bhsd(ctx, &tmV, v, kv_rows));
+    TRY(make_tmap_bhsd(ctx, &tmO, out, two_tiles ? 32 : PF_BM, out->dtype == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16));
     tmV16 = tmV;
     const int* flag = nullptr;
     if ((p_mode & 1) == 0) {
@@ -410,7 +419,7 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
         fusor_cuda_tensor4 v16 = *v;
         v16.data = ctx->v16;
         set_contiguous(&v16);
-        TRY(make_tmap_bhsd(ctx, &tmV16, &v16, PF_BN, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
+        TRY(make_tmap_bhsd(ctx, &tmV16, &v16, kv_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
         flag = ctx->d_flags + slot;
     }
     PrefillParams P;
@@ -420,7 +429,7 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.causal = mask_kind == FUSOR_CUDA_MASK_CAUSAL || mask_kind == FUSOR_CUDA_MASK_SLIDING;
     P.window = mask_kind == FUSOR_CUDA_MASK_SLIDING ? window : 0;
     P.scale_log2 = scale * 1.4426950408889634f;
-    P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
+    P.n_q_tiles = two_tiles ? (S.Sq + P2_ROWS - 1) / P2_ROWS : (S.Sq + PF_BM - 1) / PF_BM;
     P.err = ctx->d_err;
     P.debug = debug;
     P.debug_values = (p_mode & 2) ? 0 : 1;
@@ -428,6 +437,11 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.v_f16_overflow = flag;
     const long long grid = (long long)P.n_q_tiles * S.Hq * S.B;
     if (grid > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "grid too large");
+    if (two_tiles) {
+        const unsigned ctas = (unsigned)std::min<long long>(grid, ctx->num_sms);  // persistent: one CTA per SM
+        prefill2_sm100_kernel<<<ctas, P2_THREADS, P2_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
+        return launch_check(ctx, "prefill2_sm100_kernel");
+    }
     prefill_sm100_kernel<<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
     return launch_check(ctx, "prefill_sm100_kernel");
 }
