@@ -150,6 +150,9 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
         I.n = (I.active[1] ? I.je[1] : I.je[0]) - I.J0;
         return I;
     };
+    // round k of CTA c: items are dealt forwards in even rounds and backwards in odd ones (heavy-first order, so a CTA
+    // that got the heavier end of one round gets the lighter end of the next)
+    auto item_of = [&](int k) { return k * (int)gridDim.x + ((k & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x); };
     auto act = [](const Item& I, int t, int j) { return I.active[t] && j >= I.jb[t] && j < I.je[t]; };
 
     if (tid == 0) {
@@ -193,7 +196,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
             int g = 0;   // K / V blocks loaded so far: ring slot g & 1, use g >> 1
             int it = 0;  // items started
             bool ok = true;
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+            for (int item = item_of(0); item < n_items && ok; item = item_of(++it)) {
                 const Item I = decode(item);
                 auto load_q = [&](int t) {
                     // the Q buffer of tile t is free once the previous item's last S = Q K^T of that tile has completed
@@ -243,7 +246,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
             int cnt[2] = {0, 0};  // blocks of tile t whose PV has been issued, over all items: phase of p_full
             int qn[2] = {0, 0};   // Q tiles of tile t consumed: phase of q_full
             bool first_item = true;
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            for (int round = 0, item = item_of(0); item < n_items && ok; item = item_of(++round)) {
                 const Item I = decode(item);
                 bool fresh[2] = {true, true};  // the tile's first PV of this item overwrites O
                 bool q_ready[2] = {false, false};
@@ -288,6 +291,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                                 tc_mma_ts(tmem_base + P2_COL_O + t * 128, tmem_base + P2_COL_S + t * 128 + kk * 8,
                                           vd + (uint64_t)((kk * 2048) >> 4), idesc_pv, (!fresh[t] || kk > 0));
                             ok = P2_WAIT(p_full2 + t, cnt[t] & 1, abort_flag, P.err, 37 + t);
+                            if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 2);
                             if (!ok) break;
                             tc_fence_after();
 #pragma unroll
@@ -304,7 +308,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                                 k_ready = true;
                             }
                             if (!ok) break;
-                            if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 2);
                             ok = qk(t, j + 1, st1);  // overwrites the columns P_t(j) is read from: the pipe runs in issue order
                             if (!ok) break;
                             if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 3);
@@ -336,7 +339,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
         bool ok = true;
         int cb = 0;  // blocks of this tile processed over all items: phases of s_full and pv_done
         bool first_item = true;
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        for (int round = 0, item = item_of(0); item < n_items && ok; item = item_of(++round)) {
             const Item I = decode(item);
             const int r0 = I.q0 + t * P2_BM;
             const int qi = r0 + row;
@@ -363,6 +366,13 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                         if (k0 + i > k_limit || k0 + i < k_first) s[i] = -INFINITY;
                 }
                 float mx[8];
+#if P2_WHATIF == 3
+                if (jj > 0) {
+#pragma unroll
+                    for (int a = 0; a < 8; ++a) mx[a] = -INFINITY;
+                } else
+#endif
+                {
 #pragma unroll
                 for (int a = 0; a < 8; ++a) mx[a] = fmaxf(s[4 * a], s[4 * a + 1]);
 #pragma unroll
@@ -371,6 +381,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 for (int i = 32; i < P2_BN; i += 16)
 #pragma unroll
                     for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[i + 2 * a], s[i + 2 * a + 1]);
+                }
                 const float pmax = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])));
                 const float tmax = pmax * c;  // scale > 0
                 const float m_new = (tmax > m_ref + PF_RESCALE_THRESHOLD) ? tmax : m_ref;  // also taken on the first block
@@ -402,6 +413,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
     asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(s2[2 * (g)]) : "l"(c2u), "l"(nm2u));                           \
     asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(s2[2 * (g) + 1]) : "l"(c2u), "l"(nm2u));
 #define P2_E(g, k) asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(s[4 * (g) + (k)]));
+                if (tr && jj < 60) stamp(t * 512 + jj * 8 + 7);
                 P2_T(0)
                 P2_T(1)
                 P2_E(0, 0) P2_E(0, 1) P2_E(0, 2) P2_E(0, 3)
