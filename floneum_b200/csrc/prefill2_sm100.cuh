@@ -37,33 +37,6 @@ constexpr uint32_t P2_COL_S = 0, P2_COL_O = 256;  // tile t: S at 128 t, O at 25
 constexpr size_t P2_SMEM_BYTES = 1024 + 2 * (size_t)P2_TILE_BYTES /*Q*/ + 4 * (size_t)P2_TILE_BYTES /*K,V rings*/ +
                                  8 * (size_t)P2_STAGE_BYTES + 512;
 
-#ifndef P2_WHATIF
-#define P2_WHATIF 0  // timing experiments only (wrong results): 1 = bit-op pack instead of cvt, 2 = no ex2
-#endif
-#ifndef P2_SPIN
-#define P2_SPIN 0  // 1: the S-ready and P-ready hand-offs poll with test_wait instead of sleeping in try_wait
-#endif
-#if P2_SPIN
-#define P2_WAIT mbar_wait_spin
-#else
-#define P2_WAIT mbar_wait
-#endif
-#ifndef P2_POLY_CFG
-#define P2_POLY_CFG 0  // of every 8 exponentials, how many are evaluated on the FMA pipe instead of the MUFU
-#endif
-
-// 2^x for x <= 0 on the FMA pipe: x = n + f, n = floor(x), 2^f by a degree-3 polynomial on [0,1) (relative error
-// about 1e-4, below the f16 quantisation of P), the exponent added into the bit pattern.  Clamped at -126.
-__device__ __forceinline__ float poly_exp2(float x) {
-    x = fmaxf(x, -126.0f);
-    const float n = floorf(x);
-    const float f = x - n;
-    float p = fmaf(f, 0.0555041f, 0.2402265f);
-    p = fmaf(p, f, 0.6931472f);
-    p = fmaf(p, f, 1.0f);
-    return __int_as_float(__float_as_int(p) + ((int)n << 23));
-}
-
 // O row *= alpha for the 128 accumulator columns of this thread's row.  Rare (the row maximum grew by more than 2^8),
 // and kept out of line so that its registers are not reserved in the softmax loop, whose 128 scores stay in registers.
 __device__ __noinline__ void rescale_o_rows(uint32_t o_tmem, float alpha) {
@@ -276,7 +249,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                     for (int t = 0; t < 2; ++t) {
                         if (act(I, t, j)) {
                             if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 0);
-                            ok = P2_WAIT(p_full + t, cnt[t] & 1, abort_flag, P.err, 32 + t);
+                            ok = mbar_wait(p_full + t, cnt[t] & 1, abort_flag, P.err, 32 + t);
                             if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 1);
                             if (ok && !v_ready) {
                                 ok = mbar_wait(v_full + st, ph, abort_flag, P.err, 34);
@@ -290,7 +263,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                             for (int kk = 0; kk < P2_BN / 32; ++kk)
                                 tc_mma_ts(tmem_base + P2_COL_O + t * 128, tmem_base + P2_COL_S + t * 128 + kk * 8,
                                           vd + (uint64_t)((kk * 2048) >> 4), idesc_pv, (!fresh[t] || kk > 0));
-                            ok = P2_WAIT(p_full2 + t, cnt[t] & 1, abort_flag, P.err, 37 + t);
+                            ok = mbar_wait(p_full2 + t, cnt[t] & 1, abort_flag, P.err, 37 + t);
                             if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 2);
                             if (!ok) break;
                             tc_fence_after();
@@ -350,7 +323,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
             const bool tr = row == 0 && first_item;
             for (int jj = 0; jj < nb && ok; ++jj, ++cb) {
                 if (tr && jj < 60) stamp(t * 512 + jj * 8 + 0);
-                ok = P2_WAIT(s_full + t, cb & 1, abort_flag, P.err, 40 + t);
+                ok = mbar_wait(s_full + t, cb & 1, abort_flag, P.err, 40 + t);
                 if (!ok) break;
                 tc_fence_after();
                 if (tr && jj < 60) stamp(t * 512 + jj * 8 + 1);
@@ -366,12 +339,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                         if (k0 + i > k_limit || k0 + i < k_first) s[i] = -INFINITY;
                 }
                 float mx[8];
-#if P2_WHATIF == 3
-                if (jj > 0) {
-#pragma unroll
-                    for (int a = 0; a < 8; ++a) mx[a] = -INFINITY;
-                } else
-#endif
                 {
 #pragma unroll
                 for (int a = 0; a < 8; ++a) mx[a] = fmaxf(s[4 * a], s[4 * a + 1]);
@@ -404,7 +371,9 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 // its scheduler while the other tile waits, so each MUFU issue (8 cycles of the pipe) is followed in program
                 // order by independent FMA-pipe work of other groups: the sum / pack of the group before (whose exponentials
                 // were issued 32 cycles earlier) and the scale-and-subtract of the group after next.  The asm statements are
-                // volatile so that this order reaches the assembler.
+                // volatile so that this order reaches the assembler.  (Evaluating a quarter of the exponentials by a polynomial
+                // on the FMA pipe was tried in this schedule and changed nothing: the FMA-pipe instructions already fill the
+                // issue slots between the MUFU operations.)
                 uint64_t* s2 = reinterpret_cast<uint64_t*>(s);  // pairs (s[2p], s[2p+1])
                 const uint64_t c2u = *reinterpret_cast<const uint64_t*>(&c2), nm2u = *reinterpret_cast<const uint64_t*>(&nm2);
                 uint64_t ps0u = 0, ps1u = 0;  // two packed f32 zeros each
@@ -413,7 +382,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
     asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(s2[2 * (g)]) : "l"(c2u), "l"(nm2u));                           \
     asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(s2[2 * (g) + 1]) : "l"(c2u), "l"(nm2u));
 #define P2_E(g, k) asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(s[4 * (g) + (k)]));
-                if (tr && jj < 60) stamp(t * 512 + jj * 8 + 7);
                 P2_T(0)
                 P2_T(1)
                 P2_E(0, 0) P2_E(0, 1) P2_E(0, 2) P2_E(0, 3)
