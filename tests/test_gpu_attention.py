@@ -289,3 +289,31 @@ def test_prefill_cfg2_full_size_sampled_rows(device):
     tq2, tk2, tv2 = (fb.Tensor.from_slice(device, a.shape, np.ascontiguousarray(a[perm]), 1) for a in (w.q, w.k, w.v))
     got2 = tq2.flash_attention(tk2, tv2, w.scale, mask).as_slice()
     assert np.array_equal(got2, got[perm])
+
+
+def test_prefill_two_tile_kernel_many_items_and_bf16_out(device):
+    """More (row block, head, batch) items than SMs, so persistent CTAs of the two-tile kernel run several items each and
+    its barrier phases carry over; output in bf16 (the 64-column TMA store path) and f32."""
+    fb = _mods()
+    B, Hq, Hkv, S = 2, 40, 8, 512  # 2 * 40 * 2 = 160 items
+    q, k, v, scale = _bf16_case(4242, B, Hq, Hkv, S, S)
+    mask = (fb.MaskCache().get_mask(S, 0, None, device), fb.MaskKind.QKMask)
+    want = O.flash_attention(q, k, v, scale, mask_kind=O.MASK_CAUSAL, skip_masked=True)
+    got32 = _run(device, q, k, v, scale, mask, dtype=1)
+    assert_close(got32, want, what="two-tile kernel, 160 items, f32 out")
+    got16 = _run(device, q, k, v, scale, mask, dtype=1, out_dtype=1)
+    assert np.array_equal(got16.view(np.uint32), O.bf16_round(got32).view(np.uint32)), "bf16 output is the f32 output rounded once"
+
+
+def test_prefill_value_overflowing_f16_falls_back(device):
+    """|v| > 65504 cannot be held in the f16 copy of V: the kernels switch to bf16 weights and values (looser tolerance)."""
+    fb = _mods()
+    q, k, v, scale = _bf16_case(77, 1, 2, 1, 512, 512)
+    v = v.copy()
+    v[0, 0, 3, 5] = O.bf16_round(np.float32(1.0e5))
+    mask = (fb.MaskCache().get_mask(512, 0, None, device), fb.MaskKind.QKMask)
+    got = _run(device, q, k, v, scale, mask, dtype=1)
+    want = O.flash_attention(q, k, v, scale, mask_kind=O.MASK_CAUSAL, skip_masked=True)
+    assert np.isfinite(got).all()
+    rel = np.abs(got - want) / (1.0 + np.abs(want))
+    assert rel.max() < 8e-3, rel.max()
