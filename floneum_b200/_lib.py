@@ -64,6 +64,7 @@ SIGNATURES = {
     "fusor_cuda_kvcache_destroy": (c_int32, [c_void_p]),
     "fusor_cuda_kvcache_reset": (c_int32, [c_void_p]),
     "fusor_cuda_kvcache_append": (c_int32, [c_void_p, _T4, _T4]),
+    "fusor_cuda_attention_out_proj": (c_int32, [c_void_p, _T4, _T4, c_void_p, _T4]),
     "fusor_cuda_rope": (c_int32, [c_void_p, _T4, c_void_p, c_void_p, c_int32, c_int32, c_int32, _T4]),
     "fusor_cuda_kvcache_rope_append": (c_int32, [c_void_p, _T4, _T4, _T4, c_void_p, c_void_p, c_int32, c_int32, c_int32, _T4]),
     "fusor_cuda_kvcache_truncate_front": (c_int32, [c_void_p, c_int32, c_int32]),

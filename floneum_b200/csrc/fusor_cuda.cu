@@ -21,6 +21,7 @@
 #include "general_attention.cuh"
 #include "prefill_sm100.cuh"
 #include "prefill2_sm100.cuh"
+#include "oproj_sm100.cuh"
 #include "rope_append.cuh"
 
 using namespace fusor;
@@ -144,6 +145,7 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
     // opt in to large dynamic shared memory once per context
     cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
     cudaFuncSetAttribute(prefill2_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM_BYTES);
+    cudaFuncSetAttribute(oproj_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)OP_SMEM_BYTES);
     cudaFuncSetAttribute(decode_splitkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(decode_splitkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(general_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -477,6 +479,51 @@ extern "C" int32_t fusor_cuda_prefill_probe(fusor_cuda_ctx* ctx, const fusor_cud
     if (!prefill_eligible(S, q, k, v, scale, mask_kind, out))
         return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "arguments are not eligible for the tensor-core prefill kernel");
     return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, debug_device, p_format);
+}
+
+// --------------------------------------------------------------------------- output projection
+extern "C" int32_t fusor_cuda_attention_out_proj(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* attn,
+                                                 const fusor_cuda_tensor4* weight, const float* bias,
+                                                 const fusor_cuda_tensor4* out) {
+    if (!ctx) return FUSOR_CUDA_INVALID_ARGUMENT;
+    if (!attn || !weight || !out || !attn->data || !weight->data || !out->data) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    if (!dtype_ok(attn->dtype) || !dtype_ok(weight->dtype) || !dtype_ok(out->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    const long long B = attn->shape[0], Hq = attn->shape[1], S = attn->shape[2], D = attn->shape[3];
+    const long long N = weight->shape[2], K = weight->shape[3];
+    if (weight->shape[0] != 1 || weight->shape[1] != 1) return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "weight must be given as [1, 1, out_features, in_features]");
+    if (B <= 0 || Hq <= 0 || S <= 0 || D <= 0 || N <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "empty tensor");
+    if (K != Hq * D)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "weight is [%lld, %lld]; the attention output flattens to %lld input features", N, K, Hq * D);
+    if (out->shape[0] != B || out->shape[1] != 1 || out->shape[2] != S || out->shape[3] != N)
+        return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "out must be [%lld, 1, %lld, %lld]", B, S, N);
+    if (attn->dtype != FUSOR_CUDA_BF16 || weight->dtype != FUSOR_CUDA_BF16)
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the output projection takes bf16 attention output and bf16 weights");
+    if (D % OP_BK != 0) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "head_dim must be a multiple of %d", OP_BK);
+    if (!tma_view_ok(attn)) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "attention output view is not 16-byte aligned");
+    if (weight->stride[3] != 1 || weight->stride[2] % 8 != 0 || reinterpret_cast<uintptr_t>(weight->data) % 16)
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "weight rows must be contiguous and 16-byte aligned");
+    const int al = out->dtype == FUSOR_CUDA_F32 ? 4 : 8;
+    if (out->stride[3] != 1 || out->stride[2] % al != 0 || (B > 1 && out->stride[0] % al != 0) || reinterpret_cast<uintptr_t>(out->data) % 16)
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "out rows must be contiguous and 16-byte aligned");
+    if (bias && reinterpret_cast<uintptr_t>(bias) % 4) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "bias is misaligned");
+    DeviceGuard g(ctx->device);
+    fusor_cuda_tensor4 w4 = *weight;
+    w4.stride[0] = w4.stride[1] = N * weight->stride[2];
+    CUtensorMap tmA, tmW, tmO;
+    TRY(make_tmap_bhsd(ctx, &tmA, attn, OP_BM));
+    TRY(make_tmap_bhsd(ctx, &tmW, &w4, OP_BN));
+    TRY(make_tmap_bhsd(ctx, &tmO, out, 32, out->dtype == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16));
+    OprojParams P;
+    P.B = (int)B; P.Hq = (int)Hq; P.S = (int)S; P.D = (int)D; P.N = (int)N;
+    P.m_tiles_per_batch = (int)((S + OP_BM - 1) / OP_BM);
+    P.n_tiles = (int)((N + OP_BN - 1) / OP_BN);
+    P.k_chunks = (int)(K / OP_BK);
+    P.bias = bias; P.out_dtype = out->dtype; P.err = ctx->d_err;
+    const long long tiles = B * P.m_tiles_per_batch * P.n_tiles;
+    if (tiles > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "too many output tiles");
+    const unsigned ctas = (unsigned)std::min<long long>(tiles, ctx->num_sms);
+    oproj_sm100_kernel<<<ctas, OP_THREADS, OP_SMEM_BYTES, ctx->stream>>>(tmA, tmW, tmO, P);
+    return launch_check(ctx, "oproj_sm100_kernel");
 }
 
 // --------------------------------------------------------------------------- host-memory variants

@@ -6,6 +6,8 @@ Two partitions, both defined by the benchmark configurations (the reference has 
   * KV-sequence chunks (long-context decode): rank r owns keys [r*Skv/N, (r+1)*Skv/N); each rank emits
     a partial {m, l, O} per query head, the partials are all-gathered (NCCL over NVLink on GPUs, gloo in
     the CPU tests) and merged by log-sum-exp on every rank.
+The output projection that follows head-sharded attention is the one place the head partition needs a collective: rank r
+multiplies its heads by columns [q0*D, q1*D) of the weight and the partial sums are all-reduced (`out_proj_all_reduce`).
 """
 from __future__ import annotations
 
@@ -67,3 +69,29 @@ def decode_kv_chunks(device, cache, q, scale: float, group=None):
     out = torch.empty((B, Hq, D), dtype=torch.float32, device=partial.device)
     lse_combine(device, Tensor.from_torch(device, gathered), Tensor.from_torch(device, out))
     return out
+
+
+def out_proj_weight_columns(num_q_heads: int, num_kv_heads: int, head_dim: int, rank: int, world: int) -> Tuple[int, int]:
+    """Columns of the [out_features, Hq*D] projection weight that multiply the query heads of `rank`."""
+    q0, q1 = q_head_range(num_q_heads, num_kv_heads, rank, world)
+    return q0 * head_dim, q1 * head_dim
+
+
+def all_reduce_sum(t, group=None):
+    """In-place sum over ranks of a torch tensor (NCCL on GPUs, gloo in the CPU tests)."""
+    import torch.distributed as dist
+    dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return t
+
+
+def out_proj_all_reduce(device, attn, weight_shard, bias, rank: int, group=None):
+    """Tensor-parallel output projection: attn [B, Hq/N, S, D] (this rank's heads, bf16), weight_shard [out, Hq/N * D]
+    (this rank's columns), bias f32 [out] or None (added on rank 0 only) -> torch f32 [B, S, out], summed over ranks.
+    The collective runs on torch's current stream, which must be the stream the Device was created on."""
+    import torch
+    from .tensor import Tensor
+    B, _, S, _ = attn.shape()
+    n_out = weight_shard.shape()[0]
+    out = torch.empty((B, S, n_out), dtype=torch.float32, device=f"cuda:{device.ordinal}")
+    attn.out_proj(weight_shard, bias if rank == 0 else None, out=Tensor.from_torch(device, out))
+    return all_reduce_sum(out, group)

@@ -153,6 +153,30 @@ class Tensor:
             t.stride[i] = self.strides[i]
         return t
 
+    # ------------------------------------------------------------------ output projection
+    def out_proj(self, weight: "Tensor", bias: Optional["Tensor"] = None, out_dtype: int = F32,
+                 out: Optional["Tensor"] = None) -> "Tensor":
+        """self = attention output [B,Hq,S,D] (bf16) -> [B,S,N]: the layer's `transpose(1, 2).reshape(..)` followed by
+        `Linear::forward` with a dense bf16 weight [N, Hq*D] and an optional f32 bias [N]
+        (models/kalosm-llama/src/raw/attention_layer.rs:450-454; fusor-ml/fusor/src/layers/linear.rs:72-115)."""
+        B, Hq, S, D = self._shape
+        ws = weight.shape()
+        assert len(ws) == 2 and ws[1] == Hq * D, f"weight shape {list(ws)} does not match [out_features, {Hq * D}]"
+        if bias is not None:
+            assert tuple(bias.shape()) == (ws[0],) and bias.dtype == F32, "bias must be f32 [out_features]"
+        if out is None:
+            out = Tensor.empty(self.device, (B, S, ws[0]), out_dtype)
+        assert tuple(out.shape()) == (B, S, ws[0]) and out.is_contiguous(), "out must be a contiguous [B, S, out_features]"
+        out_dtype = out.dtype
+        w4 = Tensor(self.device, weight.ptr, (1, 1, ws[0], ws[1]), weight.dtype,
+                    (ws[0] * weight.strides[0], ws[0] * weight.strides[0], weight.strides[0], weight.strides[1]), owner=weight)
+        o4 = Tensor(self.device, out.ptr, (B, 1, S, ws[0]), out_dtype, (S * ws[0], S * ws[0], ws[0], 1), owner=out)
+        ca, cw, co = self._c4(), w4._c4(), o4._c4()
+        _lib.check(_lib.load().fusor_cuda_attention_out_proj(self.device.handle, ctypes.byref(ca), ctypes.byref(cw),
+                                                             bias.ptr if bias is not None else None, ctypes.byref(co)),
+                   self.device.handle)
+        return out
+
     # ------------------------------------------------------------------ rotary embedding
     def rope(self, cos: "Tensor", sin: "Tensor") -> "Tensor":
         """Tensor::rope (fusor-ml/fusor/src/composite/rope.rs:38-68): halves (i, i + D/2); cos/sin [seq, D/2]."""

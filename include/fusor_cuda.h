@@ -231,6 +231,16 @@ int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcach
  * partial f32 [B][Hq][D+2] = { m = max scaled score, l = sum exp(s - m), O[D] = sum exp(s - m) v }. */
 int32_t fusor_cuda_flash_attention_decode_partial(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
                                                   const fusor_cuda_tensor4* q, float scale, float* partial);
+/* Output projection right after attention (next-row F1): out[b, s, :] = W . flatten_h,d(attn[b, :, s, :]) + bias, the
+ * reference's attn_output.transpose(1, 2).reshape([b, q_len, hidden]) followed by Linear::forward
+ * (models/kalosm-llama/src/raw/attention_layer.rs:450-454, fusor-ml/fusor/src/layers/linear.rs:72-115; the reference
+ * multiplies by a GGUF-quantised QMatrix, here the weight is dense).  attn [B,Hq,S,D] bf16 as flash_attention wrote it
+ * (no transposed copy is made), weight bf16 given as a tensor4 of shape [1, 1, N, Hq*D] (rows contiguous), bias f32 [N] on the device or NULL, out f32 or bf16 given
+ * as a tensor4 of shape [B, 1, S, N].  Products accumulate in f32 on the tensor cores.  With the query heads split over
+ * GPUs each rank passes its heads and the matching columns of the weight and gets a partial sum (bias on one rank only);
+ * the ranks then add their results (all-reduce). */
+int32_t fusor_cuda_attention_out_proj(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* attn, const fusor_cuda_tensor4* weight,
+                                      const float* bias, const fusor_cuda_tensor4* out);
 /* Merge: parts f32 [n_parts][n_rows][D+2] -> out f32 [n_rows][D]  (M = max m, L = sum l e^(m-M),
  * out = sum O e^(m-M) / L; the (m, d) rule of fusor-ml/core/src/composite/softmax.rs:59-82).
  * A part with l == 0 contributes nothing. */

@@ -327,3 +327,33 @@ __attribute__((optimize("fp-contract=off"))) int oracle_rope_f32(const float* x,
         }
     return 0;
 }
+
+/*
+ * Output projection after attention, f32:
+ *   out[b, s, n] = sum_k x[b, s, k] * w[n, k] + bias[n],   x[b, s, h * D + d] = attn[b, h, s, d]
+ * (attn_output.transpose(1, 2).reshape([b, q_len, hidden]) then Linear::forward: matmul with the weight, bias added
+ * afterwards; models/kalosm-llama/src/raw/attention_layer.rs:450-454, fusor-ml/fusor/src/layers/linear.rs:72-115.  The
+ * reference's weight is a GGUF-quantised QMatrix; the oracle takes its dense values.)  Each output element accumulates
+ * over k in ascending order.  attn [B,Hq,S,D], w [N, Hq*D], bias [N] or NULL, out [B,S,N], all contiguous.
+ */
+int oracle_out_proj_f32(const float* attn, const float* w, const float* bias, float* out, int B, int Hq, int S, int D,
+                        int N) {
+    if (B <= 0 || Hq <= 0 || S <= 0 || D <= 0 || N <= 0) return -1;
+    const int K = Hq * D;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < B; ++b)
+        for (int s = 0; s < S; ++s) {
+            float* x = (float*)malloc((size_t)K * sizeof(float));
+            for (int h = 0; h < Hq; ++h)
+                memcpy(x + (size_t)h * D, attn + (((size_t)b * Hq + h) * S + s) * D, (size_t)D * sizeof(float));
+            float* o = out + ((size_t)b * S + s) * N;
+            for (int n = 0; n < N; ++n) {
+                const float* wr = w + (size_t)n * K;
+                float acc = 0.0f;
+                for (int k = 0; k < K; ++k) acc += x[k] * wr[k];
+                o[n] = bias ? acc + bias[n] : acc;
+            }
+            free(x);
+        }
+    return 0;
+}

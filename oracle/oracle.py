@@ -59,6 +59,8 @@ def lib():
         L.oracle_attention_partial_f32.restype = ctypes.c_int
         L.oracle_num_threads.restype = ctypes.c_int
         L.oracle_rope_f32.argtypes = [fp, fp, fp, fp] + [ctypes.c_int] * 6
+        L.oracle_out_proj_f32.argtypes = [fp, fp, fp, fp] + [ctypes.c_int] * 5
+        L.oracle_out_proj_f32.restype = ctypes.c_int
         L.oracle_rope_f32.restype = ctypes.c_int
         _lib = L
     return _lib
@@ -172,6 +174,21 @@ def lse_combine(parts) -> np.ndarray:
     n_rows = int(np.prod(parts.shape[1:-1]))
     out = np.empty(parts.shape[1:-1] + (D,), np.float32)
     lib().oracle_lse_combine(_p(parts), P, n_rows, D, _p(out))
+    return out
+
+
+# --------------------------------------------------------------------------- output projection (next-row F1)
+def out_proj(attn, w, bias=None) -> np.ndarray:
+    """attn [B,Hq,S,D], w [N, Hq*D], bias [N] or None -> [B,S,N]: transpose(1,2).reshape then x @ w.T + bias
+    (models/kalosm-llama/src/raw/attention_layer.rs:450-454; fusor-ml/fusor/src/layers/linear.rs:72-115)."""
+    attn, w = _f32(attn), _f32(w)
+    B, Hq, S, D = attn.shape
+    N, K = w.shape
+    assert K == Hq * D
+    b = _f32(bias) if bias is not None else None
+    out = np.empty((B, S, N), np.float32)
+    rc = lib().oracle_out_proj_f32(_p(attn), _p(w), _p(b), _p(out), B, Hq, S, D, N)
+    assert rc == 0
     return out
 
 

@@ -233,3 +233,18 @@ def test_rope_inverse_frequency():
     cos, sin = O.rope_tables(4, 2, 10000.0)
     np.testing.assert_allclose(cos[1], np.cos([1.0, 0.01]), rtol=1e-6)
     np.testing.assert_allclose(sin[1], np.sin([1.0, 0.01]), rtol=1e-6)
+
+
+# --------------------------------------------------------------------------- output projection
+def test_out_proj_is_transpose_reshape_linear():
+    """attention_layer.rs:450-454 + linear.rs:72-115: transpose(1, 2), reshape to [b, q_len, hidden], x @ W^T + bias."""
+    rng = np.random.default_rng(4)
+    attn = rng.standard_normal((2, 3, 5, 4)).astype(np.float32)
+    w = rng.standard_normal((7, 12)).astype(np.float32)
+    b = rng.standard_normal(7).astype(np.float32)
+    want = attn.transpose(0, 2, 1, 3).reshape(2, 5, 12).astype(np.float64) @ w.T.astype(np.float64) + b
+    np.testing.assert_allclose(O.out_proj(attn, w, b), want, atol=1e-5)
+    np.testing.assert_allclose(O.out_proj(attn, w), want - b, atol=1e-5)
+    # identity weight: the projection is just the head-interleaving transpose
+    eye = np.eye(12, dtype=np.float32)
+    assert np.array_equal(O.out_proj(attn, eye), attn.transpose(0, 2, 1, 3).reshape(2, 5, 12))

@@ -57,11 +57,21 @@ def _worker(rank, world, port, ret):
         k0, k1 = sharding.kv_head_range(Hkv, rank, world)
         mine = O.flash_attention(q[:, q0:q1], k[:, k0:k1], v[:, k0:k1], scale)
         ok_heads = float(np.abs(mine - full[:, q0:q1]).max())
+        # (3) output projection over head shards: partial sums of this rank's heads x weight columns, all-reduced
+        N = 24
+        w = rng.standard_normal((N, Hq * D), dtype=np.float32)
+        bias = rng.standard_normal(N, dtype=np.float32)
+        attn_full = rng.standard_normal((B, Hq, 5, D), dtype=np.float32)
+        c0, c1 = sharding.out_proj_weight_columns(Hq, Hkv, D, rank, world)
+        assert (c0, c1) == (q0 * D, q1 * D)
+        part_o = O.out_proj(attn_full[:, q0:q1], np.ascontiguousarray(w[:, c0:c1]), bias if rank == 0 else None)
+        summed = sharding.all_reduce_sum(torch.from_numpy(part_o)).numpy()
+        ok_proj = float(np.abs(summed - O.out_proj(attn_full, w, bias)).max())
         # max over ranks, as the benchmark does for its timings
-        t = torch.tensor([ok_chunks, ok_heads], dtype=torch.float64)
+        t = torch.tensor([ok_chunks, ok_heads, ok_proj], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if rank == 0:
-            ret["chunks"], ret["heads"] = float(t[0]), float(t[1])
+            ret["chunks"], ret["heads"], ret["proj"] = float(t[0]), float(t[1]), float(t[2])
     finally:
         dist.destroy_process_group()
 
@@ -74,3 +84,4 @@ def test_kv_chunk_allgather_and_head_shards_world2():
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
     assert ret["chunks"] < 2e-6, ret
     assert ret["heads"] == 0.0, ret
+    assert ret["proj"] < 1e-4, ret  # f32 sums of 256 terms of size ~1 in two different orders
