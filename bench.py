@@ -186,7 +186,9 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "oproj", "rope"],
+                    help="cfg2-cfg5: the attention configurations; oproj / rope: the steps after and before attention "
+                    "(output projection GEMM, fused RoPE + cache append) at config 2's sizes")
     ap.add_argument("--no-extras", action="store_true", help="skip the decode line and the CPU baseline")
     ap.add_argument("--shard-of", type=int, default=0, help="for profiler captures on one GPU: run rank 0's shard of an "
                     "N-rank job (no process group; the line is marked as a shard)")
@@ -448,10 +450,147 @@ def main():
                            "l2": "KV working set exceeds L2" if flush is None else "300 MB buffer written between timed launches"},
                 "_got": (res if isinstance(res, torch.Tensor) else out).cpu().numpy(), "_q": qn, "_krange": (k0, k1)}
 
+    # ======================================================================= the neighbours of the path
+    def time_steps(step, n_copies_note):
+        for _ in range(args.warmup):
+            step(0)
+        barrier()
+        if not args.quick:  # let the clocks settle under load, as the attention legs do
+            t_end = time.time() + 0.5
+            i = 0
+            while time.time() < t_end:
+                step(i); i += 1
+                if i % 16 == 0:
+                    torch.cuda.synchronize()
+        barrier()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        sampler.start()
+        t0 = time.time()
+        with torch.cuda.stream(stream):
+            for i, (a, b) in enumerate(evs):
+                a.record(stream)
+                step(i)
+                b.record(stream)
+        barrier()
+        t1 = time.time()
+        clocks = sampler.stop(t0, t1)
+        ms = max_over_ranks(float(np.mean([a.elapsed_time(b) for a, b in evs])))
+        return ms, clocks
+
+    def run_oproj():
+        B, Hq_all, S, D, N = (2, 16, 2048, 128, 2048) if args.small else (4, 32, 4096, 128, 4096)
+        Hq = Hq_all // world
+        rng = np.random.default_rng(21)
+        n_copies = 2
+        attn = [torch.randn((B, Hq, S, D), device=cuda, dtype=torch.bfloat16, generator=None) for _ in range(n_copies)]
+        w_all = W.bf16_round((rng.standard_normal((N, Hq_all * D)) / np.sqrt(Hq_all * D)).astype(np.float32))
+        c0, c1 = (rank * Hq * D, (rank + 1) * Hq * D)
+        w_dev = bf16_dev(w_all[:, c0:c1])
+        out = torch.empty((B, S, N), device=cuda, dtype=torch.float32)
+        ta = [fb.Tensor.from_torch(dev, a) for a in attn]
+        tw = fb.Tensor.from_torch(dev, w_dev)
+        to = fb.Tensor.from_torch(dev, out)
+        flush = torch.empty(300 << 20, dtype=torch.uint8, device=cuda)
+
+        def step(i):
+            ta[i % n_copies].out_proj(tw, None, out=to)
+            if use_dist:
+                dist.all_reduce(out)
+        with torch.cuda.stream(stream):
+            l0 = dev.launch_count()
+            ms, clocks = time_steps(step, n_copies)
+            launches = dev.launch_count() - l0
+            step(0)
+        stream.synchronize()
+        got = out.cpu().numpy()
+        flops = 2.0 * B * S * N * Hq_all * D
+        achieved = flops / world / (ms * 1e-3) / 1e12
+        # parity on sampled rows: rank 0 rebuilds the full-K rows only on one GPU (N > 1: the shards' random inputs differ)
+        par = {"finite": bool(np.isfinite(got).all())}
+        if world == 1:
+            rows = np.random.default_rng(1).integers(0, B * S, 64)
+            a0 = attn[0].float().cpu().numpy()
+            x = np.stack([a0[r // S, :, r % S, :].reshape(-1) for r in rows])
+            want = O.out_proj(x.reshape(len(rows), Hq, 1, D), w_all)[:, 0]  # each sampled row as a batch of one token
+            err = np.abs(got.reshape(B * S, N)[rows] - want)
+            par.update(max_abs=float(err.max()), mean_abs=float(err.mean()), rows_checked=int(len(rows)), tolerance="max 2e-4")
+        return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "gpu_launches": launches,
+                "clocks": clocks, "parity": par, "e2e": None,
+                "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"], "unit": "TFLOP/s",
+                             "frac": achieved / peaks["tensor_sustained"], "traffic": None,
+                             "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
+                             "frac_of_burst_peak": achieved / peaks["tensor_burst"]},
+                "config": {"workload": f"oproj: out = attn[B{B},Hq{Hq_all},S{S},D{D}] (read in place) x W[{N},{Hq_all * D}]^T, bf16 in, f32 out",
+                           "sharding": f"query heads split over {world} rank(s)" + (", partial sums all-reduced over NCCL" if use_dist else ""),
+                           "l2": f"attention input rotates over {n_copies} copies", "flops_per_step": flops}}
+
+    def run_rope():
+        B, Hq_all, Hkv_all, S, D = (2, 16, 4, 4096, 128) if args.small else (4, 32, 8, 4096, 128)
+        Hq, Hkv = Hq_all // world, Hkv_all // world
+        rc = fb.RopeCache.new(D, S, 10000.0, dev)
+        pages = (S + 15) // 16
+        cache = fb.PagedKvCache(dev, B, Hkv, D, num_pages=B * pages, max_pages_per_seq=pages)
+        q = torch.randn((B, Hq, S, D), device=cuda, dtype=torch.bfloat16)
+        k = torch.randn((B, Hkv, S, D), device=cuda, dtype=torch.bfloat16)
+        v = torch.randn((B, Hkv, S, D), device=cuda, dtype=torch.bfloat16)
+        qo = torch.empty_like(q)
+        tq, tk, tv, tqo = (fb.Tensor.from_torch(dev, t) for t in (q, k, v, qo))
+        cq, ck, cv, co = tq._c4(), tk._c4(), tv._c4(), tqo._c4()
+        flush = torch.empty(300 << 20, dtype=torch.uint8, device=cuda)
+
+        def step(i):
+            cache.reset()
+            flush.zero_()  # 300 MB written: the tensors of the next step come from HBM
+            rcode = L.fusor_cuda_kvcache_rope_append(cache._h, ctypes.byref(cq), ctypes.byref(ck), ctypes.byref(cv), rc.cos.ptr,
+                                                     rc.sin.ptr, S, 0, 0, ctypes.byref(co))
+            assert rcode == 0, L.fusor_cuda_last_error(dev.handle)
+        # time only the fused kernel: events around the call, after the flush
+        for _ in range(args.warmup):
+            step(0)
+        barrier()
+        times = []
+        sampler.start()
+        t0 = time.time()
+        with torch.cuda.stream(stream):
+            for i in range(args.steps):
+                cache.reset()
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                rcode = L.fusor_cuda_kvcache_rope_append(cache._h, ctypes.byref(cq), ctypes.byref(ck), ctypes.byref(cv), rc.cos.ptr,
+                                                         rc.sin.ptr, S, 0, 0, ctypes.byref(co))
+                b.record(stream)
+                times.append((a, b))
+        barrier()
+        t1 = time.time()
+        clocks = sampler.stop(t0, t1)
+        ms = max_over_ranks(float(np.mean([a.elapsed_time(b) for a, b in times])))
+        nbytes_rank = q.numel() * 2 * 2 + k.numel() * 2 * 2 * 2
+        # parity: rotated q rows and the gathered K of one (batch, head) against the oracle, bit for bit
+        cos, sin = O.rope_tables(D, S, 10000.0)
+        qn = q[0, 0].float().cpu().numpy()[None, None]
+        want_q = O.bf16_round(O.rope(qn, cos, sin, 0, False))
+        got_q = qo[0, 0].float().cpu().numpy()[None, None]
+        gk, _ = cache.gather(B, S)
+        want_k = O.bf16_round(O.rope(k[0, 0].float().cpu().numpy()[None, None], cos, sin, 0, False))
+        par = {"q_bit_exact": bool(np.array_equal(got_q.view(np.uint32), want_q.view(np.uint32))),
+               "k_bit_exact": bool(np.array_equal(gk.as_slice()[0, 0].view(np.uint32), want_k[0, 0].view(np.uint32)))}
+        achieved = nbytes_rank / (ms * 1e-3) / 1e9
+        return {"value": nbytes_rank * world / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "gpu_launches": args.steps,
+                "clocks": clocks, "parity": par, "e2e": None,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s", "frac": achieved / peaks["hbm"],
+                             "traffic": None, "peak_source": f"{peaks['source']} (device copy)"},
+                "config": {"workload": f"rope: fused RoPE + KV-cache append, B{B} Hq{Hq_all} Hkv{Hkv_all} S{S} D{D}, bf16 in, bf16 pages",
+                           "sharding": f"heads split over {world} rank(s), no collective", "bytes_per_step": nbytes_rank * world,
+                           "l2": "300 MB buffer written between timed launches; table uploads are inside the timed region"}}
+
     # ----------------------------------------------------------------------- run the selected workload
     from oracle import oracle as O  # checker + CPU baseline only
     extras = {}
-    if args.workload in ("cfg2", "cfg5"):
+    if args.workload in ("oproj", "rope"):
+        r = run_oproj() if args.workload == "oproj" else run_rope()
+        dtype = "bf16"
+    elif args.workload in ("cfg2", "cfg5"):
         if args.small:
             w = W.cfg2(B=2, Hq=16, Hkv=4) if args.workload == "cfg2" else W.cfg5(S=8192, Hq=8, Hkv=2)
         else:
