@@ -46,6 +46,8 @@ struct fusor_cuda_ctx {
     size_t v16_bytes = 0;
     int* d_flags = nullptr;  // [256]
     unsigned flag_counter = 0;
+    // copy streams of the _host entry points (host -> device, device -> host), created on first use
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
     int prefill_variant = 0;  // 0 = pick by shape, 1 = always the 64-key kernel (set from FUSOR_CUDA_PREFILL_VARIANT, for A/B timing)
 };
 
@@ -168,6 +170,8 @@ extern "C" int32_t fusor_cuda_ctx_destroy(fusor_cuda_ctx* ctx) {
     if (ctx->v16) cudaFree(ctx->v16);
     if (ctx->d_flags) cudaFree(ctx->d_flags);
     if (ctx->d_err) cudaFree(ctx->d_err);
+    if (ctx->h2d_stream) cudaStreamDestroy(ctx->h2d_stream);
+    if (ctx->d2h_stream) cudaStreamDestroy(ctx->d2h_stream);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return FUSOR_CUDA_OK;
@@ -580,6 +584,73 @@ extern "C" int32_t fusor_cuda_flash_attention_host(fusor_cuda_ctx* ctx, const fu
     dv.data = p; p += align256(vb);
     dout.data = p; p += align256(ob);
     set_contiguous(&dq); set_contiguous(&dk); set_contiguous(&dv); set_contiguous(&dout);
+    // Without a mask tensor every (batch, group of kv heads) is an independent problem on contiguous slices of all four
+    // tensors: large calls are cut into about eight such chunks and pipelined over three streams, so the copies in,
+    // the kernels and the copy out of different chunks overlap (PCIe is full duplex) instead of running one after another.
+    const long long chunks_per_batch = [&]() -> long long {
+        if (has_mask || qb + kb + vb + ob < (8u << 20)) return 0;
+        long long want = std::max<long long>(1, (8 + S.B - 1) / S.B), best = 1;
+        for (long long d = 1; d <= S.Hkv && d <= want; ++d)
+            if (S.Hkv % d == 0) best = d;
+        return S.B * best >= 2 ? best : 0;
+    }();
+    if (chunks_per_batch > 0) {
+        if (!ctx->h2d_stream) {
+            CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+            CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+        }
+        const long long hk_per = S.Hkv / chunks_per_batch, hq_per = hk_per * (S.Hq / S.Hkv);
+        const size_t q_chunk = (size_t)hq_per * S.Sq * S.D, kv_chunk = (size_t)hk_per * S.Skv * S.D;
+        const size_t qs = dtype_size(q->dtype), ks = dtype_size(k->dtype), vs = dtype_size(v->dtype), os = dtype_size(out->dtype);
+        int32_t rc = FUSOR_CUDA_OK;
+        std::vector<cudaEvent_t> events;
+        auto new_event = [&]() {
+            cudaEvent_t e = nullptr;
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess) events.push_back(e);
+            return e;
+        };
+        // the copies into the scratch buffers must not overtake work already queued on the context's stream
+        cudaEvent_t start = new_event();
+        if (start) { cudaEventRecord(start, ctx->stream); cudaStreamWaitEvent(ctx->h2d_stream, start, 0); }
+        for (long long c = 0; c < S.B * chunks_per_batch && rc == FUSOR_CUDA_OK; ++c) {
+            const size_t qo = (size_t)c * q_chunk, ko = (size_t)c * kv_chunk;
+            fusor_cuda_tensor4 cq = dq, ck = dk, cv = dv, co = dout;
+            cq.data = (uint8_t*)dq.data + qo * qs; ck.data = (uint8_t*)dk.data + ko * ks;
+            cv.data = (uint8_t*)dv.data + ko * vs; co.data = (uint8_t*)dout.data + qo * os;
+            cq.shape[0] = ck.shape[0] = cv.shape[0] = co.shape[0] = 1;
+            cq.shape[1] = co.shape[1] = hq_per;
+            ck.shape[1] = cv.shape[1] = hk_per;
+            cudaEvent_t in_done = new_event(), k_done = new_event();
+            if (!in_done || !k_done) { rc = fail(ctx, FUSOR_CUDA_CUDA_ERROR, "cudaEventCreate failed"); break; }
+            cudaMemcpyAsync(cq.data, (const uint8_t*)q->data + qo * qs, q_chunk * qs, cudaMemcpyHostToDevice, ctx->h2d_stream);
+            cudaMemcpyAsync(ck.data, (const uint8_t*)k->data + ko * ks, kv_chunk * ks, cudaMemcpyHostToDevice, ctx->h2d_stream);
+            cudaMemcpyAsync(cv.data, (const uint8_t*)v->data + ko * vs, kv_chunk * vs, cudaMemcpyHostToDevice, ctx->h2d_stream);
+            cudaEventRecord(in_done, ctx->h2d_stream);
+            cudaStreamWaitEvent(ctx->stream, in_done, 0);
+            rc = fusor_cuda_flash_attention(ctx, &cq, &ck, &cv, scale, nullptr, mask_kind, window, &co);
+            if (rc != FUSOR_CUDA_OK) break;
+            cudaEventRecord(k_done, ctx->stream);
+            cudaStreamWaitEvent(ctx->d2h_stream, k_done, 0);
+            cudaMemcpyAsync((uint8_t*)out->data + qo * os, co.data, q_chunk * os, cudaMemcpyDeviceToHost, ctx->d2h_stream);
+        }
+        // join: the context's stream (and the caller) see the call as one operation
+        cudaEvent_t in_all = new_event(), out_all = new_event();
+        if (in_all && out_all) {
+            cudaEventRecord(in_all, ctx->h2d_stream);
+            cudaEventRecord(out_all, ctx->d2h_stream);
+            cudaStreamWaitEvent(ctx->stream, in_all, 0);
+            cudaStreamWaitEvent(ctx->stream, out_all, 0);
+        } else {
+            cudaStreamSynchronize(ctx->h2d_stream);
+            cudaStreamSynchronize(ctx->d2h_stream);
+        }
+        const int32_t rc2 = check_device_error(ctx);  // synchronises the context's stream, hence all three
+        for (cudaEvent_t e : events) cudaEventDestroy(e);
+        cudaError_t e = cudaGetLastError();
+        if (rc == FUSOR_CUDA_OK && rc2 == FUSOR_CUDA_OK && e != cudaSuccess)
+            return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "pipelined host call: %s", cudaGetErrorString(e));
+        return rc != FUSOR_CUDA_OK ? rc : rc2;
+    }
     CUDA_TRY(ctx, cudaMemcpyAsync(dq.data, q->data, qb, cudaMemcpyHostToDevice, ctx->stream));
     CUDA_TRY(ctx, cudaMemcpyAsync(dk.data, k->data, kb, cudaMemcpyHostToDevice, ctx->stream));
     CUDA_TRY(ctx, cudaMemcpyAsync(dv.data, v->data, vb, cudaMemcpyHostToDevice, ctx->stream));

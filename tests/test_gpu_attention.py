@@ -317,3 +317,35 @@ def test_prefill_value_overflowing_f16_falls_back(device):
     assert np.isfinite(got).all()
     rel = np.abs(got - want) / (1.0 + np.abs(want))
     assert rel.max() < 8e-3, rel.max()
+
+
+def test_host_entry_point_pipelined_chunks_match_device_path(device):
+    """A host call above 8 MB is cut into (batch, kv-head group) chunks whose copies and kernels overlap; the result
+    must be bit-identical to the one-piece device path (here with ordinary pageable host memory)."""
+    import ctypes
+    from floneum_b200 import _lib
+    fb = _mods()
+    L = _lib.load()
+    B, Hq, Hkv, S = 3, 8, 4, 640
+    q, k, v, scale = _bf16_case(31, B, Hq, Hkv, S, S)
+    bits = lambda a: np.ascontiguousarray(O.bf16_bits(a))
+    hq, hk, hv = bits(q), bits(k), bits(v)
+    out = np.empty(q.shape, np.float32)
+
+    def t4(a, dtype):
+        t = _lib.Tensor4()
+        t.data, t.dtype = a.ctypes.data, dtype
+        acc = 1
+        for i in range(3, -1, -1):
+            t.shape[i], t.stride[i] = a.shape[i], acc
+            acc *= a.shape[i]
+        return t
+    cq, ck, cv, co = t4(hq, _lib.BF16), t4(hk, _lib.BF16), t4(hv, _lib.BF16), t4(out, _lib.F32)
+    assert hq.nbytes + hk.nbytes + hv.nbytes + out.nbytes > (8 << 20)
+    for _ in range(2):  # the second call reuses the copy streams and the scratch buffers
+        out[:] = np.nan
+        rc = L.fusor_cuda_flash_attention_host(device.handle, ctypes.byref(cq), ctypes.byref(ck), ctypes.byref(cv),
+                                               ctypes.c_float(scale), None, _lib.MASK_CAUSAL, 0, ctypes.byref(co))
+        _lib.check(rc, device.handle)
+        mask = (fb.MaskCache().get_mask(S, 0, None, device), fb.MaskKind.QKMask)
+        assert np.array_equal(out, _run(device, q, k, v, scale, mask, dtype=1))
