@@ -333,36 +333,72 @@ struct CombineParams {
     int mode;
 };
 
+// One block per (query head, sequence): D / 4 column groups (float4) x DEC_CL record lanes.  Lane r merges records
+// r, r + DEC_CL, ... with an online rescale (independent loads, no pass over the maxima first); the lanes' states meet
+// in shared memory and the threads of lane 0 fold them.  A long sequence split over hundreds of CTAs (the 128 K-token
+// configuration: ~74 records per kv head) is merged by 8 lanes in parallel instead of one thread per column in series.
+constexpr int DEC_CL = 8;
+
 __global__ void decode_combine_kernel(const CombineParams P) {
+    __shared__ float4 sh_acc[DEC_CL][64];
+    __shared__ float2 sh_ml[DEC_CL][64];
     const int h = blockIdx.x, b = blockIdx.y;
     const int seq = b * P.Hkv + h / P.g, rr = h % P.g;
     const int s0 = P.seq_slot_begin[seq], s1 = P.seq_slot_begin[seq + 1];
-    // one pass with an online rescale: the loads of all records are independent of the arithmetic
-    for (int d = threadIdx.x; d < P.D; d += blockDim.x) {
-        float M = -INFINITY, L = 0.0f, acc = 0.0f;
-#pragma unroll 4
-        for (int s = s0; s < s1; ++s) {
-            const float2 ml = *reinterpret_cast<const float2*>(P.part_ml + ((long long)s * DEC_GP + rr) * 2);
-            const float o = P.part_o[((long long)s * DEC_GP + rr) * P.D + d];
-            if (ml.x == -INFINITY) continue;
-            const float Mn = fmaxf(M, ml.x);
-            const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
-            L = L * a0 + ml.y * a1;
-            acc = acc * a0 + o * a1;
-            M = Mn;
-        }
-        if (P.mode == 0) {
-            const long long idx = (long long)b * P.o_sb + (long long)h * P.o_sh + d;
-            const float v = acc / L;
-            if (P.out_dtype == 0) reinterpret_cast<float*>(P.out)[idx] = v;
-            else reinterpret_cast<__nv_bfloat16*>(P.out)[idx] = __float2bfloat16_rn(v);
+    const int groups = P.D >> 2;  // <= 64
+    const int dg = threadIdx.x % groups, lane = threadIdx.x / groups;
+    float M = -INFINITY, L = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 2
+    for (int s = s0 + lane; s < s1; s += DEC_CL) {
+        const float2 ml = *reinterpret_cast<const float2*>(P.part_ml + ((long long)s * DEC_GP + rr) * 2);
+        const float4 o = *reinterpret_cast<const float4*>(P.part_o + ((long long)s * DEC_GP + rr) * P.D + dg * 4);
+        if (ml.x == -INFINITY) continue;
+        const float Mn = fmaxf(M, ml.x);
+        const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
+        L = L * a0 + ml.y * a1;
+        acc.x = acc.x * a0 + o.x * a1;
+        acc.y = acc.y * a0 + o.y * a1;
+        acc.z = acc.z * a0 + o.z * a1;
+        acc.w = acc.w * a0 + o.w * a1;
+        M = Mn;
+    }
+    sh_acc[lane][dg] = acc;
+    sh_ml[lane][dg] = make_float2(M, L);
+    __syncthreads();
+    if (lane != 0) return;
+#pragma unroll
+    for (int r = 1; r < DEC_CL; ++r) {
+        const float2 ml = sh_ml[r][dg];
+        if (ml.x == -INFINITY) continue;
+        const float4 o = sh_acc[r][dg];
+        const float Mn = fmaxf(M, ml.x);
+        const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
+        L = L * a0 + ml.y * a1;
+        acc.x = acc.x * a0 + o.x * a1;
+        acc.y = acc.y * a0 + o.y * a1;
+        acc.z = acc.z * a0 + o.z * a1;
+        acc.w = acc.w * a0 + o.w * a1;
+        M = Mn;
+    }
+    const int d = dg * 4;
+    if (P.mode == 0) {
+        const long long idx = (long long)b * P.o_sb + (long long)h * P.o_sh + d;
+        const float inv = 1.0f / L;
+        if (P.out_dtype == 0) {
+            float* o = reinterpret_cast<float*>(P.out) + idx;
+            o[0] = acc.x * inv; o[1] = acc.y * inv; o[2] = acc.z * inv; o[3] = acc.w * inv;
         } else {
-            float* rec = reinterpret_cast<float*>(P.out) + ((long long)b * P.Hq + h) * (P.D + 2);
-            rec[2 + d] = acc;
-            if (d == 0) {
-                rec[0] = M * 0.6931471805599453f;
-                rec[1] = L;
-            }
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(P.out) + idx;
+            o[0] = __float2bfloat16_rn(acc.x * inv); o[1] = __float2bfloat16_rn(acc.y * inv);
+            o[2] = __float2bfloat16_rn(acc.z * inv); o[3] = __float2bfloat16_rn(acc.w * inv);
+        }
+    } else {
+        float* rec = reinterpret_cast<float*>(P.out) + ((long long)b * P.Hq + h) * (P.D + 2);
+        rec[2 + d] = acc.x; rec[3 + d] = acc.y; rec[4 + d] = acc.z; rec[5 + d] = acc.w;
+        if (dg == 0) {
+            rec[0] = M * 0.6931471805599453f;
+            rec[1] = L;
         }
     }
 }

@@ -1228,7 +1228,7 @@ static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fus
     C.part_o = c->part_o; C.part_ml = c->part_ml; C.seq_slot_begin = c->d_seq_slot_begin;
     C.out = out; C.out_dtype = out_dtype; C.o_sb = o_sb; C.o_sh = o_sh;
     C.Hq = Hq; C.Hkv = c->Hkv; C.g = g; C.D = c->D; C.mode = mode;
-    decode_combine_kernel<<<dim3(Hq, B), c->D, 0, ctx->stream>>>(C);
+    decode_combine_kernel<<<dim3(Hq, B), (c->D / 4) * DEC_CL, 0, ctx->stream>>>(C);
     return launch_check(ctx, "decode_combine_kernel");
 }
 
