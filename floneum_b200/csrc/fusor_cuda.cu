@@ -376,9 +376,15 @@ static bool tma_view_ok(const fusor_cuda_tensor4* t) {
 }
 
 static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
-                             const fusor_cuda_tensor4* v, float scale, int32_t mask_kind, const fusor_cuda_tensor4* out) {
+                             const fusor_cuda_tensor4* v, float scale, int32_t mask_kind, const fusor_cuda_tensor4* out,
+                             const fusor_cuda_tensor2* mask = nullptr) {
     if (S.D != PF_D) return false;
-    if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL || mask_kind == FUSOR_CUDA_MASK_SLIDING)) return false;
+    if (mask_kind == FUSOR_CUDA_MASK_BATCH_KEY) {
+        // [B, Skv] additive key mask with contiguous rows
+        if (!mask || mask->stride[1] != 1) return false;
+    } else if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL || mask_kind == FUSOR_CUDA_MASK_SLIDING)) {
+        return false;
+    }
     if (!tma_view_ok(q) || !tma_view_ok(k) || !tma_view_ok(v)) return false;
     if (!(scale > 0.0f) || !std::isfinite(scale)) return false;
     const int al = out->dtype == FUSOR_CUDA_F32 ? 4 : 8;
@@ -391,7 +397,8 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
 // p_mode: 0 = f16 P with an f16 copy of V (falls back to bf16 on the device when V overflows f16), 1 = bf16 P.
 static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
                               const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
-                              const fusor_cuda_tensor4* out, float* debug, int p_mode, int window = 0) {
+                              const fusor_cuda_tensor4* out, float* debug, int p_mode, int window = 0,
+                              const fusor_cuda_tensor2* key_mask = nullptr) {
     // Two query tiles per CTA with 128-key blocks once a (batch, head) has 256 rows or more; the 64-key kernel with
     // two CTAs per SM below that (and when asked for: p_mode bit 2, diagnostics).
     const bool two_tiles = S.Sq >= P2_ROWS && (debug == nullptr || (p_mode & 8)) && (p_mode & 4) == 0 && ctx->prefill_variant != 1;
@@ -428,7 +435,7 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
         TRY(make_tmap_bhsd(ctx, &tmV16, &v16, kv_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
         flag = ctx->d_flags + slot;
     }
-    PrefillParams P;
+    PrefillParams P{};
     P.out = out->data; P.out_dtype = out->dtype;
     for (int i = 0; i < 3; ++i) P.os[i] = out->stride[i];
     P.B = S.B; P.Hq = S.Hq; P.Hkv = S.Hkv; P.Sq = S.Sq; P.Skv = S.Skv;
@@ -441,6 +448,9 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.debug_values = (p_mode & 2) ? 0 : 1;
     P.debug_cta = p_mode >> 8;
     P.v_f16_overflow = flag;
+    P.kmask = key_mask ? static_cast<const float*>(key_mask->data) : nullptr;
+    P.kmask_stride = key_mask ? key_mask->stride[0] : 0;
+    P.kmask_mul = 1.0f / scale;
     const long long grid = (long long)P.n_q_tiles * S.Hq * S.B;
     if (grid > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "grid too large");
     if (two_tiles) {
@@ -458,7 +468,9 @@ extern "C" int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_c
     AttnShape S;
     TRY(validate_attention(ctx, q, k, v, mask, mask_kind, window, out, &S));
     DeviceGuard g(ctx->device);
-    if (prefill_eligible(S, q, k, v, scale, mask_kind, out)) return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, nullptr, 0, window);
+    if (prefill_eligible(S, q, k, v, scale, mask_kind, out, mask))
+        return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, nullptr, 0, window,
+                              mask_kind == FUSOR_CUDA_MASK_BATCH_KEY ? mask : nullptr);
     return launch_general(ctx, S, q, k, v, scale, mask, mask_kind, window, out);
 }
 
@@ -1393,7 +1405,7 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
     v16t.data = v16;
     set_contiguous(&v16t);
     TRY(make_tmap_bhsd(&local, &tmV16, &v16t, PF_BN, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
-    PrefillParams P;
+    PrefillParams P{};
     P.out = out->data; P.out_dtype = out->dtype;
     for (int i = 0; i < 3; ++i) P.os[i] = out->stride[i];
     P.B = S.B; P.Hq = S.Hq; P.Hkv = S.Hkv; P.Sq = S.Sq; P.Skv = S.Skv;

@@ -333,6 +333,13 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 tc_wait_ld();
                 if (tr && jj < 60) stamp(t * 512 + jj * 8 + 2);
                 const int k0 = (I.jb[t] + jj) * P2_BN;
+                if (P.kmask != nullptr) {
+                    // additive key mask of this batch row: (s + mask / scale) * scale = s * scale + mask; every thread of the
+                    // tile reads the same values (broadcast loads); keys past Skv are cut by the edge mask below
+                    const float* mk = P.kmask + (long long)I.b * P.kmask_stride;
+#pragma unroll
+                    for (int i = 0; i < P2_BN; ++i) s[i] = fmaf(__ldg(mk + min(k0 + i, P.Skv - 1)), P.kmask_mul, s[i]);
+                }
                 if (k0 + P2_BN - 1 > k_limit || k0 < k_first) {  // diagonal, ragged or window-edge block
 #pragma unroll
                     for (int i = 0; i < P2_BN; ++i)

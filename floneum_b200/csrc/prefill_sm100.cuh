@@ -66,6 +66,9 @@ struct PrefillParams {
     int debug_values;          // dump S / O / m / l values as well as the cycle stamps
     int debug_cta;             // which CTA is traced
     const int* v_f16_overflow; // written by the V pre-pass: non-zero when some |v| does not fit f16; null = no f16 copy
+    const float* kmask;        // optional additive key mask [B][Skv] f32 (MaskKind::BatchKeyMask), added to the scaled scores
+    long long kmask_stride;    // elements between batches
+    float kmask_mul;           // 1 / scale: the mask is added to the raw scores as mask / scale, before the common scaling
 };
 
 constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_Q_BYTES + 2 * PF_SBUF * (size_t)PF_KV_BYTES + 512 + 6 * 128 * 4;
@@ -273,6 +276,13 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 for (int i = 0; i < PF_CPT; ++i) P.debug[row * PF_DEBUG_ROW + half * PF_CPT + i] = s[i];
             }
             const int k0 = (j_begin + j) * PF_BN + half * PF_CPT;
+            if (P.kmask != nullptr) {
+                // additive key mask of this batch row: (s + mask / scale) * scale = s * scale + mask; every thread of the
+                // CTA reads the same values (broadcast loads); keys past Skv are cut by the edge mask below
+                const float* mk = P.kmask + (long long)b * P.kmask_stride;
+#pragma unroll
+                for (int i = 0; i < PF_CPT; ++i) s[i] = fmaf(__ldg(mk + min(k0 + i, P.Skv - 1)), P.kmask_mul, s[i]);
+            }
             if (k0 + PF_CPT - 1 > k_limit || k0 < k_first) {  // diagonal, ragged or window-edge tile: mask in the raw domain
 #pragma unroll
                 for (int i = 0; i < PF_CPT; ++i)

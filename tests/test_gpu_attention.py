@@ -349,3 +349,24 @@ def test_host_entry_point_pipelined_chunks_match_device_path(device):
         _lib.check(rc, device.handle)
         mask = (fb.MaskCache().get_mask(S, 0, None, device), fb.MaskKind.QKMask)
         assert np.array_equal(out, _run(device, q, k, v, scale, mask, dtype=1))
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,neg", [(3, 4, 2, 200, -np.inf), (2, 8, 8, 512, -10000.0), (4, 4, 1, 333, -np.inf)])
+def test_batch_key_mask_on_the_tensor_core_kernels(device, B, Hq, Hkv, S, neg):
+    """MaskKind::BatchKeyMask ([B, Skv] additive padding mask, bidirectional attention; rbert's Qwen embedding uses -10000,
+    models/rbert/src/raw/qwen/attention.rs:93-113) through the tcgen05 kernels (64-key kernel below 256 rows, two-tile
+    kernel from 256), against the composite with the same mask."""
+    fb = _mods()
+    q, k, v, scale = _bf16_case(900 + S, B, Hq, Hkv, S, S)
+    rng = np.random.default_rng(S)
+    lens = rng.integers(S // 3, S + 1, B)
+    lens[0] = S
+    mask = np.zeros((B, S), np.float32)
+    for b in range(B):
+        mask[b, lens[b]:] = neg
+    mt = fb.Tensor.from_slice(device, mask.shape, mask)
+    before = device.launch_count()
+    got = _run(device, q, k, v, scale, (mt, fb.MaskKind.BatchKeyMask), dtype=1)
+    assert device.launch_count() - before == 2, "V pre-pass + one tensor-core kernel, not the general kernel"
+    want = O.flash_attention(q, k, v, scale, mask, O.MASK_BATCH_KEY)
+    assert_close(got, want, what=f"batch key mask B{B} S{S} pad {neg}")
