@@ -345,6 +345,28 @@ class KvCache:
         self._batch = k.shape()[0]
         return q_rot, CachedKv(self, "k"), CachedKv(self, "v")
 
+    # ------------------------------------------------------------------ session export / import
+    def export_session(self) -> dict:
+        """The cache as host arrays: {"k", "v": f32 [B, Hkv, len, D], "max_sequence_len"} (what the reference's session
+        save would hold, models/kalosm-llama/src/session.rs:51-69, where it is stubbed out).  Values are the bf16-rounded
+        rows the pages hold; an empty cache exports zero-length arrays."""
+        n = self.current_seq_len()
+        if n == 0:
+            z = np.zeros((self._batch, self._num_kv_heads, 0, self._head_dim), np.float32)
+            return {"k": z, "v": z.copy(), "max_sequence_len": self.max_sequence_len}
+        k, v = self._dense(F32)
+        return {"k": k.as_slice(), "v": v.as_slice(), "max_sequence_len": self.max_sequence_len}
+
+    @classmethod
+    def import_session(cls, device: Device, session: dict) -> "KvCache":
+        """Rebuilds a cache from `export_session`'s dictionary (dense rows go back into pages through `append`)."""
+        cache = cls(2, int(session["max_sequence_len"]))
+        k, v = np.asarray(session["k"], np.float32), np.asarray(session["v"], np.float32)
+        assert k.shape == v.shape and k.ndim == 4, "session k and v must be [B, Hkv, len, D] arrays of one shape"
+        if k.shape[2] > 0:
+            cache.append(device, Tensor.from_slice(device, k.shape, k), Tensor.from_slice(device, v.shape, v))
+        return cache
+
     def _dense(self, dtype: int) -> Tuple[Tensor, Tensor]:
         return self._paged.gather(self._batch, self.current_seq_len(), dtype)
 

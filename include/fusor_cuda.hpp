@@ -400,4 +400,73 @@ inline Tensor<4> flash_attention(const Tensor<4>& q, const CachedKv& k, const Ca
     return k.cache->attend(q, scale, mask, out_dtype);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Rotary embedding (fusor-ml/fusor/src/composite/rope.rs:38-118, 180-265) and the output projection that follows
+// attention (models/kalosm-llama/src/raw/attention_layer.rs:450-454, fusor-ml/fusor/src/layers/linear.rs:72-115).
+inline std::vector<float> base_inverse_frequency(size_t dim, float rope_theta) {  // rope.rs:189-194
+    std::vector<float> f;
+    for (size_t i = 0; i < dim; i += 2) f.push_back(1.0f / std::pow(rope_theta, (float)i / (float)dim));
+    return f;
+}
+
+// Tensor::rope (interleaved = false) / Tensor::rope_interleaved (true) with table rows start_pos .. start_pos + n
+inline Tensor<4> rope(const Tensor<4>& x, const Tensor<2>& cos, const Tensor<2>& sin, size_t start_pos = 0, bool interleaved = false) {
+    if (cos.shape() != sin.shape() || cos.shape()[1] * 2 != x.shape()[3]) throw std::logic_error("rope: cos / sin must be [context, head_dim / 2]");
+    Tensor<4> out = Tensor<4>::empty(x.device(), x.shape(), x.dtype());
+    const fusor_cuda_tensor4 vx = detail::view4(x), vo = detail::view4(out);
+    x.device()->check(fusor_cuda_rope(x.device()->raw(), &vx, static_cast<const float*>(cos.data()), static_cast<const float*>(sin.data()),
+                                      (int32_t)cos.shape()[0], (int32_t)start_pos, interleaved ? 1 : 0, &vo));
+    return out;
+}
+
+class RopeCache {
+  public:
+    // RopeCache::new (rope.rs:197-219)
+    RopeCache(size_t head_dim, size_t context_length, float rope_theta, const DevicePtr& dev) {
+        const std::vector<float> inv = base_inverse_frequency(head_dim, rope_theta);
+        std::vector<float> c(context_length * inv.size()), s(c.size());
+        for (size_t p = 0; p < context_length; ++p)
+            for (size_t i = 0; i < inv.size(); ++i) {
+                const float a = (float)p * inv[i];
+                c[p * inv.size() + i] = std::cos(a);
+                s[p * inv.size() + i] = std::sin(a);
+            }
+        cos_ = Tensor<2>::from_slice(dev, {(int64_t)context_length, (int64_t)inv.size()}, c);
+        sin_ = Tensor<2>::from_slice(dev, {(int64_t)context_length, (int64_t)inv.size()}, s);
+    }
+    RopeCache(Tensor<2> cos, Tensor<2> sin) : cos_(std::move(cos)), sin_(std::move(sin)) {}  // from_parts
+    std::pair<Tensor<4>, Tensor<4>> forward(const Tensor<4>& q, const Tensor<4>& k, size_t start_pos) const {
+        return {rope(q, cos_, sin_, start_pos, false), rope(k, cos_, sin_, start_pos, false)};
+    }
+    std::pair<Tensor<4>, Tensor<4>> forward_interleaved(const Tensor<4>& q, const Tensor<4>& k, size_t start_pos) const {
+        return {rope(q, cos_, sin_, start_pos, true), rope(k, cos_, sin_, start_pos, true)};
+    }
+    const Tensor<2>& cos() const { return cos_; }
+    const Tensor<2>& sin() const { return sin_; }
+
+  private:
+    Tensor<2> cos_, sin_;
+};
+
+// attn [B,Hq,S,D] (bf16) -> [B,S,N]: transpose(1, 2).reshape([b, q_len, hidden]) then Linear::forward with a dense bf16
+// weight [N, Hq*D] and an optional f32 bias [N]
+inline Tensor<3> out_proj(const Tensor<4>& attn, const Tensor<2>& weight, const Tensor<1>* bias = nullptr, DType out_dtype = DType::F32) {
+    const auto a = attn.shape();
+    const auto w = weight.shape();
+    if (w[1] != a[1] * a[3]) throw std::logic_error("out_proj: weight in_features do not match heads * head_dim");
+    if (bias && (bias->shape()[0] != w[0] || bias->dtype() != DType::F32)) throw std::logic_error("out_proj: bias must be f32 [out_features]");
+    Tensor<3> out = Tensor<3>::empty(attn.device(), {a[0], a[2], w[0]}, out_dtype);
+    const fusor_cuda_tensor4 va = detail::view4(attn);
+    fusor_cuda_tensor4 vw{}, vo{};
+    vw.data = weight.data(); vw.dtype = (int32_t)weight.dtype();
+    vw.shape[0] = 1; vw.shape[1] = 1; vw.shape[2] = w[0]; vw.shape[3] = w[1];
+    vw.stride[0] = vw.stride[1] = w[0] * w[1]; vw.stride[2] = w[1]; vw.stride[3] = 1;
+    vo.data = out.data(); vo.dtype = (int32_t)out_dtype;
+    vo.shape[0] = a[0]; vo.shape[1] = 1; vo.shape[2] = a[2]; vo.shape[3] = w[0];
+    vo.stride[0] = vo.stride[1] = a[2] * w[0]; vo.stride[2] = w[0]; vo.stride[3] = 1;
+    attn.device()->check(fusor_cuda_attention_out_proj(attn.device()->raw(), &va, &vw,
+                                                       bias ? static_cast<const float*>(bias->data()) : nullptr, &vo));
+    return out;
+}
+
 }  // namespace fusor_cuda

@@ -138,11 +138,52 @@ static void gpu_cases() {
     }
 }
 
+// fusor-ml/fusor/src/composite/rope.rs:272-352 (test_rope_cpu / test_rope_interleaved_cpu): [1,3,11,64] of sin(i % 64),
+// RopeCache::new(64, 11, 10000): shape kept, values finite; here also position 0 unchanged and pair norms kept.
+// The output projection: an identity weight returns the head-interleaving transpose.
+static void gpu_neighbours(const DevicePtr& dev) {
+    std::vector<float> x(1 * 3 * 11 * 64);
+    for (size_t i = 0; i < x.size(); ++i) x[i] = std::sin((float)(i % 64));
+    Tensor<4> t = Tensor<4>::from_slice(dev, {1, 3, 11, 64}, x);
+    RopeCache rc(64, 11, 10000.0f, dev);
+    for (int inter = 0; inter < 2; ++inter) {
+        auto qk = inter ? rc.forward_interleaved(t, t, 0) : rc.forward(t, t, 0);
+        CHECK((qk.first.shape() == std::array<int64_t, 4>{1, 3, 11, 64}));
+        const std::vector<float> y = qk.second.as_slice();
+        bool finite = true, row0 = true, norms = true;
+        for (size_t i = 0; i < y.size(); ++i) finite = finite && std::isfinite(y[i]);
+        for (size_t h = 0; h < 3; ++h)
+            for (size_t d = 0; d < 64; ++d) row0 = row0 && y[h * 11 * 64 + d] == x[h * 11 * 64 + d];
+        for (size_t r = 0; r < 33; ++r)
+            for (size_t i = 0; i < 32; ++i) {
+                const size_t a = inter ? r * 64 + 2 * i : r * 64 + i, b = inter ? a + 1 : a + 32;
+                norms = norms && std::fabs((y[a] * y[a] + y[b] * y[b]) - (x[a] * x[a] + x[b] * x[b])) < 1e-5f;
+            }
+        CHECK(finite);
+        CHECK(row0);
+        CHECK(norms);
+    }
+    // out_proj with an identity weight: out[b, s, h * D + d] = attn[b, h, s, d]
+    const int64_t Hq = 2, S = 40, D = 64, K = Hq * D;
+    std::vector<float> a(Hq * S * D), eye(K * K, 0.0f);
+    for (size_t i = 0; i < a.size(); ++i) a[i] = (float)((int)(i % 17) - 8) * 0.25f;  // exact in bf16
+    for (int64_t i = 0; i < K; ++i) eye[i * K + i] = 1.0f;
+    Tensor<4> attn = Tensor<4>::from_slice(dev, {1, Hq, S, D}, a, DType::BF16);
+    Tensor<2> w = Tensor<2>::from_slice(dev, {K, K}, eye, DType::BF16);
+    const std::vector<float> o = out_proj(attn, w).as_slice();
+    bool same = o.size() == (size_t)(S * K);
+    for (int64_t s = 0; s < S && same; ++s)
+        for (int64_t h = 0; h < Hq; ++h)
+            for (int64_t d = 0; d < D; ++d) same = same && o[s * K + h * D + d] == a[(h * S + s) * D + d];
+    CHECK(same);
+}
+
 int main(int argc, char** argv) {
     host_only();
     if (!(argc > 1 && std::strcmp(argv[1], "--no-gpu") == 0)) {
         try {
             gpu_cases();
+            gpu_neighbours(Device::gpu(0));
         } catch (const std::exception& e) {
             std::printf("FAILED with exception: %s\n", e.what());
             ++failures;

@@ -215,3 +215,29 @@ def test_bounded_wait_reports_timeout_and_context_survives(device):
     out = fb.Tensor.from_slice(device, q.shape, q).flash_attention(fb.Tensor.from_slice(device, q.shape, q),
                                                                    fb.Tensor.from_slice(device, q.shape, q), 0.25).as_slice()
     assert np.allclose(out, 1.0, atol=1e-6)
+
+
+def test_session_export_import_round_trip(device):
+    """KvCache.export_session / import_session (the reference's session save of the cache is stubbed out,
+    models/kalosm-llama/src/session.rs:51-69): the re-imported cache holds the same rows and decodes to the same bits."""
+    from floneum_b200 import KvCache, Tensor
+    rng = np.random.default_rng(21)
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    cache = KvCache.new(2, 96)
+    for n in (70, 1, 40):  # the last append overflows max_sequence_len: the oldest rows are dropped
+        k = O.bf16_round(rng.standard_normal((B, Hkv, n, D)).astype(np.float32))
+        v = O.bf16_round(rng.standard_normal((B, Hkv, n, D)).astype(np.float32))
+        ck, cv = cache.append(device, Tensor.from_slice(device, k.shape, k), Tensor.from_slice(device, v.shape, v))
+    assert cache.current_seq_len() == 96
+    sess = cache.export_session()
+    assert sess["k"].shape == (B, Hkv, 96, D)
+    again = KvCache.import_session(device, sess)
+    assert again.current_seq_len() == 96
+    s2 = again.export_session()
+    assert np.array_equal(s2["k"], sess["k"]) and np.array_equal(s2["v"], sess["v"])
+    q = O.bf16_round(rng.standard_normal((B, Hq, 1, D)).astype(np.float32))
+    tq = Tensor.from_slice(device, q.shape, q)
+    a = tq.flash_attention(ck, cv, D ** -0.5).as_slice()
+    b = tq.flash_attention(again.k(), again.v(), D ** -0.5).as_slice()
+    assert np.array_equal(a, b)
+    assert_close(a, O.flash_attention(q, sess["k"], sess["v"], D ** -0.5))
