@@ -192,6 +192,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the decode line and the CPU baseline")
     ap.add_argument("--shard-of", type=int, default=0, help="for profiler captures on one GPU: run rank 0's shard of an "
                     "N-rank job (no process group; the line is marked as a shard)")
+    ap.add_argument("--nccl-gather", action="store_true", help="cfg4 on several GPUs: exchange the split-KV records with an NCCL "
+                    "all-gather between two kernels instead of the library's own peer-memory push + merge")
     ap.add_argument("--no-graph", action="store_true", help="decode workloads: time eager launches instead of a CUDA graph replay")
     ap.add_argument("--quick", action="store_true", help="for profiler captures: no clock-settling loop, no e2e, no extras")
     ap.add_argument("--small", action="store_true", help="for profiler captures: a scaled-down case of the workload "
@@ -370,12 +372,16 @@ def main():
             gathered = torch.empty((world, B, q1 - q0, D + 2), dtype=torch.float32, device=cuda)
             out3 = torch.empty((B, q1 - q0, D), dtype=torch.float32, device=cuda)
             tpart, tgath, tout3 = (fb.Tensor.from_torch(dev, t) for t in (part, gathered, out3))
+            exchange = None if args.nccl_gather else sharding.PeerExchange(dev, rank, world, B * (q1 - q0) * (D + 2))
 
         def step():
             if chunked and use_dist:
                 cache.decode_partial(tq, w.scale, tpart)
-                dist.all_gather_into_tensor(gathered, part)
-                lse_combine(dev, tgath, tout3)
+                if exchange is not None:
+                    exchange.lse_combine(tpart, tout3)  # peer stores + epoch flags + merge, inside the library's kernels
+                else:
+                    dist.all_gather_into_tensor(gathered, part)
+                    lse_combine(dev, tgath, tout3)
                 return out3
             cache.decode(tq, w.scale, to)
             return out
@@ -415,7 +421,8 @@ def main():
             barrier()
             launches = dev.launch_count() - launches0
             if graph is not None:
-                launches = args.steps * (3 if (chunked and use_dist) else 2)  # kernels of ours inside each replay
+                # kernels of ours inside each replay: split-KV + combine (+ push + merge, or + merge after the NCCL gather)
+                launches = args.steps * ((4 if exchange is not None else 3) if (chunked and use_dist) else 2)
             dev.synchronize()
         ms = [a.elapsed_time(b) for a, b in evs]
         mean_ms = max_over_ranks(statistics.mean(ms))
@@ -625,7 +632,9 @@ def main():
             w = W.cfg4(rank=rank, world=world)
             r = run_decode(w, "cfg4", shard_heads=False, chunked=True)
             if world > 1:
-                r["config"]["sharding"] = f"KV sequence split into {world} contiguous chunks, partials all-gathered over NCCL"
+                r["config"]["sharding"] = (f"KV sequence split into {world} contiguous chunks, " +
+                                           ("partials all-gathered over NCCL" if args.nccl_gather else
+                                            "partial records pushed to every rank over peer memory and merged (no collective call)"))
                 r["value"] = r["value"]  # bytes_all already counts every rank's chunk
         got = r.pop("_got"); qn = r.pop("_q"); k0, k1 = r.pop("_krange")
         r["parity"] = {"finite": bool(np.isfinite(got).all())}

@@ -64,6 +64,11 @@ SIGNATURES = {
     "fusor_cuda_kvcache_destroy": (c_int32, [c_void_p]),
     "fusor_cuda_kvcache_reset": (c_int32, [c_void_p]),
     "fusor_cuda_kvcache_append": (c_int32, [c_void_p, _T4, _T4]),
+    "fusor_cuda_exchange_create": (c_int32, [c_void_p, c_int32, c_int32, c_int64, POINTER(c_void_p)]),
+    "fusor_cuda_exchange_handle": (c_int32, [c_void_p, c_void_p]),
+    "fusor_cuda_exchange_connect": (c_int32, [c_void_p, c_void_p]),
+    "fusor_cuda_exchange_destroy": (c_int32, [c_void_p]),
+    "fusor_cuda_exchange_lse_combine": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "fusor_cuda_attention_out_proj": (c_int32, [c_void_p, _T4, _T4, c_void_p, _T4]),
     "fusor_cuda_rope": (c_int32, [c_void_p, _T4, c_void_p, c_void_p, c_int32, c_int32, c_int32, _T4]),
     "fusor_cuda_kvcache_rope_append": (c_int32, [c_void_p, _T4, _T4, _T4, c_void_p, c_void_p, c_int32, c_int32, c_int32, _T4]),

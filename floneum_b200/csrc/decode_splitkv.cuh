@@ -336,8 +336,8 @@ struct CombineParams {
 // One block per (query head, sequence): D / 4 column groups (float4) x DEC_CL record lanes.  Lane r merges records
 // r, r + DEC_CL, ... with an online rescale (independent loads, no pass over the maxima first); the lanes' states meet
 // in shared memory and the threads of lane 0 fold them.  A long sequence split over hundreds of CTAs (the 128 K-token
-// configuration: ~74 records per kv head) is merged by 8 lanes in parallel instead of one thread per column in series.
-constexpr int DEC_CL = 8;
+// configuration: ~74 records per kv head) is merged by 16 lanes in parallel instead of one thread per column in series.
+constexpr int DEC_CL = 16;  // most record lanes a block may have (the host picks 2, 8 or 16 by the records per kv head)
 
 __global__ void decode_combine_kernel(const CombineParams P) {
     __shared__ float4 sh_acc[DEC_CL][64];
@@ -347,10 +347,11 @@ __global__ void decode_combine_kernel(const CombineParams P) {
     const int s0 = P.seq_slot_begin[seq], s1 = P.seq_slot_begin[seq + 1];
     const int groups = P.D >> 2;  // <= 64
     const int dg = threadIdx.x % groups, lane = threadIdx.x / groups;
+    const int lanes = blockDim.x / groups;
     float M = -INFINITY, L = 0.0f;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 2
-    for (int s = s0 + lane; s < s1; s += DEC_CL) {
+    for (int s = s0 + lane; s < s1; s += lanes) {
         const float2 ml = *reinterpret_cast<const float2*>(P.part_ml + ((long long)s * DEC_GP + rr) * 2);
         const float4 o = *reinterpret_cast<const float4*>(P.part_o + ((long long)s * DEC_GP + rr) * P.D + dg * 4);
         if (ml.x == -INFINITY) continue;
@@ -367,8 +368,7 @@ __global__ void decode_combine_kernel(const CombineParams P) {
     sh_ml[lane][dg] = make_float2(M, L);
     __syncthreads();
     if (lane != 0) return;
-#pragma unroll
-    for (int r = 1; r < DEC_CL; ++r) {
+    for (int r = 1; r < lanes; ++r) {
         const float2 ml = sh_ml[r][dg];
         if (ml.x == -INFINITY) continue;
         const float4 o = sh_acc[r][dg];

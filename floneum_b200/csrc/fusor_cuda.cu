@@ -22,6 +22,7 @@
 #include "prefill_sm100.cuh"
 #include "prefill2_sm100.cuh"
 #include "oproj_sm100.cuh"
+#include "peer_exchange.cuh"
 #include "rope_append.cuh"
 
 using namespace fusor;
@@ -1240,7 +1241,10 @@ static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fus
     C.part_o = c->part_o; C.part_ml = c->part_ml; C.seq_slot_begin = c->d_seq_slot_begin;
     C.out = out; C.out_dtype = out_dtype; C.o_sb = o_sb; C.o_sh = o_sh;
     C.Hq = Hq; C.Hkv = c->Hkv; C.g = g; C.D = c->D; C.mode = mode;
-    decode_combine_kernel<<<dim3(Hq, B), (c->D / 4) * DEC_CL, 0, ctx->stream>>>(C);
+    // record lanes per block: a kv head of a short sequence has one or two records, a 128 K-token sequence ~74
+    const int per_head = (c->n_slots + B * c->Hkv - 1) / (B * c->Hkv);
+    const int lanes = per_head <= 4 ? 2 : per_head <= 32 ? 8 : DEC_CL;
+    decode_combine_kernel<<<dim3(Hq, B), (c->D / 4) * lanes, 0, ctx->stream>>>(C);
     return launch_check(ctx, "decode_combine_kernel");
 }
 
@@ -1287,6 +1291,122 @@ extern "C" int32_t fusor_cuda_flash_attention_decode_host(fusor_cuda_ctx* ctx, f
     TRY(fusor_cuda_flash_attention_decode(ctx, cache, &dq, scale, &dout));
     CUDA_TRY(ctx, cudaMemcpyAsync(out->data, dout.data, ob, cudaMemcpyDeviceToHost, ctx->stream));
     return check_device_error(ctx);
+}
+
+// =============================================================================== peer exchange (KV-chunk decode over several GPUs)
+struct fusor_cuda_exchange {
+    fusor_cuda_ctx* ctx = nullptr;
+    int world = 0, rank = 0;
+    size_t slot_floats = 0;          // capacity of one rank's records
+    float* slots = nullptr;          // local: [2][world][slot_floats]
+    unsigned long long* flags = nullptr;  // local: [2][world], inside the same allocation
+    unsigned int* done = nullptr;    // local: [world + 1] block counters of the push kernel, then the epoch counter (u64)
+    unsigned long long* epoch_dev = nullptr;
+    void* base = nullptr;            // the local allocation that is exported
+    size_t flags_off = 0;
+    void* peer_base[PX_MAX_WORLD] = {};  // every rank's allocation as mapped here (own entry = base)
+    bool connected = false;
+};
+
+extern "C" int32_t fusor_cuda_exchange_create(fusor_cuda_ctx* ctx, int32_t world, int32_t rank, int64_t slot_floats,
+                                              fusor_cuda_exchange** out) {
+    if (!ctx || !out) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (world < 1 || world > PX_MAX_WORLD || rank < 0 || rank >= world || slot_floats <= 0 || slot_floats % 4 != 0)
+        return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "world 1..%d, rank inside it, slot_floats a positive multiple of 4", PX_MAX_WORLD);
+    DeviceGuard g(ctx->device);
+    fusor_cuda_exchange* ex = new fusor_cuda_exchange();
+    ex->ctx = ctx; ex->world = world; ex->rank = rank; ex->slot_floats = (size_t)slot_floats;
+    ex->flags_off = align256(2 * (size_t)world * ex->slot_floats * 4);
+    const size_t bytes = ex->flags_off + align256(2 * (size_t)world * 8);
+    if (cudaMalloc(&ex->base, bytes) != cudaSuccess || cudaMemset(ex->base, 0, bytes) != cudaSuccess ||
+        cudaMalloc(&ex->done, 256) != cudaSuccess || cudaMemset(ex->done, 0, 256) != cudaSuccess) {
+        cudaError_t e = cudaGetLastError();
+        if (ex->base) cudaFree(ex->base);
+        if (ex->done) cudaFree(ex->done);
+        delete ex;
+        return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "exchange allocation failed: %s", cudaGetErrorString(e));
+    }
+    ex->slots = static_cast<float*>(ex->base);
+    ex->flags = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(ex->base) + ex->flags_off);
+    ex->epoch_dev = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(ex->done) + 128);
+    ex->peer_base[rank] = ex->base;
+    ex->connected = world == 1;
+    *out = ex;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_exchange_handle(fusor_cuda_exchange* ex, void* handle64) {
+    if (!ex || !handle64) return fail(ex ? ex->ctx : nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    DeviceGuard g(ex->ctx->device);
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(ex->ctx, cudaIpcGetMemHandle(&h, ex->base));
+    std::memcpy(handle64, &h, 64);
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_exchange_connect(fusor_cuda_exchange* ex, const void* handles) {
+    if (!ex || !handles) return fail(ex ? ex->ctx : nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    fusor_cuda_ctx* ctx = ex->ctx;
+    DeviceGuard g(ctx->device);
+    for (int r = 0; r < ex->world; ++r) {
+        if (r == ex->rank || ex->peer_base[r]) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, static_cast<const uint8_t*>(handles) + (size_t)r * 64, 64);
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "cannot map rank %d's exchange buffer: %s", r, cudaGetErrorString(e));
+        }
+        ex->peer_base[r] = p;
+    }
+    ex->connected = true;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_exchange_destroy(fusor_cuda_exchange* ex) {
+    if (!ex) return FUSOR_CUDA_OK;
+    DeviceGuard g(ex->ctx->device);
+    cudaStreamSynchronize(ex->ctx->stream);
+    for (int r = 0; r < ex->world; ++r)
+        if (r != ex->rank && ex->peer_base[r]) cudaIpcCloseMemHandle(ex->peer_base[r]);
+    if (ex->base) cudaFree(ex->base);
+    if (ex->done) cudaFree(ex->done);
+    delete ex;
+    return FUSOR_CUDA_OK;
+}
+
+// Pushes `n_floats` of this rank's records into slot `rank` of every rank and merges all ranks' records
+// ([n_rows][head_dim + 2] each) into out [n_rows][head_dim].  Collective: every rank calls it once per step.
+extern "C" int32_t fusor_cuda_exchange_lse_combine(fusor_cuda_exchange* ex, const float* records, int64_t n_rows,
+                                                   int32_t head_dim, float* out) {
+    if (!ex || !records || !out) return fail(ex ? ex->ctx : nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    fusor_cuda_ctx* ctx = ex->ctx;
+    if (!ex->connected) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "exchange is not connected to its peers");
+    const long long n_floats = n_rows * (head_dim + 2);
+    if (n_rows <= 0 || head_dim <= 0 || n_floats > (long long)ex->slot_floats || n_floats % 4 != 0)
+        return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "records (%lld floats) do not fit the exchange slots (%lld) or are not a multiple of 4",
+                    n_floats, (long long)ex->slot_floats);
+    if (reinterpret_cast<uintptr_t>(records) % 16) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "records must be 16-byte aligned");
+    DeviceGuard g(ctx->device);
+    PeerPushParams P{};
+    P.src = reinterpret_cast<const float4*>(records);
+    P.n_vec = n_floats / 4;
+    P.world = ex->world; P.rank = ex->rank;
+    P.flags_off = ex->flags_off; P.slot_floats = ex->slot_floats;
+    P.epoch = ex->epoch_dev; P.done = ex->done;
+    for (int r = 0; r < ex->world; ++r) P.base[r] = static_cast<uint8_t*>(ex->peer_base[r]);
+    const unsigned blocks = (unsigned)std::max<long long>(1, std::min<long long>((P.n_vec + 255) / 256, 8));
+    peer_push_kernel<<<dim3(blocks, ex->world), 256, 0, ctx->stream>>>(P);
+    TRY(launch_check(ctx, "peer_push_kernel"));
+    PeerMergeParams M{};
+    M.slots = ex->slots; M.flags = ex->flags; M.epoch = ex->epoch_dev; M.slot_floats = ex->slot_floats;
+    M.world = ex->world; M.D = head_dim; M.n_rows = n_rows; M.out = out; M.err = ctx->d_err;
+    M.wait_limit_cycles = FUSOR_WAIT_LIMIT_CYCLES;
+    peer_merge_kernel<<<(unsigned)n_rows, std::min(head_dim, 256), 0, ctx->stream>>>(M);
+    return launch_check(ctx, "peer_merge_kernel");
 }
 
 // =============================================================================== wait-limit self test

@@ -53,6 +53,55 @@ def all_gather_partials(partial, group=None):
     return out
 
 
+class PeerExchange:
+    """This rank's end of the peer-memory record exchange (`fusor_cuda_exchange_*`): every rank's buffer is mapped into
+    every other rank's address space once (handles travel through torch.distributed), after which a step's records
+    move as peer stores inside the library's own kernels, with no collective call."""
+
+    def __init__(self, device, rank: int, world: int, slot_floats: int, group=None):
+        import ctypes
+        from . import _lib
+        self.device, self.rank, self.world = device, rank, world
+        self._L = _lib.load()
+        h = ctypes.c_void_p()
+        _lib.check(self._L.fusor_cuda_exchange_create(device.handle, world, rank, (slot_floats + 3) // 4 * 4, ctypes.byref(h)),
+                   device.handle)
+        self._h = h
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            mine = ctypes.create_string_buffer(64)
+            _lib.check(self._L.fusor_cuda_exchange_handle(self._h, mine), device.handle)
+            t = torch.frombuffer(bytearray(mine.raw), dtype=torch.uint8).to(f"cuda:{device.ordinal}")
+            allh = torch.empty(world * 64, dtype=torch.uint8, device=t.device)
+            dist.all_gather_into_tensor(allh, t, group=group)
+            blob = bytes(allh.cpu().numpy().tobytes())
+            _lib.check(self._L.fusor_cuda_exchange_connect(self._h, blob), device.handle)
+            dist.barrier(group=group)  # nobody pushes before everybody has mapped
+
+    def lse_combine(self, records, out):
+        """records: Tensor f32 [rows..., D+2] of this rank; out: Tensor f32 [rows..., D].  Collective."""
+        from . import _lib
+        shape = records.shape()
+        d = shape[-1] - 2
+        n_rows = 1
+        for x in shape[:-1]:
+            n_rows *= x
+        _lib.check(self._L.fusor_cuda_exchange_lse_combine(self._h, records.ptr, n_rows, d, out.ptr), self.device.handle)
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None) and self.device.handle:
+            self._L.fusor_cuda_exchange_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def decode_kv_chunks(device, cache, q, scale: float, group=None):
     """Long-context decode over KV chunks: local split-KV partial -> all-gather -> log-sum-exp merge.
 

@@ -232,6 +232,27 @@ int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcach
  * partial f32 [B][Hq][D+2] = { m = max scaled score, l = sum exp(s - m), O[D] = sum exp(s - m) v }. */
 int32_t fusor_cuda_flash_attention_decode_partial(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
                                                   const fusor_cuda_tensor4* q, float scale, float* partial);
+/* ------------------------------------------------------------------------------------------------
+ * Exchange of split-KV records between the GPUs of one node over peer memory (no counterpart in the reference, which
+ * has no multi-GPU path).  Each rank owns a buffer of [2 parities][world] record slots and epoch flags; the ranks map
+ * one another's buffers (CUDA IPC over NVLink) and a step's records travel as plain peer stores followed by a
+ * system-scope release of the step's epoch; the merge kernel waits for all epochs with a bound (TIMEOUT status, wait
+ * site 70, if a peer never publishes).  Replaces an all-gather between the partial and the merge kernels.
+ *   create      : allocates this rank's buffer; slot_floats = capacity of one rank's records (multiple of 4)
+ *   handle      : 64-byte handle of the local buffer, to be sent to every rank by the caller's own transport
+ *   connect     : handles of all ranks, [world][64] bytes in rank order (own entry ignored)
+ *   lse_combine : collective, stream-ordered, graph-capturable.  records f32 [n_rows][head_dim + 2] = { m (natural-log
+ *                 units), l, O[head_dim] } of this rank -> out f32 [n_rows][head_dim], merged over all ranks as
+ *                 fusor_cuda_lse_combine does. */
+typedef struct fusor_cuda_exchange fusor_cuda_exchange;
+int32_t fusor_cuda_exchange_create(fusor_cuda_ctx* ctx, int32_t world, int32_t rank, int64_t slot_floats,
+                                   fusor_cuda_exchange** out);
+int32_t fusor_cuda_exchange_handle(fusor_cuda_exchange* ex, void* handle64);
+int32_t fusor_cuda_exchange_connect(fusor_cuda_exchange* ex, const void* handles);
+int32_t fusor_cuda_exchange_destroy(fusor_cuda_exchange* ex);
+int32_t fusor_cuda_exchange_lse_combine(fusor_cuda_exchange* ex, const float* records, int64_t n_rows, int32_t head_dim,
+                                        float* out);
+
 /* Output projection right after attention (next-row F1): out[b, s, :] = W . flatten_h,d(attn[b, :, s, :]) + bias, the
  * reference's attn_output.transpose(1, 2).reshape([b, q_len, hidden]) followed by Linear::forward
  * (models/kalosm-llama/src/raw/attention_layer.rs:450-454, fusor-ml/fusor/src/layers/linear.rs:72-115; the reference

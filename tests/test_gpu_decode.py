@@ -241,3 +241,22 @@ def test_session_export_import_round_trip(device):
     b = tq.flash_attention(again.k(), again.v(), D ** -0.5).as_slice()
     assert np.array_equal(a, b)
     assert_close(a, O.flash_attention(q, sess["k"], sess["v"], D ** -0.5))
+
+
+def test_peer_exchange_world_of_one_merges_like_lse_combine(device):
+    """The peer-memory exchange with a single rank: the push goes to the rank's own slots, the merge waits for its own
+    epoch; repeated steps alternate the slot parity.  (Two or more ranks need as many GPUs: bench.py --workload cfg4.)"""
+    from floneum_b200 import Tensor
+    from floneum_b200.sharding import PeerExchange
+    rng = np.random.default_rng(33)
+    rows, D = 64, 128
+    ex = PeerExchange(device, 0, 1, rows * (D + 2))
+    for step in range(3):
+        rec = rng.standard_normal((rows, D + 2)).astype(np.float32)
+        rec[:, 1] = np.abs(rec[:, 1]) + 0.5
+        out = Tensor.zeros(device, (rows, D))
+        ex.lse_combine(Tensor.from_slice(device, rec.shape, rec), out)
+        got = out.as_slice()
+        want = O.lse_combine(rec[None])
+        assert np.abs(got - want).max() < 1e-5, step
+    ex.close()
