@@ -331,8 +331,8 @@ def main():
             "value": value, "unit": "TFLOP/s", "ms_per_step": total_ms / args.steps, "gpu_launches": launches,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          # dram read+write of one launch, scaled by (batch, head) pairs from the ncu capture of the
-                         # B2 Hq16 case (68.8 MB for 32 pairs; profiles/prefill_sm100_kernel_cfg2.md)
-                         "traffic": 68.8e6 * (B * (q1 - q0)) / 32.0 if D == 128 and S == 4096 else None,
+                         # B2 Hq16 case (68.2 MB for 32 pairs)
+                         "traffic": 68.2e6 * (B * (q1 - q0)) / 32.0 if D == 128 and S == 4096 else None,
                          "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
                          "frac_of_burst_peak": achieved / peaks["tensor_burst"], "burst_peak": peaks["tensor_burst"],
                          "frac_of_nominal_2250": achieved / 2250.0,
@@ -448,7 +448,6 @@ def main():
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
                              "frac": achieved / peaks["hbm"],
                              # ncu capture of the B16 case: dram read+write = 1.02 x the algorithmic bytes, scaled by bytes
-                             # (profiles/decode_splitkv_kernel_cfg3.md)
                              "traffic": bytes_rank * 1.02, "peak_source": f"{peaks['source']} (device copy)",
                              "frac_of_nominal_8000": achieved / 8000.0},
                 "config": {"workload": f"{tag}: paged GQA decode B{B} Hq{Hq} Hkv{Hkv_all} D{D}, 16-token pages, "

@@ -253,7 +253,7 @@ int32_t fusor_cuda_exchange_destroy(fusor_cuda_exchange* ex);
 int32_t fusor_cuda_exchange_lse_combine(fusor_cuda_exchange* ex, const float* records, int64_t n_rows, int32_t head_dim,
                                         float* out);
 
-/* Output projection right after attention (next-row F1): out[b, s, :] = W . flatten_h,d(attn[b, :, s, :]) + bias, the
+/* Output projection right after attention: out[b, s, :] = W . flatten_h,d(attn[b, :, s, :]) + bias, the
  * reference's attn_output.transpose(1, 2).reshape([b, q_len, hidden]) followed by Linear::forward
  * (models/kalosm-llama/src/raw/attention_layer.rs:450-454, fusor-ml/fusor/src/layers/linear.rs:72-115; the reference
  * multiplies by a GGUF-quantised QMatrix, here the weight is dense).  attn [B,Hq,S,D] bf16 as flash_attention wrote it

@@ -177,7 +177,7 @@ def lse_combine(parts) -> np.ndarray:
     return out
 
 
-# --------------------------------------------------------------------------- output projection (next-row F1)
+# --------------------------------------------------------------------------- output projection
 def out_proj(attn, w, bias=None) -> np.ndarray:
     """attn [B,Hq,S,D], w [N, Hq*D], bias [N] or None -> [B,S,N]: transpose(1,2).reshape then x @ w.T + bias
     (models/kalosm-llama/src/raw/attention_layer.rs:450-454; fusor-ml/fusor/src/layers/linear.rs:72-115)."""
@@ -192,7 +192,7 @@ def out_proj(attn, w, bias=None) -> np.ndarray:
     return out
 
 
-# --------------------------------------------------------------------------- rotary embedding (next-row F2)
+# --------------------------------------------------------------------------- rotary embedding
 def rope_tables(head_dim: int, context_length: int, rope_theta: float = 10000.0):
     """RopeCache::new (fusor-ml/fusor/src/composite/rope.rs:186-219): cos, sin [context_length, head_dim/2] in f32."""
     inv = np.array([1.0 / np.float32(rope_theta) ** (np.float32(i) / np.float32(head_dim)) for i in range(0, head_dim, 2)],
