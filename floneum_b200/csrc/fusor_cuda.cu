@@ -702,6 +702,11 @@ struct fusor_cuda_kvcache {
     bool plan_dirty = true;
     int plan_g = 0;
     int grid = 0, n_slots = 0, max_grid = 0, max_slots = 0;
+    // the plan lives in one device block [cta_seg_start: max_grid + 1][seq_slot_begin: max_batch * Hkv + 1][pad to 32 bytes]
+    // [segments: max_slots], uploaded in one copy whenever the lengths changed
+    void* d_plan = nullptr;
+    size_t plan_seg_off = 0;  // byte offset of the segments
+    std::vector<unsigned char> h_plan;
     DecodeSegment* d_segs = nullptr;
     int* d_cta_seg_start = nullptr;
     int* d_seq_slot_begin = nullptr;
@@ -734,12 +739,15 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
     bool ok = cudaMalloc(&c->k_pages, pool_bytes) == cudaSuccess && cudaMalloc(&c->v_pages, pool_bytes) == cudaSuccess &&
               cudaMalloc(&c->d_tables, ((size_t)2 * max_batch + (size_t)max_batch * max_pages_per_seq) * 4) == cudaSuccess &&
 
-              cudaMalloc(&c->d_segs, (size_t)c->max_slots * sizeof(DecodeSegment)) == cudaSuccess &&
-              cudaMalloc(&c->d_cta_seg_start, (size_t)(c->max_grid + 1) * 4) == cudaSuccess &&
-              cudaMalloc(&c->d_seq_slot_begin, (size_t)(max_batch * num_kv_heads + 1) * 4) == cudaSuccess &&
+              cudaMalloc(&c->d_plan, (((size_t)(c->max_grid + 1) + (size_t)(max_batch * num_kv_heads + 1)) * 4 + 31) / 32 * 32 +
+                                         (size_t)c->max_slots * sizeof(DecodeSegment)) == cudaSuccess &&
               cudaMalloc(&c->part_o, (size_t)c->max_slots * DEC_GP * head_dim * 4) == cudaSuccess &&
               cudaMalloc(&c->part_ml, (size_t)c->max_slots * DEC_GP * 2 * 4) == cudaSuccess;
     if (ok) {
+        c->plan_seg_off = (((size_t)(c->max_grid + 1) + (size_t)(max_batch * num_kv_heads + 1)) * 4 + 31) / 32 * 32;
+        c->d_cta_seg_start = static_cast<int*>(c->d_plan);
+        c->d_seq_slot_begin = c->d_cta_seg_start + (c->max_grid + 1);
+        c->d_segs = reinterpret_cast<DecodeSegment*>(static_cast<unsigned char*>(c->d_plan) + c->plan_seg_off);
         c->d_len_before = c->d_tables;
         c->d_kv_len = c->d_tables + max_batch;
         c->d_page_table = c->d_tables + 2 * max_batch;
@@ -787,8 +795,7 @@ extern "C" int32_t fusor_cuda_kvcache_destroy(fusor_cuda_kvcache* c) {
     if (!c) return FUSOR_CUDA_OK;
     DeviceGuard g(c->ctx->device);
     cudaStreamSynchronize(c->ctx->stream);
-    void* ptrs[] = {c->k_pages, c->v_pages, c->d_tables, c->d_segs,
-                    c->d_cta_seg_start, c->d_seq_slot_begin, c->part_o, c->part_ml};
+    void* ptrs[] = {c->k_pages, c->v_pages, c->d_tables, c->d_plan, c->part_o, c->part_ml};
     for (void* p : ptrs)
         if (p) cudaFree(p);
 
@@ -1219,9 +1226,15 @@ static int32_t build_decode_plan(fusor_cuda_kvcache* c) {
     std::vector<int> cta_start, seq_slot;
     plan_segments(c->h_kv_len.data(), B, Hkv, grid, segs, cta_start, seq_slot);
     if ((int)segs.size() > c->max_slots) return fail(ctx, FUSOR_CUDA_INTERNAL, "plan has %d segments, room for %d", (int)segs.size(), c->max_slots);
-    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_segs, segs.data(), segs.size() * sizeof(DecodeSegment), cudaMemcpyHostToDevice, ctx->stream));
-    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_cta_seg_start, cta_start.data(), cta_start.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
-    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_seq_slot_begin, seq_slot.data(), seq_slot.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    if ((int)cta_start.size() > c->max_grid + 1 || (int)seq_slot.size() > c->max_batch * c->Hkv + 1)
+        return fail(ctx, FUSOR_CUDA_INTERNAL, "plan tables exceed their buffers");
+    // one staging image of the device block, one copy
+    const size_t bytes = c->plan_seg_off + segs.size() * sizeof(DecodeSegment);
+    c->h_plan.assign(bytes, 0);
+    std::memcpy(c->h_plan.data(), cta_start.data(), cta_start.size() * 4);
+    std::memcpy(c->h_plan.data() + (size_t)(c->max_grid + 1) * 4, seq_slot.data(), seq_slot.size() * 4);
+    std::memcpy(c->h_plan.data() + c->plan_seg_off, segs.data(), segs.size() * sizeof(DecodeSegment));
+    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_plan, c->h_plan.data(), bytes, cudaMemcpyHostToDevice, ctx->stream));
     c->grid = grid;
     c->n_slots = (int)segs.size();
     c->plan_dirty = false;
