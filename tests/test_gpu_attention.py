@@ -370,3 +370,35 @@ def test_batch_key_mask_on_the_tensor_core_kernels(device, B, Hq, Hkv, S, neg):
     assert device.launch_count() - before == 2, "V pre-pass + one tensor-core kernel, not the general kernel"
     want = O.flash_attention(q, k, v, scale, mask, O.MASK_BATCH_KEY)
     assert_close(got, want, what=f"batch key mask B{B} S{S} pad {neg}")
+
+
+@pytest.mark.parametrize("it", range(10))
+def test_prefill_two_tile_kernel_shape_fuzz(device, it):
+    """Seeded shapes for the two-tile kernel (Sq >= 256): ragged query and key counts, key offsets (Skv > Sq), no mask /
+    causal / sliding window / key mask, GQA groups 1-4, against the composite."""
+    fb = _mods()
+    rng = np.random.default_rng(7000 + it)
+    B, Hkv, g = int(rng.integers(1, 3)), int(rng.integers(1, 3)), int(rng.integers(1, 5))
+    Sq = int(rng.integers(256, 700))
+    off = int(rng.choice([0, 0, 1, 77, 128, 300]))
+    kind = ["none", "causal", "window", "keymask"][it % 4]
+    if kind == "window":
+        w = int(rng.integers(1, Sq + 50))
+        off = min(off, max(w - Sq, 0))
+    Skv = Sq + off
+    q, k, v, scale = _bf16_case(8000 + it, B, Hkv * g, Hkv, Sq, Skv)
+    if kind == "none":
+        got = _run(device, q, k, v, scale, None, dtype=1)
+        want = O.flash_attention(q, k, v, scale)
+    elif kind == "causal":
+        got = _run(device, q, k, v, scale, (fb.MaskCache().get_mask(Sq, off, None, device), fb.MaskKind.QKMask), dtype=1)
+        want = O.flash_attention(q, k, v, scale, mask_kind=O.MASK_CAUSAL, skip_masked=True)
+    elif kind == "window":
+        got = _run(device, q, k, v, scale, (fb.MaskCache().get_mask(Sq, off, w, device), fb.MaskKind.QKMask), dtype=1)
+        want = O.flash_attention(q, k, v, scale, O.get_mask(Sq, off, w), O.MASK_QK)
+    else:
+        mask = np.where(rng.random((B, Skv)) < 0.3, -np.inf, 0.0).astype(np.float32)
+        mask[:, 0] = 0.0
+        got = _run(device, q, k, v, scale, (fb.Tensor.from_slice(device, mask.shape, mask), fb.MaskKind.BatchKeyMask), dtype=1)
+        want = O.flash_attention(q, k, v, scale, mask, O.MASK_BATCH_KEY)
+    assert_close(got, want, what=f"two-tile fuzz {it}: B{B} Hq{Hkv * g}/{Hkv} Sq{Sq} Skv{Skv} {kind}")
