@@ -10,7 +10,9 @@
 //   * warp 9 issues every MMA from one elected lane, in the order PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1): while the
 //     softmax of one tile runs, the tensor pipe works for the other tile (the tiles ping-pong, half a period apart);
 //   * warps 0-3 softmax of tile A, warps 4-7 softmax of tile B: one thread per query row, 128 scores in registers,
-//     running max with lazy rescale of O (threshold 2^8), P written back to TMEM, row sums in registers;
+//     running max with lazy rescale of O (threshold 2^8), P written back to TMEM and handed over in two halves (keys
+//     0-63 first, so that half of P V runs under the second half of the exponentials), row sums in registers; the
+//     launch bound leaves 168 registers per thread, setmaxnreg moves the copy / issue warpgroup's share to these warps;
 //   * epilogue per warp: O / l -> a 4 KB swizzled staging area of its own -> TMA store of a [32 rows][128 bytes] box,
 //     no CTA-wide barrier, while the other tile still computes.
 // The CTAs are persistent: each walks its share of the (row block, head, batch) items; barrier phases run on across
