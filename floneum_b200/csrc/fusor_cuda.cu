@@ -535,6 +535,7 @@ extern "C" int32_t fusor_cuda_attention_out_proj(fusor_cuda_ctx* ctx, const fuso
     P.m_tiles_per_batch = (int)((S + OP_BM - 1) / OP_BM);
     P.n_tiles = (int)((N + OP_BN - 1) / OP_BN);
     P.k_chunks = (int)(K / OP_BK);
+    P.n_group = (int)std::max<long long>(1, std::min<long long>(P.n_tiles, (32ll << 20) / ((long long)OP_BN * K * 2)));
     P.bias = bias; P.out_dtype = out->dtype; P.err = ctx->d_err;
     const long long tiles = B * P.m_tiles_per_batch * P.n_tiles;
     if (tiles > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "too many output tiles");

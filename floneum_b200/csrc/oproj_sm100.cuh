@@ -8,8 +8,8 @@
 // Persistent CTAs, one per SM; output tiles 128 x 256, K step 64, 4-stage TMA ring (48 KB per stage); warp 0 producer,
 // warp 1 allocates TMEM and issues tcgen05.mma (M 128, N 256, K 16, both operands K-major from shared memory), warps 2-5
 // epilogue.  Two 256-column accumulators in TMEM: the epilogue of tile i (TMEM -> registers -> + bias -> swizzled staging
-// -> TMA store) runs under the main loop of tile i + 1.  Tiles are walked n-fastest so that the 128-row A panel is read
-// from HBM once and the weight stays in L2.  All waits are bounded.
+// -> TMA store) runs under the main loop of tile i + 1.  Tiles are walked n-fastest inside groups of n tiles whose weight
+// rows fit L2 (op_tile_coords).  All waits are bounded.
 // Shared-memory traffic is 12 KB per 128 tensor cycles (under the port's rate); L2 -> SM traffic is 48 KB per 512 cycles
 // = 96 B/clk/SM, above the 46 B/clk/SM this GPU delivers to all SMs at once, so without sharing operand tiles between
 // CTAs the kernel is bound by L2 bandwidth at about half the tensor peak.
@@ -30,10 +30,23 @@ constexpr size_t OP_SMEM_BYTES = 1024 + (size_t)OP_STAGES * OP_STAGE_BYTES + 4 *
 struct OprojParams {
     int B, Hq, S, D, N;
     int m_tiles_per_batch, n_tiles, k_chunks;  // K = Hq * D in chunks of 64
+    int n_group;                               // n tiles per raster group (their weight rows stay in L2 while all m sweep by)
     const float* bias;                         // [N] or null
     int out_dtype;                             // 0 f32, 1 bf16
     int* err;
 };
+
+// Tile order: groups of n_group neighbouring n tiles; inside a group every m tile in turn, n fastest.  The group's weight
+// rows (n_group x 256 x K x 2 bytes, sized by the host to about a quarter of L2) stay resident while the A panels stream by;
+// with a weight that fits L2 whole there is one group and A is read once.
+__device__ __forceinline__ void op_tile_coords(const OprojParams& P, int tile, int& nt, int& mt) {
+    const int m_total = P.B * P.m_tiles_per_batch;
+    const int g = tile / (P.n_group * m_total);
+    const int r = tile - g * P.n_group * m_total;
+    const int width = min(P.n_group, P.n_tiles - g * P.n_group);
+    mt = r / width;
+    nt = g * P.n_group + r % width;
+}
 
 __global__ void __launch_bounds__(OP_THREADS, 1)
     oproj_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
@@ -84,7 +97,8 @@ __global__ void __launch_bounds__(OP_THREADS, 1)
             int it = 0;  // K steps loaded so far: ring slot it % 4
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
-                const int nt = tile % P.n_tiles, mt = tile / P.n_tiles;
+                int nt, mt;
+                op_tile_coords(P, tile, nt, mt);
                 const int b = mt / P.m_tiles_per_batch, s0 = (mt % P.m_tiles_per_batch) * OP_BM;
                 for (int kc = 0; kc < P.k_chunks; ++kc, ++it) {
                     const int st = it % OP_STAGES, use = it / OP_STAGES;
@@ -132,7 +146,8 @@ __global__ void __launch_bounds__(OP_THREADS, 1)
         int tc = 0, stores = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++tc) {
-            const int nt = tile % P.n_tiles, mt = tile / P.n_tiles;
+            int nt, mt;
+            op_tile_coords(P, tile, nt, mt);
             const int b = mt / P.m_tiles_per_batch, s0 = (mt % P.m_tiles_per_batch) * OP_BM;
             const int ab = tc & 1;
             const int row_g = s0 + quad * 32;
