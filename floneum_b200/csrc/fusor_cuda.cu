@@ -928,11 +928,19 @@ static int32_t rope_launch(fusor_cuda_ctx* ctx, const RopeParams& P) {
                rope_vec_ok(P.q, P.q_dtype, P.qs) && rope_vec_ok(P.q_out, P.qo_dtype, P.qos);
     if (vec && P.k_pages) vec = rope_vec_ok(P.k_new, P.k_dtype, P.ks) && rope_vec_ok(P.v_new, P.v_dtype, P.vs);
     const long long pairs = (long long)P.B * heads * P.n * (P.D / 2);
-    const long long threads = vec ? pairs / 8 : pairs;
+    RopeParams Q = P;
+    long long threads = pairs;
+    if (vec) {
+        // enough (batch, token, chunk) items to fill the GPU twice over: let a thread walk several heads with its cos / sin
+        const long long items = (long long)P.B * P.n * (P.D / 16);
+        const long long groups = std::max<long long>(1, std::min<long long>(heads, ((long long)ctx->num_sms * 4096 + items - 1) / items));
+        Q.heads_per_thread = (int)((heads + groups - 1) / groups);
+        threads = items * ((heads + Q.heads_per_thread - 1) / Q.heads_per_thread);
+    }
     const int blocks = (int)std::max<long long>(1, std::min<long long>((threads + 255) / 256, (long long)ctx->num_sms * 16));
     if (!vec) rope_append_kernel<<<blocks, 256, 0, ctx->stream>>>(P);
-    else if (P.interleaved) rope_append_vec_kernel<true><<<blocks, 256, 0, ctx->stream>>>(P);
-    else rope_append_vec_kernel<false><<<blocks, 256, 0, ctx->stream>>>(P);
+    else if (P.interleaved) rope_append_vec_kernel<true><<<blocks, 256, 0, ctx->stream>>>(Q);
+    else rope_append_vec_kernel<false><<<blocks, 256, 0, ctx->stream>>>(Q);
     return launch_check(ctx, "rope_append_kernel");
 }
 

@@ -62,6 +62,7 @@ struct RopeParams {
     int B, n, D;
     int start_pos;  // table row of token 0; < 0: each sequence's len_before
     int interleaved;
+    int heads_per_thread;  // vector kernel: heads a thread walks with one set of cos / sin values
 };
 
 __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams P) {
@@ -159,52 +160,62 @@ __device__ __forceinline__ void rope_rotate8(float (&a)[8], float (&b)[8], const
     }
 }
 
+// A thread owns 8 pairs of one (batch, token) and walks `heads_per_thread` heads with them, so the cos / sin values it
+// loaded (64 bytes against 32 bytes of bf16 data per head) are reused instead of re-read from L2 for every head.
 template <bool INTERLEAVED>
 __global__ void __launch_bounds__(256) rope_append_vec_kernel(const RopeParams P) {
     const int half = P.D >> 1;
     const unsigned chunks = (unsigned)half >> 3;  // 8 pairs per thread
     const unsigned heads = (unsigned)(P.Hq + (P.k_pages ? P.Hkv : 0));
-    const unsigned long long total = (unsigned long long)P.B * heads * P.n * chunks;
+    const unsigned hpt = (unsigned)P.heads_per_thread;
+    const unsigned groups = (heads + hpt - 1) / hpt;
+    const unsigned long long total = (unsigned long long)P.B * groups * P.n * chunks;
     for (unsigned long long idx = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; idx < total;
          idx += (unsigned long long)gridDim.x * blockDim.x) {
         const unsigned ch = (unsigned)(idx % chunks);
         const unsigned long long r = idx / chunks;
         const unsigned t = (unsigned)(r % (unsigned)P.n);
-        const unsigned bh = (unsigned)(r / (unsigned)P.n);
-        const unsigned h = bh % heads, b = bh / heads;
+        const unsigned bg = (unsigned)(r / (unsigned)P.n);
+        const unsigned hg = bg % groups, b = bg / groups;
         const int before = P.len_before ? P.len_before[b] : 0;
         const int row = (P.start_pos >= 0 ? P.start_pos : before) + (int)t;
         const int i0 = (int)ch * 8;
-        float c[8], s[8], xa[8], xb[8];
+        float c[8], s[8];
         rope_load8(P.cos_t, 0, (long long)row * half + i0, c);
         rope_load8(P.sin_t, 0, (long long)row * half + i0, s);
         const int offa = INTERLEAVED ? 2 * i0 : i0;
         const int offb = INTERLEAVED ? 2 * i0 + 8 : i0 + half;
-        if (h < (unsigned)P.Hq) {
-            const long long src = b * P.qs[0] + h * P.qs[1] + t * P.qs[2];
-            const long long dst = b * P.qos[0] + h * P.qos[1] + t * P.qos[2];
-            rope_load8(P.q, P.q_dtype, src + offa, xa);
-            rope_load8(P.q, P.q_dtype, src + offb, xb);
-            rope_rotate8<INTERLEAVED>(xa, xb, c, s);
-            rope_store8(P.q_out, P.qo_dtype, dst + offa, xa);
-            rope_store8(P.q_out, P.qo_dtype, dst + offb, xb);
-        } else {
-            const unsigned hk = h - (unsigned)P.Hq;
-            const int pos = before + (int)t;
-            const int page = P.page_table[(long long)b * P.max_pages + pos / DEC_PT];
-            const long long dst = (((long long)page * P.Hkv + hk) * DEC_PT + pos % DEC_PT) * P.D;
-            const long long ksrc = b * P.ks[0] + hk * P.ks[1] + t * P.ks[2];
-            const long long vsrc = b * P.vs[0] + hk * P.vs[1] + t * P.vs[2];
-            float va[8], vb[8];
-            rope_load8(P.k_new, P.k_dtype, ksrc + offa, xa);
-            rope_load8(P.k_new, P.k_dtype, ksrc + offb, xb);
-            rope_load8(P.v_new, P.v_dtype, vsrc + offa, va);
-            rope_load8(P.v_new, P.v_dtype, vsrc + offb, vb);
-            rope_rotate8<INTERLEAVED>(xa, xb, c, s);
-            rope_store8(P.k_pages, 1, dst + offa, xa);
-            rope_store8(P.k_pages, 1, dst + offb, xb);
-            rope_store8(P.v_pages, 1, dst + offa, va);
-            rope_store8(P.v_pages, 1, dst + offb, vb);
+        const unsigned h_end = min(heads, (hg + 1) * hpt);
+        int page = -1;  // looked up once, when the first kv head comes by
+        const int pos = before + (int)t;
+#pragma unroll 2
+        for (unsigned h = hg * hpt; h < h_end; ++h) {
+            float xa[8], xb[8];
+            if (h < (unsigned)P.Hq) {
+                const long long src = b * P.qs[0] + h * P.qs[1] + t * P.qs[2];
+                const long long dst = b * P.qos[0] + h * P.qos[1] + t * P.qos[2];
+                rope_load8(P.q, P.q_dtype, src + offa, xa);
+                rope_load8(P.q, P.q_dtype, src + offb, xb);
+                rope_rotate8<INTERLEAVED>(xa, xb, c, s);
+                rope_store8(P.q_out, P.qo_dtype, dst + offa, xa);
+                rope_store8(P.q_out, P.qo_dtype, dst + offb, xb);
+            } else {
+                const unsigned hk = h - (unsigned)P.Hq;
+                if (page < 0) page = P.page_table[(long long)b * P.max_pages + pos / DEC_PT];
+                const long long dst = (((long long)page * P.Hkv + hk) * DEC_PT + pos % DEC_PT) * P.D;
+                const long long ksrc = b * P.ks[0] + hk * P.ks[1] + t * P.ks[2];
+                const long long vsrc = b * P.vs[0] + hk * P.vs[1] + t * P.vs[2];
+                float va[8], vb[8];
+                rope_load8(P.k_new, P.k_dtype, ksrc + offa, xa);
+                rope_load8(P.k_new, P.k_dtype, ksrc + offb, xb);
+                rope_load8(P.v_new, P.v_dtype, vsrc + offa, va);
+                rope_load8(P.v_new, P.v_dtype, vsrc + offb, vb);
+                rope_rotate8<INTERLEAVED>(xa, xb, c, s);
+                rope_store8(P.k_pages, 1, dst + offa, xa);
+                rope_store8(P.k_pages, 1, dst + offb, xb);
+                rope_store8(P.v_pages, 1, dst + offa, va);
+                rope_store8(P.v_pages, 1, dst + offb, vb);
+            }
         }
     }
 }
