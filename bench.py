@@ -147,6 +147,26 @@ def reference_arm(args, rank):
         cfg = {"workload": f"{args.workload}: causal flash-attention prefill B{w.q.shape[0]} S{w.q.shape[2]} Hq{w.q.shape[1]} "
                            f"Hkv{w.k.shape[1]} D128, bf16 in, f32 out", "flops_per_step": w.flops,
                "note": "CPU arm: each step is the bounded sample named in cpu_baseline.sample"}
+    elif args.workload == "oproj":
+        B, Hq, S, D, N, rows = 4, 32, 4096, 128, 4096, 256
+        rng = np.random.default_rng(21)
+        x = W.bf16_round(rng.standard_normal((1, Hq, rows, D)).astype(np.float32))
+        wt = W.bf16_round((rng.standard_normal((N, Hq * D)) / 64).astype(np.float32))
+        fn = lambda: O.out_proj(x, wt)
+        work, desc = 2.0 * rows * N * Hq * D, f"{rows} of the {B * S} rows, all {N} outputs (f32 transpose + matmul)"
+        unit, scale_div = "TFLOP/s", 1e12
+        cfg = {"workload": f"oproj: out = attn[B{B},Hq{Hq},S{S},D{D}] (read in place) x W[{N},{Hq * D}]^T, bf16 in, f32 out",
+               "flops_per_step": 2.0 * B * S * N * Hq * D, "note": "CPU arm: each step is the bounded sample named in cpu_baseline.sample"}
+    elif args.workload == "rope":
+        B, Hq, Hkv, S, D = 4, 32, 8, 4096, 128
+        rng = np.random.default_rng(22)
+        x = rng.standard_normal((1, Hq + Hkv, S, D)).astype(np.float32)
+        cos, sin = O.rope_tables(D, S, 10000.0)
+        fn = lambda: O.rope(x, cos, sin, 0, False)
+        work, desc = float(x.nbytes * 2), "one batch entry: all 40 heads rotated, f32 (read + write bytes counted)"
+        unit, scale_div = "GB/s", 1e9
+        cfg = {"workload": f"rope: fused RoPE + KV-cache append, B{B} Hq{Hq} Hkv{Hkv} S{S} D{D}, bf16 in, bf16 pages",
+               "note": "CPU arm: rotation only, on f32 copies; each step is the bounded sample named in cpu_baseline.sample"}
     else:
         w = W.cfg3() if args.workload == "cfg3" else W.cfg4()
         fn, work, desc = cpu_decode_sample(w)
