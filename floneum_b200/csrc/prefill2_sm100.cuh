@@ -10,8 +10,8 @@
 //   * warp 9 issues every MMA from one elected lane, in the order PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1): while the
 //     softmax of one tile runs, the tensor pipe works for the other tile (the tiles ping-pong, half a period apart);
 //   * warps 0-3 softmax of tile A, warps 4-7 softmax of tile B: one thread per query row, 128 scores in registers,
-//     running max with lazy rescale of O (threshold 2^8), P written back to TMEM and handed over in two halves (keys
-//     0-63 first, so that half of P V runs under the second half of the exponentials), row sums in registers; the
+//     running max with lazy rescale of O (threshold 2^8), P written back to TMEM and handed over in two parts (keys
+//     0-95 first, so that three quarters of P V run under the last quarter of the exponentials), row sums in registers; the
 //     launch bound leaves 168 registers per thread, setmaxnreg moves the copy / issue warpgroup's share to these warps;
 //   * epilogue per warp: O / l -> a 4 KB swizzled staging area of its own -> TMA store of a [32 rows][128 bytes] box,
 //     no CTA-wide barrier, while the other tile still computes.
@@ -34,6 +34,10 @@ constexpr int P2_TILE_BYTES = 128 * 128 * 2;      // a [128][128] 16-bit tile = 
 constexpr int P2_HALF = P2_TILE_BYTES / 2;
 constexpr int P2_STAGE_BYTES = 32 * 128;          // per-warp output staging: 32 rows x 128 bytes
 constexpr int P2_REGS_IO = 120, P2_REGS_SOFTMAX = 192;  // 256 x 192 + 128 x 120 = 64512 <= 65536
+#ifndef P2_SPLIT_CFG
+#define P2_SPLIT_CFG 96
+#endif
+constexpr int P2_SPLIT = P2_SPLIT_CFG;  // keys of a block handed to the MMA warp early (a multiple of 32: a whole TMEM store)
 constexpr uint32_t P2_TMEM_COLS = 512;
 constexpr uint32_t P2_COL_S = 0, P2_COL_O = 256;  // tile t: S at 128 t, O at 256 + 128 t
 constexpr size_t P2_SMEM_BYTES = 1024 + 2 * (size_t)P2_TILE_BYTES /*Q*/ + 4 * (size_t)P2_TILE_BYTES /*K,V rings*/ +
@@ -76,8 +80,8 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
     uint64_t* v_full = bars + 6;    // [2]
     uint64_t* v_empty = bars + 8;   // [2]
     uint64_t* s_full = bars + 10;   // [2] per tile: S of the tile's next block is in TMEM
-    uint64_t* p_full = bars + 12;   // [2] per tile: keys 0..63 of P written (128 arrivals), O rescaled if it had to be
-    uint64_t* p_full2 = bars + 18;  // [2] per tile: keys 64..127 of P written
+    uint64_t* p_full = bars + 12;   // [2] per tile: the first P2_SPLIT keys of P written (128 arrivals), O rescaled if it had to be
+    uint64_t* p_full2 = bars + 18;  // [2] per tile: the remaining keys of P written
     uint64_t* pv_done = bars + 14;  // [2] per tile: O holds every block issued so far
     uint64_t* q_empty = bars + 16;  // [2] per tile: the item's last S = Q K^T of the tile has completed
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
@@ -260,9 +264,9 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                             if (!ok) break;
                             tc_fence_after();
                             const uint64_t vd = v_desc0 + (uint64_t)((st * P2_TILE_BYTES) >> 4);
-                            // the first 64 keys go ahead while the softmax still works on the other 64
+                            // the first P2_SPLIT keys go ahead while the softmax still works on the rest
 #pragma unroll
-                            for (int kk = 0; kk < P2_BN / 32; ++kk)
+                            for (int kk = 0; kk < P2_SPLIT / 16; ++kk)
                                 tc_mma_ts(tmem_base + P2_COL_O + t * 128, tmem_base + P2_COL_S + t * 128 + kk * 8,
                                           vd + (uint64_t)((kk * 2048) >> 4), idesc_pv, (!fresh[t] || kk > 0));
                             ok = mbar_wait(p_full2 + t, cnt[t] & 1, abort_flag, P.err, 37 + t);
@@ -270,7 +274,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                             if (!ok) break;
                             tc_fence_after();
 #pragma unroll
-                            for (int kk = P2_BN / 32; kk < P2_BN / 16; ++kk)
+                            for (int kk = P2_SPLIT / 16; kk < P2_BN / 16; ++kk)
                                 tc_mma_ts(tmem_base + P2_COL_O + t * 128, tmem_base + P2_COL_S + t * 128 + kk * 8,
                                           vd + (uint64_t)((kk * 2048) >> 4), idesc_pv, true);
                             fresh[t] = false;
@@ -410,7 +414,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                     if ((g & 7) == 7) {
                         // P chunk g / 8 overwrites columns [16 cc, 16 cc + 16) of S_t (all of S_t is in registers)
                         tmem_st16(s_tmem + (g >> 3) * 16, pk);
-                        if (g == 15) {  // keys 0..63 are in place: the MMA warp may start on them
+                        if (g == P2_SPLIT / 4 - 1) {  // keys 0 .. P2_SPLIT-1 are in place: the MMA warp may start on them
                             tc_wait_st();
                             tc_fence_before();
                             mbar_arrive(p_full + t);
