@@ -470,23 +470,38 @@ __global__ void cast_v_to_f16_kernel(const CastVParams P) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *P.clear_slot = 0;
     const int vec_per_row = P.D / 8;
     bool bad = false;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < P.n_vec; i += (long long)gridDim.x * blockDim.x) {
-        const int c = (int)(i % vec_per_row);
-        const long long row = i / vec_per_row;
-        const int s = (int)(row % P.S);
-        const int h = (int)((row / P.S) % P.H);
-        const long long b = row / ((long long)P.S * P.H);
-        const uint4 in = *reinterpret_cast<const uint4*>(P.src + b * P.s0 + h * P.s1 + s * P.s2 + c * 8);
-        const __nv_bfloat162* iv = reinterpret_cast<const __nv_bfloat162*>(&in);
-        uint4 out;
-        __half2* ov = reinterpret_cast<__half2*>(&out);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    // four independent 16-byte loads per thread and trip: the pass is a plain stream and wants bytes in flight
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < P.n_vec; i0 += 4 * stride) {
+        uint4 in[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(iv[e]);
-            bad |= !(fabsf(f.x) <= 65504.0f) || !(fabsf(f.y) <= 65504.0f);
-            ov[e] = __floats2half2_rn(f.x, f.y);
+        for (int u = 0; u < 4; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < P.n_vec) {
+                const int c = (int)(i % vec_per_row);
+                const long long row = i / vec_per_row;
+                const int s = (int)(row % P.S);
+                const int h = (int)((row / P.S) % P.H);
+                const long long b = row / ((long long)P.S * P.H);
+                in[u] = __ldg(reinterpret_cast<const uint4*>(P.src + b * P.s0 + h * P.s1 + s * P.s2 + c * 8));
+            }
         }
-        *reinterpret_cast<uint4*>(P.dst + i * 8) = out;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < P.n_vec) {
+                const __nv_bfloat162* iv = reinterpret_cast<const __nv_bfloat162*>(&in[u]);
+                uint4 out;
+                __half2* ov = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(iv[e]);
+                    bad |= !(fabsf(f.x) <= 65504.0f) || !(fabsf(f.y) <= 65504.0f);
+                    ov[e] = __floats2half2_rn(f.x, f.y);
+                }
+                *reinterpret_cast<uint4*>(P.dst + i * 8) = out;
+            }
+        }
     }
     if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(P.overflow, 1);
 }
