@@ -13,5 +13,5 @@ load()
 
 from .device import Device  # noqa: E402,F401
 from .tensor import MaskKind, Tensor  # noqa: E402,F401
-from .cache import AttentionMask, KvCache, MaskCache, PagedKvCache  # noqa: E402,F401
+from .cache import AttentionMask, KvCache, LlamaCache, MaskCache, PagedKvCache  # noqa: E402,F401
 from .rope import RopeCache, rope  # noqa: E402,F401

@@ -12,7 +12,7 @@ from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_voi
 from . import build as _build
 
 OK, INVALID_ARGUMENT, SHAPE_MISMATCH, UNSUPPORTED, CUDA_ERROR, NO_DEVICE, TIMEOUT, OUT_OF_PAGES, INTERNAL = range(9)
-F32, BF16 = 0, 1
+F32, BF16, F16 = 0, 1, 2
 MASK_NONE, MASK_QK, MASK_BATCH_KEY, MASK_CAUSAL, MASK_SLIDING = range(5)
 
 STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "SHAPE_MISMATCH", "UNSUPPORTED", "CUDA_ERROR", "NO_DEVICE", "TIMEOUT",
@@ -58,7 +58,6 @@ SIGNATURES = {
     "fusor_cuda_flash_attention_general": (c_int32, [c_void_p, _T4, _T4, _T4, c_float, _T2, c_int32, c_int32, _T4]),
     "fusor_cuda_flash_attention_noalloc": (c_int32, [c_void_p, _T4, _T4, _T4, c_float, c_int32, _T4]),
     "fusor_cuda_selftest_wait_limit": (c_int32, [c_void_p]),
-    "fusor_cuda_prefill_probe": (c_int32, [c_void_p, _T4, _T4, _T4, c_float, c_int32, _T4, c_int32, c_void_p]),
     "fusor_cuda_kvcache_create": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                             POINTER(c_void_p)]),
     "fusor_cuda_kvcache_destroy": (c_int32, [c_void_p]),
@@ -67,7 +66,10 @@ SIGNATURES = {
     "fusor_cuda_exchange_create": (c_int32, [c_void_p, c_int32, c_int32, c_int64, POINTER(c_void_p)]),
     "fusor_cuda_exchange_handle": (c_int32, [c_void_p, c_void_p]),
     "fusor_cuda_exchange_connect": (c_int32, [c_void_p, c_void_p]),
+    "fusor_cuda_exchange_disconnect": (c_int32, [c_void_p]),
     "fusor_cuda_exchange_destroy": (c_int32, [c_void_p]),
+    "fusor_cuda_exchange_decode": (c_int32, [c_void_p, c_void_p, _T4, c_float, c_void_p]),
+    "fusor_cuda_kvcache_set_decode_ctas": (c_int32, [c_void_p, c_int32]),
     "fusor_cuda_exchange_lse_combine": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "fusor_cuda_attention_out_proj": (c_int32, [c_void_p, _T4, _T4, c_void_p, _T4]),
     "fusor_cuda_rope": (c_int32, [c_void_p, _T4, c_void_p, c_void_p, c_int32, c_int32, c_int32, _T4]),
@@ -83,7 +85,7 @@ SIGNATURES = {
     "fusor_cuda_flash_attention_decode_partial": (c_int32, [c_void_p, c_void_p, _T4, c_float, c_void_p]),
     "fusor_cuda_flash_attention_decode_host": (c_int32, [c_void_p, c_void_p, _T4, c_float, _T4]),
     "fusor_cuda_decode_plan": (c_int32, [POINTER(c_int32), c_int32, c_int32, c_int32, POINTER(c_int32), c_int32,
-                                         POINTER(c_int32), POINTER(c_int32), POINTER(c_int32)]),
+                                         POINTER(c_int32), POINTER(c_int32)]),
     "fusor_cuda_lse_combine": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p]),
 }
 

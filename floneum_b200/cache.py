@@ -200,6 +200,10 @@ class PagedKvCache:
         self._ck(self._L.fusor_cuda_kvcache_gather(self._h, ctypes.byref(ck), ctypes.byref(cv)))
         return k, v
 
+    def set_decode_ctas(self, ctas: int):
+        """Grid size of the decode kernel: 0 = automatic (from the number of cached pages), n > 0 = exactly n CTAs."""
+        self._ck(self._L.fusor_cuda_kvcache_set_decode_ctas(self._h, int(ctas)))
+
     def decode(self, q: Tensor, scale: float, out: Optional[Tensor] = None, out_dtype: int = F32) -> Tensor:
         """q [B,Hq,1,D] -> out [B,Hq,1,D]."""
         if out is None:
@@ -383,3 +387,36 @@ class KvCache:
             return self._paged.decode(q, scale, out_dtype=out_dtype)
         kd, vd = self._dense(BF16)
         return q.to_bf16().flash_attention(kd, vd, scale, mask, out_dtype)
+
+
+class LlamaCache:
+    """One `KvCache` per layer (models/kalosm-llama/src/raw/cache.rs:14-54), concatenating along axis 2.
+
+    With a sliding-window model (`sliding_window_type` and `sliding_window_size` both given) layer i keeps
+    `sliding_window_size` tokens unless (i + 1) % sliding_window_type == 0; those layers, and every layer of a model
+    without a window, keep `context_length` tokens.  The layer loop hands `blocks[i]` to layer i
+    (models/kalosm-llama/src/raw/mod.rs:614-627)."""
+
+    CONCAT_DIMENSION = 2
+
+    def __init__(self, n_layer: int, context_length: int, sliding_window_type: Optional[int] = None,
+                 sliding_window_size: Optional[int] = None):
+        self.start_time = 0
+        self.tokens: list = []
+        self.blocks = [KvCache(self.CONCAT_DIMENSION, self.layer_max_seq_len(i, context_length, sliding_window_type,
+                                                                             sliding_window_size))
+                       for i in range(n_layer)]
+
+    new = classmethod(lambda cls, *a, **kw: cls(*a, **kw))
+
+    @staticmethod
+    def layer_max_seq_len(layer_idx: int, context_length: int, sliding_window_type: Optional[int],
+                          sliding_window_size: Optional[int]) -> int:
+        if sliding_window_type is not None and sliding_window_size is not None:
+            if (layer_idx + 1) % sliding_window_type != 0:
+                return sliding_window_size
+        return context_length
+
+    def clear(self):
+        for block in self.blocks:
+            block.reset()

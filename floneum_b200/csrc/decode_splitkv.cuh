@@ -3,13 +3,18 @@
 // HBM-bound: every K and V byte is read exactly once and shared by the g query heads of
 // its kv head.  A persistent grid deals the pages of all (sequence, kv head) pairs out
 // evenly; a CTA's share is a list of segments (runs of pages of one (sequence, kv head)).
+// The deal is computed by every CTA from the device-resident lengths (no host plan, nothing to
+// upload when a sequence grows): pages are numbered in (sequence, kv head, page) order, CTA c
+// owns [c T / grid, (c + 1) T / grid) of the T pages, and the partial record of (sequence-head s,
+// CTA c) lives in slot s + c, so the records of one sequence-head are contiguous.
 // Inside a CTA one producer warp streams 4 KB page tiles with TMA into a shared-memory
-// ring (128-byte swizzle, one mbarrier pair per slot); four consumer warps take pages
+// ring (128-byte swizzle, one mbarrier pair per slot); the consumer warps take pages
 // round-robin, compute S = Q K^T and O += P V with warp-level tensor-core MMAs
 // (m16n8k16, the g query heads padded to the 16-row tile), keep an online-softmax state
-// per warp, and merge the four states at the end of each segment into one partial
-// (m, l, O) record.  decode_combine_kernel merges the records of a sequence by
-// log-sum-exp (the (m, d) rule of fusor-ml/core/src/composite/softmax.rs:59-82).
+// per warp, and merge their states at the end of each segment into one partial
+// (m, l, O) record.  The CTA that completes the last record of a sequence-head (a device
+// counter per sequence-head) merges that head's records by log-sum-exp (the (m, d) rule of
+// fusor-ml/core/src/composite/softmax.rs:59-82) and writes the result: one launch per step.
 //
 // Replaces the Sq == 1 regime of the reference's fused kernel
 // (fusor-ml/core/src/composite/flash_attention.rs:147-331), which walks all keys serially
@@ -17,6 +22,7 @@
 #pragma once
 #include <cuda.h>
 
+#include "peer_exchange.cuh"
 #include "ptx_sm100.cuh"
 
 namespace fusor {
@@ -29,34 +35,96 @@ namespace fusor {
 #endif
 constexpr int DEC_PT = 16;              // tokens per page
 constexpr int DEC_NW = DEC_NW_CFG;      // consumer warps
-constexpr int DEC_CTAS = DEC_CTAS_CFG;  // resident CTAs per SM the kernel is sized for
+constexpr int DEC_CTAS = DEC_CTAS_CFG;  // most resident CTAs per SM the kernel is sized for
 constexpr int DEC_THREADS = (DEC_NW + 1) * 32;
 constexpr int DEC_GP = 8;   // query heads per kv head are padded to 8 rows (g <= 8)
 
+// One run of pages of one (sequence, kv head) inside one CTA's share.
 struct DecodeSegment {
     int b, hk;
     int page_begin, page_end;  // logical pages of sequence b
     int kv_len;                // tokens in sequence b
-    int slot;                  // partial record index
+    int slot;                  // partial record index = sequence-head index + CTA index
     int cta_page_off;          // index of this segment's first page in the CTA's page stream
-    int pad;
+    int n_rec;                 // records of this sequence-head (CTAs its pages are spread over)
+    int first_slot;            // slot of its first record; the records are [first_slot, first_slot + n_rec)
 };
+
+// ---- the deal, shared by the kernel and by the host restatement behind fusor_cuda_decode_plan
+// Page counts fit 32 bits (the pool has fewer than 2^31 rows of 16 tokens); only the products need 64.
+// CTA that owns global page gp when T pages are dealt to `grid` CTAs as [c T / grid, (c + 1) T / grid).
+__host__ __device__ inline int decode_page_owner(int T, int grid, int gp) { return (int)((((long long)gp + 1) * grid - 1) / T); }
+
+struct DecodeWalk {
+    int g, g_begin, g_end;  // next global page and this CTA's range
+    int b;                  // sequence the next page belongs to
+    int cum;                // pages (per kv head) of the sequences before b
+};
+
+__host__ __device__ inline void decode_walk_init(DecodeWalk& w, int T, int grid, int cta, int b_start, int cum_start) {
+    w.g_begin = (int)((long long)cta * T / grid);
+    w.g_end = (int)((long long)(cta + 1) * T / grid);
+    w.g = w.g_begin;
+    w.b = b_start;
+    w.cum = cum_start;
+}
+
+// Next segment of the CTA's share, or false when the share is exhausted.  (b_start, cum_start) may be any sequence at or
+// before the one that holds the CTA's first page: sequences that end before it are skipped.
+__host__ __device__ inline bool decode_next_segment(const int* kv_len, int B, int Hkv, int T, int grid, int cta,
+                                                    DecodeWalk& w, DecodeSegment& s) {
+    while (w.g < w.g_end && w.b < B) {
+        const int len = kv_len[w.b];
+        const int pages = (len + DEC_PT - 1) / DEC_PT;
+        const int rel = w.g - Hkv * w.cum;
+        if (pages <= 0 || rel >= Hkv * pages) {
+            w.cum += pages > 0 ? pages : 0;
+            ++w.b;
+            continue;
+        }
+        const int hk = rel / pages, page = rel - hk * pages;
+        const int left = w.g_end - w.g;
+        const int take = pages - page < left ? pages - page : left;
+        const int p0 = Hkv * w.cum + hk * pages;  // first global page of (b, hk)
+        const int c_first = decode_page_owner(T, grid, p0), c_last = decode_page_owner(T, grid, p0 + pages - 1);
+        s.b = w.b; s.hk = hk; s.page_begin = page; s.page_end = page + take; s.kv_len = len;
+        s.slot = w.b * Hkv + hk + cta;
+        s.cta_page_off = w.g - w.g_begin;
+        s.n_rec = c_last - c_first + 1;
+        s.first_slot = w.b * Hkv + hk + c_first;
+        w.g += take;
+        return true;
+    }
+    return false;
+}
 
 struct DecodeParams {
     const void* q;
-    int q_dtype;
+    int q_dtype;           // 0 f32, 1 bf16, 2 f16
     long long q_sb, q_sh;  // element strides of batch and head
     const int* page_table;
     int max_pages;
     int num_pages;
-    const DecodeSegment* segs;
-    const int* cta_seg_start;  // [grid + 1]
-    float* part_o;             // [slots][DEC_GP][D]
+    const int* kv_len;         // [B] device-resident lengths; every sequence holds at least one token
+    int B;
+    float* part_o;             // [slots][DEC_GP][D], slots >= B * Hkv + grid
     float* part_ml;            // [slots][DEC_GP][2]  (m in log2 units, l)
+    unsigned int* seq_done;    // [B * Hkv] finished records per sequence-head, zero between launches
     int Hkv, g;
     float scale_log2;
     int ring;
     int* err;
+    // result of the merged records:
+    //   mode 0: out[b][h][0][:] = O / L                         (dtype f32 or bf16, strided)
+    //   mode 1: out[b][h][:] = { M ln2, L, O }                  (f32, packed [B][Hq][D+2]; merged across GPUs later)
+    //   mode 2: the mode-1 record, stored into this rank's slot on every rank of `push` (and published once all
+    //           sequence-heads of this rank are in place)
+    void* out;
+    int out_dtype;
+    long long o_sb, o_sh;
+    int Hq;
+    int mode;
+    PeerTargets push;
 };
 
 template <int D>
@@ -84,6 +152,8 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
     uint64_t* full = reinterpret_cast<uint64_t*>(merge_ml + DEC_NW * DEC_GP * 2);
     uint64_t* empty = full + R;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + R);
+    volatile int* last_flag = abort_flag + 1;
+    int* walk0 = const_cast<int*>(abort_flag) + 2;  // [3]: T, first sequence, pages before it
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -96,10 +166,51 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
     }
+    if (warp == 0) {
+        // T = Hkv * sum of pages, then the sequence that holds this CTA's first page (32 sequences per step)
+        int sum = 0;
+        for (int b0 = 0; b0 < P.B; b0 += 32) {
+            const int b = b0 + lane;
+            int pg = b < P.B ? (P.kv_len[b] + DEC_PT - 1) / DEC_PT : 0;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) pg += __shfl_xor_sync(0xffffffffu, pg, o);
+            sum += pg;
+        }
+        const int T = sum * P.Hkv;
+        const int g0 = (int)((long long)blockIdx.x * T / gridDim.x);
+        int cum = 0;
+        int b_start = P.B;
+        for (int b0 = 0; b0 < P.B; b0 += 32) {
+            const int b = b0 + lane;
+            const int pg = b < P.B ? (P.kv_len[b] + DEC_PT - 1) / DEC_PT : 0;
+            int incl = pg;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            // first sequence whose pages end after g0
+            const unsigned hit = __ballot_sync(0xffffffffu, b < P.B && (cum + incl) * P.Hkv > g0);
+            if (hit) {
+                const int l = __ffs(hit) - 1;
+                const int before = __shfl_sync(0xffffffffu, incl - pg, l);
+                b_start = b0 + l;
+                cum += before;
+                break;
+            }
+            cum += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) {
+            walk0[0] = T;
+            walk0[1] = b_start;
+            walk0[2] = cum;
+        }
+    }
     __syncthreads();
-
-    const int seg_begin = P.cta_seg_start[blockIdx.x];
-    const int seg_end = P.cta_seg_start[blockIdx.x + 1];
+    const int T = walk0[0];
+    DecodeWalk W;
+    decode_walk_init(W, T, (int)gridDim.x, (int)blockIdx.x, walk0[1], walk0[2]);
+    DecodeSegment S;
 
     if (warp == DEC_NW) {
         // ------------------------------------------------------------------ producer warp
@@ -109,8 +220,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
         int slot = 0, phase = 0;  // ring position of the next page; `phase` flips each time the ring wraps
         bool wrapped = false;
         bool ok = true;
-        for (int sg = seg_begin; sg < seg_end && ok; ++sg) {
-            const DecodeSegment S = P.segs[sg];
+        while (ok && decode_next_segment(P.kv_len, P.B, P.Hkv, T, (int)gridDim.x, (int)blockIdx.x, W, S)) {
             const int* pt = P.page_table + (long long)S.b * P.max_pages;
             int next_phys = (S.page_begin + lane < S.page_end) ? pt[S.page_begin + lane] : 0;
             for (int p0 = S.page_begin; p0 < S.page_end && ok; p0 += 32) {
@@ -156,9 +266,41 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
         // ldmatrix lane geometry
         const int lm_j = lane >> 3, lm_r = lane & 7;
         const uint32_t ksm_u = smem_u32(ksm), vsm_u = smem_u32(vsm);
+        constexpr int NC = DEC_NW * 32;   // consumer threads
+        constexpr int DG = D / 4;         // float4 column groups of a row
+        // mode 2: the epoch this step publishes (the counter only moves in the merge kernel that follows)
+        const unsigned long long e_push = P.mode == 2 ? *reinterpret_cast<volatile unsigned long long*>(P.push.epoch) + 1 : 0ull;
 
-        for (int sg = seg_begin; sg < seg_end; ++sg) {
-            const DecodeSegment S = P.segs[sg];
+        // Result of one (sequence-head, query row, column group) after all its records have been merged.
+        auto emit = [&](int b, int hk, int rr, int dg, float M, float L, float4 acc) {
+            const int h = hk * P.g + rr, d = dg * 4;
+            if (P.mode == 0) {
+                const long long idx = (long long)b * P.o_sb + (long long)h * P.o_sh + d;
+                const float inv = 1.0f / L;
+                if (P.out_dtype == 0) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + idx) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+                } else {
+                    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(P.out) + idx) =
+                        make_uint2(pack_16(P.out_dtype, acc.x * inv, acc.y * inv), pack_16(P.out_dtype, acc.z * inv, acc.w * inv));
+                }
+                return;
+            }
+            const long long off = ((long long)b * P.Hq + h) * (D + 2);
+            const float m_ln = M * 0.6931471805599453f;
+            if (P.mode == 1) {
+                float* rec = reinterpret_cast<float*>(P.out) + off;
+                rec[2 + d] = acc.x; rec[3 + d] = acc.y; rec[4 + d] = acc.z; rec[5 + d] = acc.w;
+                if (dg == 0) { rec[0] = m_ln; rec[1] = L; }
+            } else {
+                for (int pr = 0; pr < P.push.world; ++pr) {
+                    float* rec = peer_slot(P.push, pr, e_push) + off;
+                    rec[2 + d] = acc.x; rec[3 + d] = acc.y; rec[4 + d] = acc.z; rec[5 + d] = acc.w;
+                    if (dg == 0) { rec[0] = m_ln; rec[1] = L; }
+                }
+            }
+        };
+
+        while (decode_next_segment(P.kv_len, P.B, P.Hkv, T, (int)gridDim.x, (int)blockIdx.x, W, S)) {
             // Q fragments: rows >= g are zero.
             uint32_t qa[D / 16][2];
 #pragma unroll
@@ -175,10 +317,9 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
                         const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(P.q) + qoff;
                         qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp + d0);
                         qa[ks][1] = *reinterpret_cast<const uint32_t*>(qp + d0 + 8);
-                    } else {
-                        const float* qp = reinterpret_cast<const float*>(P.q) + qoff;
-                        qa[ks][0] = pack_bf16(qp[d0], qp[d0 + 1]);
-                        qa[ks][1] = pack_bf16(qp[d0 + 8], qp[d0 + 9]);
+                    } else {  // f32 or f16 queries are rounded to bf16, the type of the cached keys
+                        qa[ks][0] = pack_bf16(ld_as_float(P.q, P.q_dtype, qoff + d0), ld_as_float(P.q, P.q_dtype, qoff + d0 + 1));
+                        qa[ks][1] = pack_bf16(ld_as_float(P.q, P.q_dtype, qoff + d0 + 8), ld_as_float(P.q, P.q_dtype, qoff + d0 + 9));
                     }
                 }
             }
@@ -292,113 +433,85 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
                     merge_ml[(warp * DEC_GP + r) * 2 + 1] = l_run;
                 }
             }
-            named_bar_sync(1, DEC_NW * 32);
-            for (int idx = tid; idx < P.g * D; idx += DEC_NW * 32) {
-                const int rr = idx / D, d = idx - rr * D;
+            named_bar_sync(1, NC);
+            const bool whole = S.n_rec == 1;  // this CTA saw every page of the sequence-head: no record leaves the CTA
+            for (int item = tid; item < P.g * DG; item += NC) {
+                const int rr = item / DG, dg = item - rr * DG;
                 float M = -INFINITY;
 #pragma unroll
                 for (int w = 0; w < DEC_NW; ++w) M = fmaxf(M, merge_ml[(w * DEC_GP + rr) * 2]);
-                float acc = 0.0f, L = 0.0f;
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                float L = 0.0f;
 #pragma unroll
                 for (int w = 0; w < DEC_NW; ++w) {
                     const float mw = merge_ml[(w * DEC_GP + rr) * 2];
                     const float a = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - M);
-                    acc += a * merge_o[(w * DEC_GP + rr) * D + d];
+                    const float4 ow = *reinterpret_cast<const float4*>(merge_o + (w * DEC_GP + rr) * D + dg * 4);
+                    acc.x += a * ow.x; acc.y += a * ow.y; acc.z += a * ow.z; acc.w += a * ow.w;
                     L += a * merge_ml[(w * DEC_GP + rr) * 2 + 1];
                 }
-                if (!aborted) {
-                    P.part_o[((long long)S.slot * DEC_GP + rr) * D + d] = acc;
-                    if (d == 0) {
-                        P.part_ml[((long long)S.slot * DEC_GP + rr) * 2 + 0] = M;
-                        P.part_ml[((long long)S.slot * DEC_GP + rr) * 2 + 1] = L;
+                if (aborted) continue;
+                if (whole) {
+                    emit(S.b, S.hk, rr, dg, M, L, acc);
+                } else {
+                    *reinterpret_cast<float4*>(P.part_o + ((long long)S.slot * DEC_GP + rr) * D + dg * 4) = acc;
+                    if (dg == 0) *reinterpret_cast<float2*>(P.part_ml + ((long long)S.slot * DEC_GP + rr) * 2) = make_float2(M, L);
+                }
+            }
+            bool finished = whole;  // true in the CTA that completes the sequence-head
+            if (!whole) {
+                // The CTA that adds the last record of a sequence-head merges them all.  Every thread fences its own
+                // record stores before the barrier; the counter is bumped after it, and the merging CTA reads the
+                // records of the other CTAs from L2.  The counter is back at zero when the kernel ends.
+                __threadfence();
+                named_bar_sync(1, NC);
+                if (tid == 0) {
+                    const int seq = S.b * P.Hkv + S.hk;
+                    const unsigned prev = atomicAdd(P.seq_done + seq, 1u);
+                    const int last = prev == (unsigned)(S.n_rec - 1);
+                    if (last) {
+                        P.seq_done[seq] = 0;
+                        __threadfence();
+                    }
+                    *last_flag = last;
+                }
+                named_bar_sync(1, NC);
+                finished = *last_flag != 0;
+                if (finished) {
+                    for (int item = tid; item < P.g * DG; item += NC) {
+                        const int rr = item / DG, dg = item - rr * DG;
+                        float M = -INFINITY, L = 0.0f;
+                        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+                        for (int rec = 0; rec < S.n_rec; ++rec) {
+                            const long long sl = S.first_slot + rec;
+                            const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml + (sl * DEC_GP + rr) * 2));
+                            const float4 ow = __ldcg(reinterpret_cast<const float4*>(P.part_o + (sl * DEC_GP + rr) * D + dg * 4));
+                            if (ml.x == -INFINITY) continue;
+                            const float Mn = fmaxf(M, ml.x);
+                            const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
+                            L = L * a0 + ml.y * a1;
+                            acc.x = acc.x * a0 + ow.x * a1;
+                            acc.y = acc.y * a0 + ow.y * a1;
+                            acc.z = acc.z * a0 + ow.z * a1;
+                            acc.w = acc.w * a0 + ow.w * a1;
+                            M = Mn;
+                        }
+                        if (!aborted) emit(S.b, S.hk, rr, dg, M, L, acc);
                     }
                 }
             }
-            named_bar_sync(1, DEC_NW * 32);
-        }
-    }
-}
-
-// Merges the partial records of each (sequence, query head).
-//   mode 0: out[b][h][0][:] = sum_i O_i 2^(m_i - M) / L        (dtype f32 or bf16, strided)
-//   mode 1: partial[b][h][:] = { M ln2, L, sum_i O_i 2^(m_i - M) }   (f32, packed [B][Hq][D+2])
-struct CombineParams {
-    const float* part_o;
-    const float* part_ml;
-    const int* seq_slot_begin;  // [B*Hkv + 1]
-    void* out;
-    int out_dtype;
-    long long o_sb, o_sh;
-    int Hq, Hkv, g, D;
-    int mode;
-};
-
-// One block per (query head, sequence): D / 4 column groups (float4) x DEC_CL record lanes.  Lane r merges records
-// r, r + DEC_CL, ... with an online rescale (independent loads, no pass over the maxima first); the lanes' states meet
-// in shared memory and the threads of lane 0 fold them.  A long sequence split over hundreds of CTAs (the 128 K-token
-// configuration: ~74 records per kv head) is merged by 16 lanes in parallel instead of one thread per column in series.
-constexpr int DEC_CL = 16;  // most record lanes a block may have (the host picks 2, 8 or 16 by the records per kv head)
-
-__global__ void decode_combine_kernel(const CombineParams P) {
-    __shared__ float4 sh_acc[DEC_CL][64];
-    __shared__ float2 sh_ml[DEC_CL][64];
-    const int h = blockIdx.x, b = blockIdx.y;
-    const int seq = b * P.Hkv + h / P.g, rr = h % P.g;
-    const int s0 = P.seq_slot_begin[seq], s1 = P.seq_slot_begin[seq + 1];
-    const int groups = P.D >> 2;  // <= 64
-    const int dg = threadIdx.x % groups, lane = threadIdx.x / groups;
-    const int lanes = blockDim.x / groups;
-    float M = -INFINITY, L = 0.0f;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll 2
-    for (int s = s0 + lane; s < s1; s += lanes) {
-        const float2 ml = *reinterpret_cast<const float2*>(P.part_ml + ((long long)s * DEC_GP + rr) * 2);
-        const float4 o = *reinterpret_cast<const float4*>(P.part_o + ((long long)s * DEC_GP + rr) * P.D + dg * 4);
-        if (ml.x == -INFINITY) continue;
-        const float Mn = fmaxf(M, ml.x);
-        const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
-        L = L * a0 + ml.y * a1;
-        acc.x = acc.x * a0 + o.x * a1;
-        acc.y = acc.y * a0 + o.y * a1;
-        acc.z = acc.z * a0 + o.z * a1;
-        acc.w = acc.w * a0 + o.w * a1;
-        M = Mn;
-    }
-    sh_acc[lane][dg] = acc;
-    sh_ml[lane][dg] = make_float2(M, L);
-    __syncthreads();
-    if (lane != 0) return;
-    for (int r = 1; r < lanes; ++r) {
-        const float2 ml = sh_ml[r][dg];
-        if (ml.x == -INFINITY) continue;
-        const float4 o = sh_acc[r][dg];
-        const float Mn = fmaxf(M, ml.x);
-        const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
-        L = L * a0 + ml.y * a1;
-        acc.x = acc.x * a0 + o.x * a1;
-        acc.y = acc.y * a0 + o.y * a1;
-        acc.z = acc.z * a0 + o.z * a1;
-        acc.w = acc.w * a0 + o.w * a1;
-        M = Mn;
-    }
-    const int d = dg * 4;
-    if (P.mode == 0) {
-        const long long idx = (long long)b * P.o_sb + (long long)h * P.o_sh + d;
-        const float inv = 1.0f / L;
-        if (P.out_dtype == 0) {
-            float* o = reinterpret_cast<float*>(P.out) + idx;
-            o[0] = acc.x * inv; o[1] = acc.y * inv; o[2] = acc.z * inv; o[3] = acc.w * inv;
-        } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(P.out) + idx;
-            o[0] = __float2bfloat16_rn(acc.x * inv); o[1] = __float2bfloat16_rn(acc.y * inv);
-            o[2] = __float2bfloat16_rn(acc.z * inv); o[3] = __float2bfloat16_rn(acc.w * inv);
-        }
-    } else {
-        float* rec = reinterpret_cast<float*>(P.out) + ((long long)b * P.Hq + h) * (P.D + 2);
-        rec[2 + d] = acc.x; rec[3 + d] = acc.y; rec[4 + d] = acc.z; rec[5 + d] = acc.w;
-        if (dg == 0) {
-            rec[0] = M * 0.6931471805599453f;
-            rec[1] = L;
+            if (P.mode == 2 && finished) {
+                // the records of this sequence-head are on their way to every rank; the CTA that completes the rank's
+                // last sequence-head publishes the epoch
+                __threadfence_system();
+                named_bar_sync(1, NC);
+                if (tid == 0 && atomicAdd(P.push.done, 1u) == (unsigned)(P.B * P.Hkv) - 1) {
+                    *P.push.done = 0;
+                    peer_publish(P.push, e_push);
+                }
+            }
+            named_bar_sync(1, NC);  // the merge area is rewritten by the next segment
         }
     }
 }
@@ -454,10 +567,8 @@ __global__ void kvcache_append_kernel(const AppendParams P) {
         const long long dst = (((long long)page * P.Hkv + hk) * DEC_PT + pos % DEC_PT) * P.D + d;
         const long long ksrc = b * P.ks[0] + hk * P.ks[1] + t * P.ks[2] + d;
         const long long vsrc = b * P.vs[0] + hk * P.vs[1] + t * P.vs[2] + d;
-        const float kf = P.k_dtype == 0 ? reinterpret_cast<const float*>(P.k_new)[ksrc]
-                                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.k_new)[ksrc]);
-        const float vf = P.v_dtype == 0 ? reinterpret_cast<const float*>(P.v_new)[vsrc]
-                                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.v_new)[vsrc]);
+        const float kf = ld_as_float(P.k_new, P.k_dtype, ksrc);
+        const float vf = ld_as_float(P.v_new, P.v_dtype, vsrc);
         P.k_pages[dst] = __float2bfloat16_rn(kf);
         P.v_pages[dst] = __float2bfloat16_rn(vf);
     }
@@ -494,20 +605,47 @@ __global__ void kvcache_gather_kernel(const GatherParams P) {
         }
         const long long kd = b * P.ks[0] + hk * P.ks[1] + t * P.ks[2] + d;
         const long long vd = b * P.vs[0] + hk * P.vs[1] + t * P.vs[2] + d;
-        if (P.k_dtype == 0) reinterpret_cast<float*>(P.k_out)[kd] = kf;
-        else reinterpret_cast<__nv_bfloat16*>(P.k_out)[kd] = __float2bfloat16_rn(kf);
-        if (P.v_dtype == 0) reinterpret_cast<float*>(P.v_out)[vd] = vf;
-        else reinterpret_cast<__nv_bfloat16*>(P.v_out)[vd] = __float2bfloat16_rn(vf);
+        st_from_float(P.k_out, P.k_dtype, kd, kf);
+        st_from_float(P.v_out, P.v_dtype, vd, vf);
     }
 }
 
-__global__ void cast_f32_to_bf16_kernel(const float* src, __nv_bfloat16* dst, long long n) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-        dst[i] = __float2bfloat16_rn(src[i]);
+// Token-granular eviction of one sequence: rows [drop, drop + keep) of its pages -> dense staging [Hkv][keep][D]
+// (to_pages = 0), then staging -> rows [0, keep) of the same pages (to_pages = 1).  16 bytes per thread and step.
+struct ShiftParams {
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+    const int* row;  // the sequence's page-table row on the device
+    __nv_bfloat16* sk;
+    __nv_bfloat16* sv;
+    int Hkv, D, keep, drop;
+    int to_pages;
+};
+
+__global__ void kvcache_shift_kernel(const ShiftParams P) {
+    const int vec = P.D / 8;
+    const long long total = (long long)P.Hkv * P.keep * vec;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % vec);
+        const int t = (int)((i / vec) % P.keep);
+        const int hk = (int)(i / ((long long)vec * P.keep));
+        const long long dense = ((long long)hk * P.keep + t) * P.D + c * 8;
+        const int tok = P.to_pages ? t : t + P.drop;
+        const long long paged = (((long long)P.row[tok / DEC_PT] * P.Hkv + hk) * DEC_PT + tok % DEC_PT) * P.D + c * 8;
+        if (P.to_pages) {
+            *reinterpret_cast<uint4*>(P.k_pages + paged) = *reinterpret_cast<const uint4*>(P.sk + dense);
+            *reinterpret_cast<uint4*>(P.v_pages + paged) = *reinterpret_cast<const uint4*>(P.sv + dense);
+        } else {
+            *reinterpret_cast<uint4*>(P.sk + dense) = *reinterpret_cast<const uint4*>(P.k_pages + paged);
+            *reinterpret_cast<uint4*>(P.sv + dense) = *reinterpret_cast<const uint4*>(P.v_pages + paged);
+        }
+    }
 }
-__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* src, float* dst, long long n) {
+
+// Contiguous cast between any two of f32 / bf16 / f16 (through f32, round to nearest even).
+__global__ void cast_kernel(const void* src, int src_dtype, void* dst, int dst_dtype, long long n) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-        dst[i] = __bfloat162float(src[i]);
+        st_from_float(dst, dst_dtype, i, ld_as_float(src, src_dtype, i));
 }
 
 }  // namespace fusor

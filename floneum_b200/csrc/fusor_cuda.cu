@@ -49,7 +49,6 @@ struct fusor_cuda_ctx {
     unsigned flag_counter = 0;
     // copy streams of the _host entry points (host -> device, device -> host), created on first use
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
-    int prefill_variant = 0;  // 0 = pick by shape, 1 = always the 64-key kernel (set from FUSOR_CUDA_PREFILL_VARIANT, for A/B timing)
 };
 
 static thread_local std::string g_last_error;
@@ -118,7 +117,7 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
     if (prop.major != 10)
         return fail(nullptr, FUSOR_CUDA_NO_DEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only", device,
                     prop.major, prop.minor);
-    CUDA_TRY(nullptr, cudaSetDevice(device));
+    DeviceGuard guard(device);  // the caller's current device is restored on return
     fusor_cuda_ctx* ctx = new fusor_cuda_ctx();
     ctx->device = device;
     ctx->num_sms = prop.multiProcessorCount;
@@ -127,24 +126,25 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
     } else {
         cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
         if (e != cudaSuccess) {
-            delete ctx;
+            ctx->stream = nullptr;
+            fusor_cuda_ctx_destroy(ctx);
             return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cudaStreamCreate: %s", cudaGetErrorString(e));
         }
         ctx->owns_stream = true;
     }
     if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess ||
         cudaMalloc(&ctx->d_flags, 256 * sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_flags, 0, 256 * sizeof(int)) != cudaSuccess) {
-        delete ctx;
+        cudaGetLastError();
+        fusor_cuda_ctx_destroy(ctx);
         return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cannot allocate the device error word");
     }
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) {
-        delete ctx;
+        fusor_cuda_ctx_destroy(ctx);
         return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "cuTensorMapEncodeTiled is not available in this driver");
     }
     ctx->encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
-    if (const char* pv = std::getenv("FUSOR_CUDA_PREFILL_VARIANT")) ctx->prefill_variant = std::atoi(pv);
     // opt in to large dynamic shared memory once per context
     cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
     cudaFuncSetAttribute(prefill2_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM_BYTES);
@@ -155,7 +155,7 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
                          (int)general_smem_bytes(GEN_MAX_D));
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
-        delete ctx;
+        fusor_cuda_ctx_destroy(ctx);
         return fail(nullptr, FUSOR_CUDA_CUDA_ERROR, "kernel attribute setup: %s", cudaGetErrorString(e));
     }
     *out = ctx;
@@ -180,8 +180,11 @@ extern "C" int32_t fusor_cuda_ctx_destroy(fusor_cuda_ctx* ctx) {
 
 extern "C" int32_t fusor_cuda_ctx_set_stream(fusor_cuda_ctx* ctx, void* stream) {
     if (!ctx) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "ctx is null");
+    DeviceGuard g(ctx->device);
+    // Work queued on the old stream may still read the context's scratch buffers (the f16 copy of V, the host-call
+    // staging area); those are regrown with cudaFree after a wait on the *current* stream only, so drain the old one.
+    cudaStreamSynchronize(ctx->stream);
     if (ctx->owns_stream) {
-        cudaStreamSynchronize(ctx->stream);
         cudaStreamDestroy(ctx->stream);
         ctx->owns_stream = false;
     }
@@ -253,7 +256,7 @@ static int32_t launch_check(fusor_cuda_ctx* ctx, const char* what) {
 }
 
 static size_t dtype_size(int32_t dt) { return dt == FUSOR_CUDA_F32 ? 4 : 2; }
-static bool dtype_ok(int32_t dt) { return dt == FUSOR_CUDA_F32 || dt == FUSOR_CUDA_BF16; }
+static bool dtype_ok(int32_t dt) { return dt == FUSOR_CUDA_F32 || dt == FUSOR_CUDA_BF16 || dt == FUSOR_CUDA_F16; }
 
 extern "C" int32_t fusor_cuda_cast(fusor_cuda_ctx* ctx, void* dst, int32_t dst_dtype, const void* src, int32_t src_dtype,
                                    int64_t n) {
@@ -266,11 +269,8 @@ extern "C" int32_t fusor_cuda_cast(fusor_cuda_ctx* ctx, void* dst, int32_t dst_d
         return FUSOR_CUDA_OK;
     }
     const int blocks = (int)std::min<long long>((n + 255) / 256, (long long)ctx->num_sms * 16);
-    if (dst_dtype == FUSOR_CUDA_BF16)
-        cast_f32_to_bf16_kernel<<<blocks, 256, 0, ctx->stream>>>((const float*)src, (__nv_bfloat16*)dst, n);
-    else
-        cast_bf16_to_f32_kernel<<<blocks, 256, 0, ctx->stream>>>((const __nv_bfloat16*)src, (float*)dst, n);
-    return launch_check(ctx, "cast");
+    cast_kernel<<<blocks, 256, 0, ctx->stream>>>(src, src_dtype, dst, dst_dtype, n);
+    return launch_check(ctx, "cast_kernel");
 }
 
 // =============================================================================== attention: validation
@@ -367,9 +367,13 @@ static int32_t make_tmap_bhsd(fusor_cuda_ctx* ctx, CUtensorMap* tm, const fusor_
     return FUSOR_CUDA_OK;
 }
 
+static CUtensorMapDataType tmap_dtype(int32_t dt) {
+    return dt == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : dt == FUSOR_CUDA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+}
+
 static void set_contiguous(fusor_cuda_tensor4* t);
 static bool tma_view_ok(const fusor_cuda_tensor4* t) {
-    if (t->dtype != FUSOR_CUDA_BF16) return false;
+    if (t->dtype != FUSOR_CUDA_BF16 && t->dtype != FUSOR_CUDA_F16) return false;
     if (reinterpret_cast<uintptr_t>(t->data) % 16) return false;
     for (int i = 0; i < 3; ++i)
         if (t->shape[i] > 1 && (t->stride[i] % 8 != 0 || t->stride[i] <= 0)) return false;
@@ -387,6 +391,7 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
         return false;
     }
     if (!tma_view_ok(q) || !tma_view_ok(k) || !tma_view_ok(v)) return false;
+    if (q->dtype != k->dtype || q->dtype != v->dtype) return false;  // one 16-bit type per call: the MMA takes no mixed pair
     if (!(scale > 0.0f) || !std::isfinite(scale)) return false;
     const int al = out->dtype == FUSOR_CUDA_F32 ? 4 : 8;
     if (reinterpret_cast<uintptr_t>(out->data) % 16) return false;
@@ -395,23 +400,24 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
     return true;
 }
 
-// p_mode: 0 = f16 P with an f16 copy of V (falls back to bf16 on the device when V overflows f16), 1 = bf16 P.
+// The softmax weights are kept in f16 against an f16 copy of V (the kernels fall back to bf16 weights and the bf16 V on
+// the device when some |v| does not fit f16).
 static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
                               const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
-                              const fusor_cuda_tensor4* out, float* debug, int p_mode, int window = 0,
-                              const fusor_cuda_tensor2* key_mask = nullptr) {
+                              const fusor_cuda_tensor4* out, int window = 0, const fusor_cuda_tensor2* key_mask = nullptr) {
     // Two query tiles per CTA with 128-key blocks once a (batch, head) has 256 rows or more; the 64-key kernel with
-    // two CTAs per SM below that (and when asked for: p_mode bit 2, diagnostics).
-    const bool two_tiles = S.Sq >= P2_ROWS && (debug == nullptr || (p_mode & 8)) && (p_mode & 4) == 0 && ctx->prefill_variant != 1;
+    // two CTAs per SM below that.
+    const bool two_tiles = S.Sq >= P2_ROWS;
     const int kv_rows = two_tiles ? P2_BN : PF_BN;
+    const bool in_f16 = q->dtype == FUSOR_CUDA_F16;  // f16 tensors need no copy of V: the weights are f16 against V itself
     CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
-    TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM));
-    TRY(make_tmap_bhsd(ctx, &tmK, k, kv_rows));
-    TRY(make_tmap_bhsd(ctx, &tmV, v, kv_rows));
-    TRY(make_tmap_bhsd(ctx, &tmO, out, two_tiles ? 32 : PF_BM, out->dtype == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16));
+    TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM, tmap_dtype(q->dtype)));
+    TRY(make_tmap_bhsd(ctx, &tmK, k, kv_rows, tmap_dtype(k->dtype)));
+    TRY(make_tmap_bhsd(ctx, &tmV, v, kv_rows, tmap_dtype(v->dtype)));
+    TRY(make_tmap_bhsd(ctx, &tmO, out, two_tiles ? 32 : PF_BM, tmap_dtype(out->dtype)));
     tmV16 = tmV;
     const int* flag = nullptr;
-    if ((p_mode & 1) == 0) {
+    if (!in_f16) {
         const size_t n = (size_t)S.B * S.Hkv * S.Skv * S.D;
         if (ctx->v16_bytes < n * 2) {
             CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
@@ -445,10 +451,8 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.scale_log2 = scale * 1.4426950408889634f;
     P.n_q_tiles = two_tiles ? (S.Sq + P2_ROWS - 1) / P2_ROWS : (S.Sq + PF_BM - 1) / PF_BM;
     P.err = ctx->d_err;
-    P.debug = debug;
-    P.debug_values = (p_mode & 2) ? 0 : 1;
-    P.debug_cta = p_mode >> 8;
     P.v_f16_overflow = flag;
+    P.in_f16 = in_f16 ? 1 : 0;
     P.kmask = key_mask ? static_cast<const float*>(key_mask->data) : nullptr;
     P.kmask_stride = key_mask ? key_mask->stride[0] : 0;
     P.kmask_mul = 1.0f / scale;
@@ -470,7 +474,7 @@ extern "C" int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_c
     TRY(validate_attention(ctx, q, k, v, mask, mask_kind, window, out, &S));
     DeviceGuard g(ctx->device);
     if (prefill_eligible(S, q, k, v, scale, mask_kind, out, mask))
-        return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, nullptr, 0, window,
+        return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, window,
                               mask_kind == FUSOR_CUDA_MASK_BATCH_KEY ? mask : nullptr);
     return launch_general(ctx, S, q, k, v, scale, mask, mask_kind, window, out);
 }
@@ -483,19 +487,6 @@ extern "C" int32_t fusor_cuda_flash_attention_general(fusor_cuda_ctx* ctx, const
     TRY(validate_attention(ctx, q, k, v, mask, mask_kind, window, out, &S));
     DeviceGuard g(ctx->device);
     return launch_general(ctx, S, q, k, v, scale, mask, mask_kind, window, out);
-}
-
-// Diagnostic: runs the tensor-core prefill kernel (P format 0 = f16, 1 = bf16) and dumps, for CTA 0,
-// [128][258] floats: raw S of its first key tile, un-normalised O, running max (log2 units) and row sum.
-extern "C" int32_t fusor_cuda_prefill_probe(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
-                                            const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
-                                            const fusor_cuda_tensor4* out, int32_t p_format, float* debug_device) {
-    AttnShape S;
-    TRY(validate_attention(ctx, q, k, v, nullptr, mask_kind, 0, out, &S));
-    DeviceGuard g(ctx->device);
-    if (!prefill_eligible(S, q, k, v, scale, mask_kind, out))
-        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "arguments are not eligible for the tensor-core prefill kernel");
-    return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, debug_device, p_format);
 }
 
 // --------------------------------------------------------------------------- output projection
@@ -513,8 +504,8 @@ extern "C" int32_t fusor_cuda_attention_out_proj(fusor_cuda_ctx* ctx, const fuso
         return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "weight is [%lld, %lld]; the attention output flattens to %lld input features", N, K, Hq * D);
     if (out->shape[0] != B || out->shape[1] != 1 || out->shape[2] != S || out->shape[3] != N)
         return fail(ctx, FUSOR_CUDA_SHAPE_MISMATCH, "out must be [%lld, 1, %lld, %lld]", B, S, N);
-    if (attn->dtype != FUSOR_CUDA_BF16 || weight->dtype != FUSOR_CUDA_BF16)
-        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the output projection takes bf16 attention output and bf16 weights");
+    if (attn->dtype != FUSOR_CUDA_BF16 || weight->dtype != FUSOR_CUDA_BF16 || out->dtype == FUSOR_CUDA_F16)
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the output projection takes bf16 attention output and bf16 weights and writes f32 or bf16");
     if (D % OP_BK != 0) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "head_dim must be a multiple of %d", OP_BK);
     if (!tma_view_ok(attn)) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "attention output view is not 16-byte aligned");
     if (weight->stride[3] != 1 || weight->stride[2] % 8 != 0 || reinterpret_cast<uintptr_t>(weight->data) % 16)
@@ -529,7 +520,7 @@ extern "C" int32_t fusor_cuda_attention_out_proj(fusor_cuda_ctx* ctx, const fuso
     CUtensorMap tmA, tmW, tmO;
     TRY(make_tmap_bhsd(ctx, &tmA, attn, OP_BM));
     TRY(make_tmap_bhsd(ctx, &tmW, &w4, OP_BN));
-    TRY(make_tmap_bhsd(ctx, &tmO, out, 32, out->dtype == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16));
+    TRY(make_tmap_bhsd(ctx, &tmO, out, 32, tmap_dtype(out->dtype)));
     OprojParams P;
     P.B = (int)B; P.Hq = (int)Hq; P.S = (int)S; P.D = (int)D; P.N = (int)N;
     P.m_tiles_per_batch = (int)((S + OP_BM - 1) / OP_BM);
@@ -699,22 +690,15 @@ struct fusor_cuda_kvcache {
     int active_B = 0;
     bool table_dirty = true;
     CUtensorMap tmK, tmV;
-    // split-KV plan
-    bool plan_dirty = true;
-    int plan_g = 0;
-    int grid = 0, n_slots = 0, max_grid = 0, max_slots = 0;
-    // the plan lives in one device block [cta_seg_start: max_grid + 1][seq_slot_begin: max_batch * Hkv + 1][pad to 32 bytes]
-    // [segments: max_slots], uploaded in one copy whenever the lengths changed
-    void* d_plan = nullptr;
-    size_t plan_seg_off = 0;  // byte offset of the segments
-    std::vector<unsigned char> h_plan;
-    DecodeSegment* d_segs = nullptr;
-    int* d_cta_seg_start = nullptr;
-    int* d_seq_slot_begin = nullptr;
-    float* part_o = nullptr;
-    float* part_ml = nullptr;
-    int ring = 0;
-    size_t smem = 0;
+    // split-KV decode: the kernel deals the pages out itself from d_kv_len, the host only sizes the grid
+    int max_grid = 0, max_slots = 0;
+    int decode_ctas = 0;              // 0 = automatic grid size
+    float* part_o = nullptr;          // [max_slots][DEC_GP][D]
+    float* part_ml = nullptr;         // [max_slots][DEC_GP][2]
+    unsigned int* seq_done = nullptr; // [max_batch * Hkv], zero between launches
+    // dense staging for token-granular eviction, grown on demand
+    __nv_bfloat16* shift_buf = nullptr;
+    size_t shift_bytes = 0;
 };
 
 static int32_t kv_fail(fusor_cuda_kvcache* c, int32_t code, const char* msg) { return fail(c ? c->ctx : nullptr, code, "%s", msg); }
@@ -739,16 +723,10 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
     c->max_slots = max_batch * num_kv_heads + c->max_grid;
     bool ok = cudaMalloc(&c->k_pages, pool_bytes) == cudaSuccess && cudaMalloc(&c->v_pages, pool_bytes) == cudaSuccess &&
               cudaMalloc(&c->d_tables, ((size_t)2 * max_batch + (size_t)max_batch * max_pages_per_seq) * 4) == cudaSuccess &&
-
-              cudaMalloc(&c->d_plan, (((size_t)(c->max_grid + 1) + (size_t)(max_batch * num_kv_heads + 1)) * 4 + 31) / 32 * 32 +
-                                         (size_t)c->max_slots * sizeof(DecodeSegment)) == cudaSuccess &&
+              cudaMalloc(&c->seq_done, (size_t)max_batch * num_kv_heads * 4) == cudaSuccess &&
               cudaMalloc(&c->part_o, (size_t)c->max_slots * DEC_GP * head_dim * 4) == cudaSuccess &&
               cudaMalloc(&c->part_ml, (size_t)c->max_slots * DEC_GP * 2 * 4) == cudaSuccess;
     if (ok) {
-        c->plan_seg_off = (((size_t)(c->max_grid + 1) + (size_t)(max_batch * num_kv_heads + 1)) * 4 + 31) / 32 * 32;
-        c->d_cta_seg_start = static_cast<int*>(c->d_plan);
-        c->d_seq_slot_begin = c->d_cta_seg_start + (c->max_grid + 1);
-        c->d_segs = reinterpret_cast<DecodeSegment*>(static_cast<unsigned char*>(c->d_plan) + c->plan_seg_off);
         c->d_len_before = c->d_tables;
         c->d_kv_len = c->d_tables + max_batch;
         c->d_page_table = c->d_tables + 2 * max_batch;
@@ -756,7 +734,8 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
     if (ok) ok = cudaMemsetAsync(c->k_pages, 0, pool_bytes, ctx->stream) == cudaSuccess &&
                  cudaMemsetAsync(c->v_pages, 0, pool_bytes, ctx->stream) == cudaSuccess &&
                  cudaMemsetAsync(c->d_page_table, 0, (size_t)max_batch * max_pages_per_seq * 4, ctx->stream) == cudaSuccess &&
-                 cudaMemsetAsync(c->d_kv_len, 0, (size_t)max_batch * 4, ctx->stream) == cudaSuccess;
+                 cudaMemsetAsync(c->d_kv_len, 0, (size_t)max_batch * 4, ctx->stream) == cudaSuccess &&
+                 cudaMemsetAsync(c->seq_done, 0, (size_t)max_batch * num_kv_heads * 4, ctx->stream) == cudaSuccess;
     if (!ok) {
         cudaError_t e = cudaGetLastError();
         fusor_cuda_kvcache_destroy(c);
@@ -782,12 +761,6 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
             return fail(ctx, FUSOR_CUDA_CUDA_ERROR, "cuTensorMapEncodeTiled (page pool) failed with %d", (int)r);
         }
     }
-    // ring depth: two CTAs per SM, each within 113 KB of dynamic shared memory
-    const int page_bytes = DEC_PT * head_dim * 2;
-    // ring depth: DEC_CTAS CTAs per SM within ~227 KB of shared memory
-    const int budget = (227 * 1024) / DEC_CTAS - 1024 - 1024 - DEC_NW * DEC_GP * (head_dim + 2) * 4 - 1024;
-    c->ring = std::min(24, budget / (2 * page_bytes + 16));
-    c->smem = head_dim == 128 ? DecodeSmem<128>::bytes(c->ring) : DecodeSmem<64>::bytes(c->ring);
     *out = c;
     return FUSOR_CUDA_OK;
 }
@@ -796,7 +769,7 @@ extern "C" int32_t fusor_cuda_kvcache_destroy(fusor_cuda_kvcache* c) {
     if (!c) return FUSOR_CUDA_OK;
     DeviceGuard g(c->ctx->device);
     cudaStreamSynchronize(c->ctx->stream);
-    void* ptrs[] = {c->k_pages, c->v_pages, c->d_tables, c->d_plan, c->part_o, c->part_ml};
+    void* ptrs[] = {c->k_pages, c->v_pages, c->d_tables, c->seq_done, c->part_o, c->part_ml, c->shift_buf};
     for (void* p : ptrs)
         if (p) cudaFree(p);
 
@@ -812,7 +785,6 @@ extern "C" int32_t fusor_cuda_kvcache_reset(fusor_cuda_kvcache* c) {
     for (int i = 0; i < c->num_pages; ++i) c->free_list[i] = c->num_pages - 1 - i;
     c->active_B = 0;
     c->table_dirty = true;
-    c->plan_dirty = true;
     return FUSOR_CUDA_OK;
 }
 
@@ -876,7 +848,6 @@ static int32_t kv_reserve(fusor_cuda_kvcache* c, const fusor_cuda_tensor4* k_new
     }
     c->active_B = B;
     if (need > 0) c->table_dirty = true;  // the page table travels only when a page was mapped
-    c->plan_dirty = true;
     return kv_upload_tables(c, before.data(), B);
 }
 
@@ -1029,7 +1000,6 @@ extern "C" int32_t fusor_cuda_kvcache_set_page_table(fusor_cuda_kvcache* c, cons
         if (!used[i]) c->free_list.push_back(i);
     c->active_B = B;
     c->table_dirty = true;
-    c->plan_dirty = true;
     DeviceGuard g(ctx->device);
     return kv_sync_tables(c);
 }
@@ -1113,146 +1083,87 @@ extern "C" int32_t fusor_cuda_kvcache_truncate_front(fusor_cuda_kvcache* c, int3
         }
         for (int p = dp; p < old_pages; ++p) row[p - dp] = row[p];
     } else {
-        // token-granular shift: copy the kept rows into fresh positions through a dense staging buffer
+        // token-granular shift: the kept rows go through a dense staging buffer and back into pages 0.. of the same
+        // table row, two launches whatever the length (the row on the device is the one from before the eviction)
         const size_t elems = (size_t)c->Hkv * keep * c->D;
-        TRY(ensure_scratch(ctx, 2 * align256(elems * 2)));
-        __nv_bfloat16* sk = (__nv_bfloat16*)ctx->scratch;
-        __nv_bfloat16* sv = (__nv_bfloat16*)((uint8_t*)ctx->scratch + align256(elems * 2));
-        TRY(kv_sync_tables(c));
-        // gather rows [drop, len) of sequence b: reuse the gather kernel on a one-sequence view shifted by `drop`
-        // (implemented as a strided device copy per page row run)
-        const size_t row_bytes = (size_t)c->D * 2;
-        for (int hk = 0; hk < c->Hkv; ++hk) {
-            int t = drop;
-            while (t < len) {
-                const int page = row[t / DEC_PT];
-                const int in_page = t % DEC_PT;
-                const int run = std::min(DEC_PT - in_page, len - t);
-                const size_t src = (((size_t)page * c->Hkv + hk) * DEC_PT + in_page) * c->D;
-                const size_t dst = ((size_t)hk * keep + (t - drop)) * c->D;
-                CUDA_TRY(ctx, cudaMemcpyAsync(sk + dst, c->k_pages + src, run * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
-                CUDA_TRY(ctx, cudaMemcpyAsync(sv + dst, c->v_pages + src, run * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
-                t += run;
-            }
+        if (c->shift_bytes < 2 * elems * 2) {
+            CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            if (c->shift_buf) CUDA_TRY(ctx, cudaFree(c->shift_buf));
+            c->shift_buf = nullptr;
+            c->shift_bytes = 0;
+            const size_t want = 2 * align256((size_t)c->Hkv * c->max_pages * DEC_PT * c->D * 2);  // the longest sequence: no regrowth
+            CUDA_TRY(ctx, cudaMalloc(&c->shift_buf, want));
+            c->shift_bytes = want;
         }
+        TRY(kv_sync_tables(c));
+        ShiftParams P;
+        P.k_pages = c->k_pages; P.v_pages = c->v_pages; P.row = c->d_page_table + (size_t)b * c->max_pages;
+        P.sk = c->shift_buf; P.sv = c->shift_buf + c->shift_bytes / 4;
+        P.Hkv = c->Hkv; P.D = c->D; P.keep = keep; P.drop = drop;
+        const long long n_vec = (long long)elems / 8;
+        const int blocks = (int)std::max<long long>(1, std::min<long long>((n_vec + 255) / 256, (long long)ctx->num_sms * 8));
+        P.to_pages = 0;
+        kvcache_shift_kernel<<<blocks, 256, 0, ctx->stream>>>(P);
+        TRY(launch_check(ctx, "kvcache_shift_kernel"));
+        P.to_pages = 1;
+        kvcache_shift_kernel<<<blocks, 256, 0, ctx->stream>>>(P);
+        TRY(launch_check(ctx, "kvcache_shift_kernel"));
         const int new_pages = (keep + DEC_PT - 1) / DEC_PT;
         for (int p = new_pages; p < old_pages; ++p) {
             c->page_used[row[p]] = 0;
             c->free_list.push_back(row[p]);
         }
-        for (int hk = 0; hk < c->Hkv; ++hk) {
-            int t = 0;
-            while (t < keep) {
-                const int page = row[t / DEC_PT];
-                const int run = std::min(DEC_PT, keep - t);
-                const size_t dst = (((size_t)page * c->Hkv + hk) * DEC_PT) * c->D;
-                const size_t src = ((size_t)hk * keep + t) * c->D;
-                CUDA_TRY(ctx, cudaMemcpyAsync(c->k_pages + dst, sk + src, run * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
-                CUDA_TRY(ctx, cudaMemcpyAsync(c->v_pages + dst, sv + src, run * row_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
-                t += run;
-            }
-        }
     }
     c->h_kv_len[b] = keep;
     c->table_dirty = true;
-    c->plan_dirty = true;
     return kv_sync_tables(c);
 }
 
 // =============================================================================== decode
-// Deals the pages of all (sequence, kv head) pairs evenly to `grid` CTAs (pure host logic).
-// Flattened page order is (b, hk, page); CTA c owns global pages [c*total/grid, (c+1)*total/grid).
-// A segment is the run of pages of one (b, hk) inside one CTA's range; segments are numbered in
-// global order, so the partial records of one (b, hk) are contiguous: [seq_slot[s], seq_slot[s+1]).
-static void plan_segments(const int* kv_len, int B, int Hkv, int grid, std::vector<DecodeSegment>& segs,
-                          std::vector<int>& cta_start, std::vector<int>& seq_slot) {
-    long long total = 0;
-    for (int b = 0; b < B; ++b) total += (long long)((kv_len[b] + DEC_PT - 1) / DEC_PT) * Hkv;
-    segs.clear();
-    cta_start.assign(grid + 1, 0);
-    seq_slot.assign((size_t)B * Hkv + 1, 0);
-    int cta = 0;
-    long long pos = 0;
-    long long cta_end = total / grid;
-    int cta_off = 0;
-    for (int b = 0; b < B; ++b) {
-        const int np = (kv_len[b] + DEC_PT - 1) / DEC_PT;
-        for (int hk = 0; hk < Hkv; ++hk) {
-            seq_slot[(size_t)b * Hkv + hk] = (int)segs.size();
-            int p = 0;
-            while (p < np) {
-                while (pos >= cta_end) {
-                    ++cta;
-                    cta_start[cta] = (int)segs.size();
-                    cta_end = total * (cta + 1) / grid;
-                    cta_off = 0;
-                }
-                const int take = (int)std::min<long long>(np - p, cta_end - pos);
-                DecodeSegment s;
-                s.b = b; s.hk = hk; s.page_begin = p; s.page_end = p + take; s.kv_len = kv_len[b];
-                s.slot = (int)segs.size(); s.cta_page_off = cta_off; s.pad = 0;
-                segs.push_back(s);
-                p += take; pos += take; cta_off += take;
-            }
-        }
-    }
-    seq_slot[(size_t)B * Hkv] = (int)segs.size();
-    for (int i = cta + 1; i <= grid; ++i) cta_start[i] = (int)segs.size();
-}
-
+// The split-KV deal as pure host logic: the same functions the kernel runs (decode_splitkv.cuh), walked for every CTA.
 extern "C" int32_t fusor_cuda_decode_plan(const int32_t* kv_len, int32_t B, int32_t num_kv_heads, int32_t grid,
                                           int32_t* segments, int32_t segment_capacity, int32_t* n_segments,
-                                          int32_t* cta_seg_start, int32_t* seq_slot_begin) {
-    if (!kv_len || !segments || !n_segments || !cta_seg_start || !seq_slot_begin || B <= 0 || num_kv_heads <= 0 || grid <= 0)
+                                          int32_t* cta_seg_start) {
+    if (!kv_len || !segments || !n_segments || !cta_seg_start || B <= 0 || num_kv_heads <= 0 || grid <= 0)
         return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument or non-positive size");
     long long total = 0;
     for (int b = 0; b < B; ++b) {
         if (kv_len[b] <= 0) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "sequence %d is empty", b);
         total += (long long)((kv_len[b] + DEC_PT - 1) / DEC_PT) * num_kv_heads;
     }
-    if (grid > total) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "grid %d exceeds the %lld pages", grid, total);
-    std::vector<DecodeSegment> segs;
-    std::vector<int> cta_start, seq_slot;
-    plan_segments(kv_len, B, num_kv_heads, grid, segs, cta_start, seq_slot);
-    *n_segments = (int)segs.size();
-    if ((int)segs.size() > segment_capacity) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "segment capacity %d < %d", segment_capacity, (int)segs.size());
-    std::memcpy(segments, segs.data(), segs.size() * sizeof(DecodeSegment));
-    std::memcpy(cta_seg_start, cta_start.data(), cta_start.size() * 4);
-    std::memcpy(seq_slot_begin, seq_slot.data(), seq_slot.size() * 4);
+    static_assert(sizeof(DecodeSegment) == 9 * sizeof(int32_t), "segment record layout");
+    if (total > 0x7fffffffLL / 16) return fail(nullptr, FUSOR_CUDA_UNSUPPORTED, "more than 2^27 pages");
+    int n = 0;
+    for (int c = 0; c < grid; ++c) {
+        cta_seg_start[c] = n;
+        DecodeWalk w;
+        decode_walk_init(w, (int)total, grid, c, 0, 0);
+        DecodeSegment sg;
+        while (decode_next_segment(kv_len, B, num_kv_heads, (int)total, grid, c, w, sg)) {
+            if (n >= segment_capacity) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "segment capacity %d is too small", segment_capacity);
+            std::memcpy(segments + (size_t)n * 9, &sg, sizeof sg);
+            ++n;
+        }
+    }
+    cta_seg_start[grid] = n;
+    *n_segments = n;
     return FUSOR_CUDA_OK;
 }
 
-static int32_t build_decode_plan(fusor_cuda_kvcache* c) {
-    fusor_cuda_ctx* ctx = c->ctx;
-    const int B = c->active_B, Hkv = c->Hkv;
-    long long total = 0;
-    for (int b = 0; b < B; ++b) {
-        if (c->h_kv_len[b] <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "sequence %d is empty; decode needs at least one cached token", b);
-        total += (long long)((c->h_kv_len[b] + DEC_PT - 1) / DEC_PT) * Hkv;
-    }
-    const int grid = (int)std::min<long long>(c->max_grid, total);
-    std::vector<DecodeSegment> segs;
-    std::vector<int> cta_start, seq_slot;
-    plan_segments(c->h_kv_len.data(), B, Hkv, grid, segs, cta_start, seq_slot);
-    if ((int)segs.size() > c->max_slots) return fail(ctx, FUSOR_CUDA_INTERNAL, "plan has %d segments, room for %d", (int)segs.size(), c->max_slots);
-    if ((int)cta_start.size() > c->max_grid + 1 || (int)seq_slot.size() > c->max_batch * c->Hkv + 1)
-        return fail(ctx, FUSOR_CUDA_INTERNAL, "plan tables exceed their buffers");
-    // one staging image of the device block, one copy
-    const size_t bytes = c->plan_seg_off + segs.size() * sizeof(DecodeSegment);
-    c->h_plan.assign(bytes, 0);
-    std::memcpy(c->h_plan.data(), cta_start.data(), cta_start.size() * 4);
-    std::memcpy(c->h_plan.data() + (size_t)(c->max_grid + 1) * 4, seq_slot.data(), seq_slot.size() * 4);
-    std::memcpy(c->h_plan.data() + c->plan_seg_off, segs.data(), segs.size() * sizeof(DecodeSegment));
-    CUDA_TRY(ctx, cudaMemcpyAsync(c->d_plan, c->h_plan.data(), bytes, cudaMemcpyHostToDevice, ctx->stream));
-    c->grid = grid;
-    c->n_slots = (int)segs.size();
-    c->plan_dirty = false;
+extern "C" int32_t fusor_cuda_kvcache_set_decode_ctas(fusor_cuda_kvcache* c, int32_t ctas) {
+    if (!c) return kv_fail(c, FUSOR_CUDA_INVALID_ARGUMENT, "cache is null");
+    if (ctas < 0 || ctas > c->max_grid) return fail(c->ctx, FUSOR_CUDA_INVALID_ARGUMENT, "decode grid must be 0 (automatic) .. %d CTAs", c->max_grid);
+    c->decode_ctas = ctas;
     return FUSOR_CUDA_OK;
 }
+
+// Pages per CTA below which the automatic grid takes fewer CTAs per SM: a CTA's fixed cost (ring fill, per-segment
+// merge, its partial record and the share of the final merge) is spread over at least this many 8 KB page pairs.
+static constexpr long long kDecodeMinPagesPerCta = 24;
 
 static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fusor_cuda_tensor4* q, float scale, void* out,
-                           int out_dtype, long long o_sb, long long o_sh, int mode) {
-    if (!ctx || !c || !q || !q->data || !out) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+                           int out_dtype, long long o_sb, long long o_sh, int mode, const PeerTargets* push = nullptr) {
+    if (!ctx || !c || !q || !q->data || (!out && mode != 2)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
     if (c->ctx != ctx) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "cache belongs to another context");
     if (!dtype_ok(q->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
     if (c->active_B == 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "the cache is empty");
@@ -1265,32 +1176,41 @@ static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fus
     const int g = Hq / c->Hkv;
     if (g > DEC_GP) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "more than %d query heads per kv head", DEC_GP);
     if (q->stride[3] != 1) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the head_dim axis must be contiguous");
-    if (q->dtype == FUSOR_CUDA_BF16 && ((q->stride[0] | q->stride[1]) & 1 || reinterpret_cast<uintptr_t>(q->data) % 4))
-        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "bf16 q rows must be 4-byte aligned");
-    if (Hq > 65535 || B > 65535) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "more than 65535 heads or batches");
+    if (q->dtype != FUSOR_CUDA_F32 && ((q->stride[0] | q->stride[1]) & 1 || reinterpret_cast<uintptr_t>(q->data) % 4))
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "16-bit q rows must be 4-byte aligned");
+    if (mode == 0 && (o_sb % 4 != 0 || o_sh % 4 != 0 || reinterpret_cast<uintptr_t>(out) % (out_dtype == FUSOR_CUDA_F32 ? 16 : 8)))
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "decode output rows must start on a multiple of four elements");
+    long long total = 0;
+    for (int b = 0; b < B; ++b) {
+        if (c->h_kv_len[b] <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "sequence %d is empty; decode needs at least one cached token", b);
+        total += (long long)((c->h_kv_len[b] + DEC_PT - 1) / DEC_PT) * c->Hkv;
+    }
     DeviceGuard guard(ctx->device);
     TRY(kv_sync_tables(c));
-    if (c->plan_dirty) TRY(build_decode_plan(c));
-    DecodeParams P;
+    // grid: whole multiples of the SM count while a CTA keeps a worthwhile share, never more CTAs than pages
+    int per_sm = c->decode_ctas > 0 ? (c->decode_ctas + ctx->num_sms - 1) / ctx->num_sms
+                                    : (int)std::max<long long>(1, std::min<long long>(DEC_CTAS, total / (kDecodeMinPagesPerCta * ctx->num_sms)));
+    per_sm = std::min(per_sm, DEC_CTAS);
+    int grid = c->decode_ctas > 0 ? c->decode_ctas : per_sm * ctx->num_sms;
+    grid = (int)std::min<long long>(std::min(grid, c->max_grid), total);
+    // ring depth: `per_sm` CTAs share ~227 KB of shared memory
+    const int page_bytes = DEC_PT * c->D * 2;
+    const int budget = (227 * 1024) / per_sm - 1024 - 1024 - DEC_NW * DEC_GP * (c->D + 2) * 4 - 1024;
+    const int ring = std::max(2, std::min(24, budget / (2 * page_bytes + 16)));
+    const size_t smem = c->D == 128 ? DecodeSmem<128>::bytes(ring) : DecodeSmem<64>::bytes(ring);
+    DecodeParams P{};
     P.q = q->data; P.q_dtype = q->dtype; P.q_sb = q->stride[0]; P.q_sh = q->stride[1];
     P.page_table = c->d_page_table; P.max_pages = c->max_pages; P.num_pages = c->num_pages;
-    P.segs = c->d_segs; P.cta_seg_start = c->d_cta_seg_start;
-    P.part_o = c->part_o; P.part_ml = c->part_ml;
-    P.Hkv = c->Hkv; P.g = g; P.scale_log2 = scale * 1.4426950408889634f; P.ring = c->ring; P.err = ctx->d_err;
+    P.kv_len = c->d_kv_len; P.B = B;
+    P.part_o = c->part_o; P.part_ml = c->part_ml; P.seq_done = c->seq_done;
+    P.Hkv = c->Hkv; P.g = g; P.scale_log2 = scale * 1.4426950408889634f; P.ring = ring; P.err = ctx->d_err;
+    P.out = out; P.out_dtype = out_dtype; P.o_sb = o_sb; P.o_sh = o_sh; P.Hq = Hq; P.mode = mode;
+    if (push) P.push = *push;
     if (c->D == 128)
-        decode_splitkv_kernel<128><<<c->grid, DEC_THREADS, c->smem, ctx->stream>>>(c->tmK, c->tmV, P);
+        decode_splitkv_kernel<128><<<grid, DEC_THREADS, smem, ctx->stream>>>(c->tmK, c->tmV, P);
     else
-        decode_splitkv_kernel<64><<<c->grid, DEC_THREADS, c->smem, ctx->stream>>>(c->tmK, c->tmV, P);
-    TRY(launch_check(ctx, "decode_splitkv_kernel"));
-    CombineParams C;
-    C.part_o = c->part_o; C.part_ml = c->part_ml; C.seq_slot_begin = c->d_seq_slot_begin;
-    C.out = out; C.out_dtype = out_dtype; C.o_sb = o_sb; C.o_sh = o_sh;
-    C.Hq = Hq; C.Hkv = c->Hkv; C.g = g; C.D = c->D; C.mode = mode;
-    // record lanes per block: a kv head of a short sequence has one or two records, a 128 K-token sequence ~74
-    const int per_head = (c->n_slots + B * c->Hkv - 1) / (B * c->Hkv);
-    const int lanes = per_head <= 4 ? 2 : per_head <= 32 ? 8 : DEC_CL;
-    decode_combine_kernel<<<dim3(Hq, B), (c->D / 4) * lanes, 0, ctx->stream>>>(C);
-    return launch_check(ctx, "decode_combine_kernel");
+        decode_splitkv_kernel<64><<<grid, DEC_THREADS, smem, ctx->stream>>>(c->tmK, c->tmV, P);
+    return launch_check(ctx, "decode_splitkv_kernel");
 }
 
 extern "C" int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
@@ -1345,7 +1265,7 @@ struct fusor_cuda_exchange {
     size_t slot_floats = 0;          // capacity of one rank's records
     float* slots = nullptr;          // local: [2][world][slot_floats]
     unsigned long long* flags = nullptr;  // local: [2][world], inside the same allocation
-    unsigned int* done = nullptr;    // local: [world + 1] block counters of the push kernel, then the epoch counter (u64)
+    unsigned int* done = nullptr;    // local: block counters [0] push, [2] merge; the epoch counter (u64) 128 bytes in
     unsigned long long* epoch_dev = nullptr;
     void* base = nullptr;            // the local allocation that is exported
     size_t flags_off = 0;
@@ -1411,20 +1331,47 @@ extern "C" int32_t fusor_cuda_exchange_connect(fusor_cuda_exchange* ex, const vo
     return FUSOR_CUDA_OK;
 }
 
-extern "C" int32_t fusor_cuda_exchange_destroy(fusor_cuda_exchange* ex) {
+// Teardown has two phases with a barrier of the caller's between them: freeing an exported buffer while another
+// process still has it mapped is undefined, so every rank first closes its mappings of the others (disconnect),
+// the ranks meet, and only then does each free its own buffer (destroy).
+extern "C" int32_t fusor_cuda_exchange_disconnect(fusor_cuda_exchange* ex) {
     if (!ex) return FUSOR_CUDA_OK;
     DeviceGuard g(ex->ctx->device);
     cudaStreamSynchronize(ex->ctx->stream);
     for (int r = 0; r < ex->world; ++r)
-        if (r != ex->rank && ex->peer_base[r]) cudaIpcCloseMemHandle(ex->peer_base[r]);
+        if (r != ex->rank && ex->peer_base[r]) {
+            cudaIpcCloseMemHandle(ex->peer_base[r]);
+            ex->peer_base[r] = nullptr;
+        }
+    ex->connected = ex->world == 1;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_exchange_destroy(fusor_cuda_exchange* ex) {
+    if (!ex) return FUSOR_CUDA_OK;
+    fusor_cuda_exchange_disconnect(ex);
+    DeviceGuard g(ex->ctx->device);
     if (ex->base) cudaFree(ex->base);
     if (ex->done) cudaFree(ex->done);
     delete ex;
     return FUSOR_CUDA_OK;
 }
 
+static void exchange_targets(const fusor_cuda_exchange* ex, PeerTargets* T) {
+    for (int r = 0; r < ex->world; ++r) T->base[r] = static_cast<uint8_t*>(ex->peer_base[r]);
+    T->flags_off = ex->flags_off; T->slot_floats = ex->slot_floats;
+    T->world = ex->world; T->rank = ex->rank;
+    T->epoch = ex->epoch_dev; T->done = ex->done;
+}
+
+static void exchange_merge_params(const fusor_cuda_exchange* ex, PeerMergeParams* M, int64_t n_rows, int32_t head_dim, float* out) {
+    M->slots = ex->slots; M->flags = ex->flags; M->epoch = ex->epoch_dev; M->done = ex->done + 2;
+    M->slot_floats = ex->slot_floats; M->world = ex->world; M->D = head_dim; M->n_rows = n_rows; M->out = out;
+    M->err = ex->ctx->d_err; M->wait_limit_cycles = FUSOR_WAIT_LIMIT_CYCLES;
+}
+
 // Pushes `n_floats` of this rank's records into slot `rank` of every rank and merges all ranks' records
-// ([n_rows][head_dim + 2] each) into out [n_rows][head_dim].  Collective: every rank calls it once per step.
+// ([n_rows][head_dim + 2] each) into out [n_rows][head_dim], in one launch.  Collective: every rank calls it once per step.
 extern "C" int32_t fusor_cuda_exchange_lse_combine(fusor_cuda_exchange* ex, const float* records, int64_t n_rows,
                                                    int32_t head_dim, float* out) {
     if (!ex || !records || !out) return fail(ex ? ex->ctx : nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
@@ -1436,21 +1383,36 @@ extern "C" int32_t fusor_cuda_exchange_lse_combine(fusor_cuda_exchange* ex, cons
                     n_floats, (long long)ex->slot_floats);
     if (reinterpret_cast<uintptr_t>(records) % 16) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "records must be 16-byte aligned");
     DeviceGuard g(ctx->device);
-    PeerPushParams P{};
+    PeerPushMergeParams P{};
     P.src = reinterpret_cast<const float4*>(records);
     P.n_vec = n_floats / 4;
-    P.world = ex->world; P.rank = ex->rank;
-    P.flags_off = ex->flags_off; P.slot_floats = ex->slot_floats;
-    P.epoch = ex->epoch_dev; P.done = ex->done;
-    for (int r = 0; r < ex->world; ++r) P.base[r] = static_cast<uint8_t*>(ex->peer_base[r]);
-    const unsigned blocks = (unsigned)std::max<long long>(1, std::min<long long>((P.n_vec + 255) / 256, 8));
-    peer_push_kernel<<<dim3(blocks, ex->world), 256, 0, ctx->stream>>>(P);
-    TRY(launch_check(ctx, "peer_push_kernel"));
+    exchange_targets(ex, &P.T);
+    exchange_merge_params(ex, &P.M, n_rows, head_dim, out);
+    // every block must be resident (the blocks wait on one another's stores through the peers): one per SM at most
+    const unsigned blocks = (unsigned)std::max<long long>(1, std::min<long long>(n_rows, ctx->num_sms));
+    peer_push_merge_kernel<<<blocks, std::max(32, std::min(head_dim, 256)), 0, ctx->stream>>>(P);
+    return launch_check(ctx, "peer_push_merge_kernel");
+}
+
+// KV-chunk decode over several GPUs in two launches: the split-KV kernel, whose last CTA per (sequence, kv head)
+// stores that head's merged records on every rank, and the merge of all ranks' records.
+extern "C" int32_t fusor_cuda_exchange_decode(fusor_cuda_exchange* ex, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
+                                              float scale, float* out) {
+    if (!ex || !cache || !q || !out) return fail(ex ? ex->ctx : nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    fusor_cuda_ctx* ctx = ex->ctx;
+    if (!ex->connected) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "exchange is not connected to its peers");
+    const long long n_rows = q->shape[0] * q->shape[1];
+    if (n_rows <= 0 || n_rows * (cache->D + 2) > (long long)ex->slot_floats)
+        return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "the records of %lld rows do not fit the exchange slots (%lld floats)", n_rows,
+                    (long long)ex->slot_floats);
+    PeerTargets T{};
+    exchange_targets(ex, &T);
+    TRY(decode_impl(ctx, cache, q, scale, nullptr, FUSOR_CUDA_F32, 0, 0, 2, &T));
+    DeviceGuard g(ctx->device);
     PeerMergeParams M{};
-    M.slots = ex->slots; M.flags = ex->flags; M.epoch = ex->epoch_dev; M.slot_floats = ex->slot_floats;
-    M.world = ex->world; M.D = head_dim; M.n_rows = n_rows; M.out = out; M.err = ctx->d_err;
-    M.wait_limit_cycles = FUSOR_WAIT_LIMIT_CYCLES;
-    peer_merge_kernel<<<(unsigned)n_rows, std::min(head_dim, 256), 0, ctx->stream>>>(M);
+    exchange_merge_params(ex, &M, n_rows, cache->D, out);
+    const unsigned blocks = (unsigned)std::min<long long>(n_rows, ctx->num_sms);
+    peer_merge_kernel<<<blocks, std::max(32, std::min(cache->D, 256)), 0, ctx->stream>>>(M);
     return launch_check(ctx, "peer_merge_kernel");
 }
 
@@ -1489,6 +1451,7 @@ struct NoallocDevice {
     bool ready = false;
     unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on this device
     PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+    int num_sms = 0;
 };
 static NoallocDevice g_noalloc[64];
 static std::mutex g_noalloc_mutex;
@@ -1508,7 +1471,8 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
     local.stream = static_cast<cudaStream_t>(stream);
     AttnShape S;
     TRY(validate_attention(&local, q, k, v, nullptr, mask_kind, 0, out, &S));
-    if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL) || !prefill_eligible(S, q, k, v, scale, mask_kind, out))
+    if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL) || q->dtype != FUSOR_CUDA_BF16 ||
+        !prefill_eligible(S, q, k, v, scale, mask_kind, out))
         return fail(nullptr, FUSOR_CUDA_UNSUPPORTED,
                     "the allocation-free entry point takes bf16 q/k/v with head_dim 128, 16-byte aligned rows, "
                     "mask NONE or CAUSAL and a positive scale");
@@ -1519,6 +1483,18 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
                     "(B * Hkv * Skv * 128 <= 4194304)", v_elems, kNoallocMaxVElems);
     const long long grid = (long long)((S.Sq + PF_BM - 1) / PF_BM) * S.Hq * S.B;
     if (grid > 0x7fffffffLL) return fail(nullptr, FUSOR_CUDA_UNSUPPORTED, "grid too large");
+    // The tensor maps and the static scratch belong to the current device: all four tensors must live there.
+    {
+        const fusor_cuda_tensor4* ts[4] = {q, k, v, out};
+        const char* names[4] = {"q", "k", "v", "out"};
+        for (int i = 0; i < 4; ++i) {
+            cudaPointerAttributes at{};
+            if (cudaPointerGetAttributes(&at, ts[i]->data) != cudaSuccess || at.type != cudaMemoryTypeDevice || at.device != dev) {
+                cudaGetLastError();
+                return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "%s is not device memory of the current device %d", names[i], dev);
+            }
+        }
+    }
 
     NoallocDevice& nd = g_noalloc[dev];
     {
@@ -1542,6 +1518,7 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
             CUDA_TRY(nullptr, cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES));
             nd.scratch = static_cast<unsigned char*>(p);
             nd.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+            nd.num_sms = prop.multiProcessorCount;
             nd.ready = true;
         }
     }
@@ -1557,12 +1534,12 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
     C.s0 = v->stride[0]; C.s1 = v->stride[1]; C.s2 = v->stride[2];
     C.H = S.Hkv; C.S = S.Skv; C.D = S.D; C.n_vec = (long long)(v_elems / 8);
     C.overflow = d_overflow; C.clear_slot = d_err + 2;  // an unused header word
-    const int blocks = (int)std::min<long long>((C.n_vec + 255) / 256, 148LL * 8);
+    const int blocks = (int)std::min<long long>((C.n_vec + 255) / 256, (long long)nd.num_sms * 8);
     cast_v_to_f16_kernel<<<blocks, 256, 0, local.stream>>>(C);
     TRY(launch_check(&local, "cast_v_to_f16_kernel"));
 
     CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
-    TRY(make_tmap_bhsd(&local, &tmO, out, PF_BM, out->dtype == FUSOR_CUDA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16));
+    TRY(make_tmap_bhsd(&local, &tmO, out, PF_BM, tmap_dtype(out->dtype)));
     TRY(make_tmap_bhsd(&local, &tmQ, q, PF_BM));
     TRY(make_tmap_bhsd(&local, &tmK, k, PF_BN));
     TRY(make_tmap_bhsd(&local, &tmV, v, PF_BN));
@@ -1579,9 +1556,6 @@ extern "C" int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_
     P.scale_log2 = scale * 1.4426950408889634f;
     P.n_q_tiles = (S.Sq + PF_BM - 1) / PF_BM;
     P.err = d_err;
-    P.debug = nullptr;
-    P.debug_values = 0;
-    P.debug_cta = 0;
     P.v_f16_overflow = d_overflow;
     prefill_sm100_kernel<<<(unsigned)grid, PF_THREADS, PF_SMEM_BYTES, local.stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
     TRY(launch_check(&local, "prefill_sm100_kernel"));

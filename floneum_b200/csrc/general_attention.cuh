@@ -1,4 +1,4 @@
-// General attention kernel: f32 arithmetic on CUDA cores, any head_dim <= 256, f32 or bf16
+// General attention kernel: f32 arithmetic on CUDA cores, any head_dim <= 256, f32, bf16 or f16
 // operands with arbitrary batch/head/row strides, additive mask tensors (QKMask, BatchKeyMask)
 // or analytic causal / sliding-window masks.  It covers every call of the reference's
 // Tensor::flash_attention (fusor-ml/fusor/src/composite/flash_attention.rs:52-73) that the
@@ -20,7 +20,7 @@ struct GeneralParams {
     const void* v;
     void* out;
     const float* mask;
-    int q_dtype, k_dtype, v_dtype, out_dtype;  // 0 = f32, 1 = bf16
+    int q_dtype, k_dtype, v_dtype, out_dtype;  // 0 = f32, 1 = bf16, 2 = f16
     int B, Hq, Hkv, Sq, Skv, D;
     long long qs[3], ks[3], vs[3], os[3];  // element strides of batch, head, row
     long long ms[2];                       // mask strides
@@ -29,10 +29,7 @@ struct GeneralParams {
     float scale;
 };
 
-__device__ __forceinline__ float ld_elem(const void* p, int dtype, long long i) {
-    if (dtype == 0) return reinterpret_cast<const float*>(p)[i];
-    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
-}
+__device__ __forceinline__ float ld_elem(const void* p, int dtype, long long i) { return ld_as_float(p, dtype, i); }
 
 __global__ void __launch_bounds__(GEN_THREADS) general_attention_kernel(const GeneralParams P) {
     extern __shared__ float gen_smem[];
@@ -143,8 +140,7 @@ __global__ void __launch_bounds__(GEN_THREADS) general_attention_kernel(const Ge
             if (d < D) {
                 const float o = acc[r][i] / l[r];  // fully masked row: 0/0 = NaN, as the reference
                 const long long idx = obase + (long long)qi * P.os[2] + d;
-                if (P.out_dtype == 0) reinterpret_cast<float*>(P.out)[idx] = o;
-                else reinterpret_cast<__nv_bfloat16*>(P.out)[idx] = __float2bfloat16_rn(o);
+                st_from_float(P.out, P.out_dtype, idx, o);
             }
         }
     }

@@ -88,14 +88,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool use_f16 = P.v_f16_overflow != nullptr && *P.v_f16_overflow == 0;
-    // diagnostic timeline (probe entry point only): cycle stamps of one CTA; softmax of tile t at 512 t + 8 block + k,
-    // the MMA warp at 1024 + 8 block + k
-    const long long t_start = clock64();
-    const bool trace = P.debug != nullptr && (int)blockIdx.x == P.debug_cta;
-    auto stamp = [&](int slot) {
-        if (trace) P.debug[slot] = (float)(clock64() - t_start);
-    };
+    const bool use_f16 = P.in_f16 != 0 || (P.v_f16_overflow != nullptr && *P.v_f16_overflow == 0);
 
     // ---- work items: 256-row blocks of one (batch, head), heavy (late) row blocks first, dealt round-robin to the
     // persistent CTAs; consecutive items share a kv head.  Every role walks the same item sequence.
@@ -204,7 +197,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
         } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one_sync()) {
-            constexpr uint32_t idesc_qk = make_idesc_f16(1, 1, 0, 0, P2_BM, P2_BN);
+            const uint32_t idesc_qk = P.in_f16 ? make_idesc_f16(0, 0, 0, 0, P2_BM, P2_BN) : make_idesc_f16(1, 1, 0, 0, P2_BM, P2_BN);
             const uint32_t idesc_pv = use_f16 ? make_idesc_f16(0, 0, 0, 1, P2_BM, P2_D) : make_idesc_f16(1, 1, 0, 1, P2_BM, P2_D);
             const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(q_sm), 16, 1024);
             const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(k_sm), 16, 1024);
@@ -224,7 +217,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
             int g = 0;            // K / V blocks consumed so far (ring position)
             int cnt[2] = {0, 0};  // blocks of tile t whose PV has been issued, over all items: phase of p_full
             int qn[2] = {0, 0};   // Q tiles of tile t consumed: phase of q_full
-            bool first_item = true;
             for (int round = 0, item = item_of(0); item < n_items && ok; item = item_of(++round)) {
                 const Item I = decode(item);
                 bool fresh[2] = {true, true};  // the tile's first PV of this item overwrites O
@@ -254,9 +246,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
                         if (act(I, t, j)) {
-                            if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 0);
                             ok = mbar_wait(p_full + t, cnt[t] & 1, abort_flag, P.err, 32 + t);
-                            if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 1);
                             if (ok && !v_ready) {
                                 ok = mbar_wait(v_full + st, ph, abort_flag, P.err, 34);
                                 v_ready = true;
@@ -270,7 +260,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                                 tc_mma_ts(tmem_base + P2_COL_O + t * 128, tmem_base + P2_COL_S + t * 128 + kk * 8,
                                           vd + (uint64_t)((kk * 2048) >> 4), idesc_pv, (!fresh[t] || kk > 0));
                             ok = mbar_wait(p_full2 + t, cnt[t] & 1, abort_flag, P.err, 37 + t);
-                            if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 2);
                             if (!ok) break;
                             tc_fence_after();
 #pragma unroll
@@ -289,7 +278,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                             if (!ok) break;
                             ok = qk(t, j + 1, st1);  // overwrites the columns P_t(j) is read from: the pipe runs in issue order
                             if (!ok) break;
-                            if (first_item && i < 60) stamp(1024 + i * 8 + t * 4 + 3);
                         }
                     }
                     if (!ok) break;
@@ -299,7 +287,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 // an idle tile still releases its (unused) Q buffer, so that the producer sees one phase per item
                 for (int t = 0; t < 2 && ok; ++t)
                     if (!I.active[t]) tc_commit(q_empty + t);
-                first_item = false;
             }
         }
         }
@@ -317,7 +304,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
         uint8_t* my = stage + lane * 128;
         bool ok = true;
         int cb = 0;  // blocks of this tile processed over all items: phases of s_full and pv_done
-        bool first_item = true;
         for (int round = 0, item = item_of(0); item < n_items && ok; item = item_of(++round)) {
             const Item I = decode(item);
             const int r0 = I.q0 + t * P2_BM;
@@ -326,18 +312,14 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
             const int k_first = P.window > 0 ? qi + offset - P.window + 1 : 0;
             const int nb = I.active[t] ? I.je[t] - I.jb[t] : 0;
             float m_ref = -INFINITY, l = 0.0f;
-            const bool tr = row == 0 && first_item;
             for (int jj = 0; jj < nb && ok; ++jj, ++cb) {
-                if (tr && jj < 60) stamp(t * 512 + jj * 8 + 0);
                 ok = mbar_wait(s_full + t, cb & 1, abort_flag, P.err, 40 + t);
                 if (!ok) break;
                 tc_fence_after();
-                if (tr && jj < 60) stamp(t * 512 + jj * 8 + 1);
                 float s[P2_BN];
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) tmem_ld32(s_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
                 tc_wait_ld();
-                if (tr && jj < 60) stamp(t * 512 + jj * 8 + 2);
                 const int k0 = (I.jb[t] + jj) * P2_BN;
                 if (P.kmask != nullptr) {
                     // additive key mask of this batch row: (s + mask / scale) * scale = s * scale + mask; every thread of the
@@ -367,7 +349,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 const float m_new = (tmax > m_ref + PF_RESCALE_THRESHOLD) ? tmax : m_ref;  // also taken on the first block
                 const float alpha = (m_new == -INFINITY) ? 1.0f : fast_exp2(m_ref - m_new);
                 m_ref = m_new;
-                if (tr && jj < 60) stamp(t * 512 + jj * 8 + 3);
                 if (jj > 0) {
                     // O must hold block jj-1 before it is rescaled and before any of P(jj) is handed over.  S(jj) is ready,
                     // so the PV of block jj-1, issued before it on the in-order pipe, has completed: this wait is a formality
@@ -418,7 +399,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                             tc_wait_st();
                             tc_fence_before();
                             mbar_arrive(p_full + t);
-                            if (tr && jj < 60) stamp(t * 512 + jj * 8 + 4);
                         }
                     }
                 }
@@ -428,13 +408,10 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 ps1 = *reinterpret_cast<float2*>(&ps1u);
                 l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
                 tc_wait_st();
-                if (tr && jj < 60) stamp(t * 512 + jj * 8 + 5);
                 tc_fence_before();
                 mbar_arrive(p_full2 + t);
-                if (tr && jj < 60) stamp(t * 512 + jj * 8 + 6);
             }
             if (ok && nb > 0) ok = mbar_wait(pv_done + t, (cb - 1) & 1, abort_flag, P.err, 44 + t);
-            if (tr) stamp(2000 + t * 2);
             // Epilogue, per warp: 32 rows x 128 bytes of O / l at a time through this warp's staging area, TMA store.
             // The next item's first P_t is only handed over after these reads of O_t (program order), so the MMA warp
             // cannot overwrite O_t early; meanwhile it works for the other tile and on the next item's first S.
@@ -464,7 +441,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                     } else {
-                        // bf16: 32 columns fill half a row; one store per two chunks
+                        // bf16 / f16: 32 columns fill half a row; one store per two chunks
                         if (cc == 2) {
                             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                             __syncwarp();
@@ -473,10 +450,10 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
                             *reinterpret_cast<uint4*>(my + (((ch0 + i) ^ (lane & 7)) << 4)) =
-                                make_uint4(pack_bf16(orr[8 * i] * inv_l, orr[8 * i + 1] * inv_l),
-                                           pack_bf16(orr[8 * i + 2] * inv_l, orr[8 * i + 3] * inv_l),
-                                           pack_bf16(orr[8 * i + 4] * inv_l, orr[8 * i + 5] * inv_l),
-                                           pack_bf16(orr[8 * i + 6] * inv_l, orr[8 * i + 7] * inv_l));
+                                make_uint4(pack_16(P.out_dtype, orr[8 * i] * inv_l, orr[8 * i + 1] * inv_l),
+                                           pack_16(P.out_dtype, orr[8 * i + 2] * inv_l, orr[8 * i + 3] * inv_l),
+                                           pack_16(P.out_dtype, orr[8 * i + 4] * inv_l, orr[8 * i + 5] * inv_l),
+                                           pack_16(P.out_dtype, orr[8 * i + 6] * inv_l, orr[8 * i + 7] * inv_l));
                         if (cc & 1) {
                             fence_proxy_async_smem();
                             __syncwarp();
@@ -490,9 +467,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 // the staging area is written again in the next item: its last store must have been read out
                 if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
-                if (tr) stamp(2001 + t * 2);
             }
-            first_item = false;
         }
     }
     // ---- teardown: every role falls through to here, also after a timeout

@@ -31,9 +31,6 @@ namespace fusor {
 #ifndef PF_SBUF_CFG
 #define PF_SBUF_CFG 2
 #endif
-#ifndef PF_WHATIF
-#define PF_WHATIF 0  // timing experiments only (wrong results): 1 no ex2, 2 no row max, 3 no PV MMAs, 4 softmax skeleton
-#endif
 #ifndef PF_TPR_CFG
 #define PF_TPR_CFG 1
 #endif
@@ -49,12 +46,11 @@ constexpr int PF_KV_HALF = PF_KV_BYTES / 2;
 constexpr uint32_t PF_TMEM_COLS = 256;
 constexpr uint32_t PF_COL_S = 0, PF_COL_O = 128;  // S buffer b at PF_COL_S + PF_BN b
 constexpr float PF_RESCALE_THRESHOLD = 8.0f;      // in log2 units
-constexpr int PF_DEBUG_ROW = 258;                 // debug dump: per row raw scores [0,PF_BN), O at [128,256), m, l
 static_assert(PF_SBUF * PF_BN <= 128 && PF_CPT % 32 == 0 && (PF_TPR == 1 || PF_TPR == 2), "tile configuration");
 
 struct PrefillParams {
     void* out;
-    int out_dtype;             // 0 f32, 1 bf16
+    int out_dtype;             // 0 f32, 1 bf16, 2 f16
     long long os[3];           // element strides of batch, head, row
     int B, Hq, Hkv, Sq, Skv;
     int causal;
@@ -62,10 +58,8 @@ struct PrefillParams {
     float scale_log2;
     int n_q_tiles;
     int* err;
-    float* debug;              // optional diagnostic dump from CTA 0 (see fusor_cuda_prefill_probe)
-    int debug_values;          // dump S / O / m / l values as well as the cycle stamps
-    int debug_cta;             // which CTA is traced
     const int* v_f16_overflow; // written by the V pre-pass: non-zero when some |v| does not fit f16; null = no f16 copy
+    int in_f16;                // q, k and v are f16 (else bf16): f16 weights against V itself, no copy, no fallback
     const float* kmask;        // optional additive key mask [B][Skv] f32 (MaskKind::BatchKeyMask), added to the scaled scores
     long long kmask_stride;    // elements between batches
     float kmask_mul;           // 1 / scale: the mask is added to the raw scores as mask / scale, before the common scaling
@@ -102,20 +96,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
     float* xch = reinterpret_cast<float*>(bars + 32);  // [3][2 halves][128 rows]: partial maxima (2 buffers), row sums
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // diagnostic timeline (probe entry point only): cycle stamps of CTA 0 after the [128][258] value dump
-    const long long t_start = clock64();
-    const bool trace = P.debug != nullptr && blockIdx.x == P.debug_cta;
-    auto stamp = [&](int slot) {
-        if (trace) P.debug[128 * PF_DEBUG_ROW + slot] = (float)(clock64() - t_start);
-    };
-    auto stamp_ns = [&](int slot) {  // low 24 bits of the nanosecond wall clock
-        if (trace) {
-            unsigned long long ns;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
-            P.debug[128 * PF_DEBUG_ROW + slot] = (float)(ns & 0xFFFFFFull);
-        }
-    };
-    const bool use_f16 = P.v_f16_overflow != nullptr && *P.v_f16_overflow == 0;
+    const bool use_f16 = P.in_f16 != 0 || (P.v_f16_overflow != nullptr && *P.v_f16_overflow == 0);
 
     // ---- which tile: heavy (late) query tiles first; consecutive CTAs share a kv head
     const int heads_total = P.Hq * P.B;
@@ -180,7 +161,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one_sync()) {
             // S = Q K^T : A, B bf16, both K-major, M = 128, N = PF_BN
-            constexpr uint32_t idesc_qk = make_idesc_f16(1, 1, 0, 0, PF_BM, PF_BN);
+            const uint32_t idesc_qk = P.in_f16 ? make_idesc_f16(0, 0, 0, 0, PF_BM, PF_BN) : make_idesc_f16(1, 1, 0, 0, PF_BM, PF_BN);
             // O += P V  : A = P (TMEM, K-major), B = V MN-major, M = 128, N = D; both f16 or both bf16
             const uint32_t idesc_pv = use_f16 ? make_idesc_f16(0, 0, 0, 1, PF_BM, PF_D) : make_idesc_f16(1, 1, 0, 1, PF_BM, PF_D);
             // descriptors are built once; a k-step or a ring slot only moves the start-address field (units of 16 bytes)
@@ -204,21 +185,17 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 ok = mbar_wait(k_full + t, 0, abort_flag, P.err);
                 if (ok) {
                     tc_fence_after();
-                    stamp(400 + 2 * t);
                     issue_qk(t);
-                    stamp(401 + 2 * t);
                 }
             }
             for (int j = 0; j < n_kv && ok; ++j) {
                 const int st = j % PF_SBUF, ph = (j / PF_SBUF) & 1;
-                if (j < 32) stamp(256 + j * 4 + 0);
                 ok = mbar_wait(p_full + st, ph, abort_flag, P.err) && mbar_wait(v_full + st, ph, abort_flag, P.err);
                 if (!ok) break;
                 tc_fence_after();
-                if (j < 32) stamp(256 + j * 4 + 1);
                 const uint64_t v_desc = v_desc0 + (uint64_t)((st * PF_KV_BYTES) >> 4);
 #pragma unroll
-                for (int kk = 0; kk < (PF_WHATIF == 3 ? 1 : PF_BN / 16); ++kk) {
+                for (int kk = 0; kk < PF_BN / 16; ++kk) {
                     // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2 KB) of the V tile
                     tc_mma_ts(tmem_base + PF_COL_O, tmem_base + PF_COL_S + st * PF_BN + kk * 8,
                               v_desc + (uint64_t)((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0));
@@ -230,9 +207,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                     ok = mbar_wait(k_full + st, ((j + PF_SBUF) / PF_SBUF) & 1, abort_flag, P.err);
                     if (!ok) break;
                     tc_fence_after();
-                    if (j < 32) stamp(256 + j * 4 + 2);
                     issue_qk(j + PF_SBUF);
-                    if (j < 32) stamp(256 + j * 4 + 3);
                 }
             }
         }
@@ -252,29 +227,17 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
         const uint32_t o_tmem = tmem_base + lane_base + PF_COL_O + half * OC;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
-        const bool tr = row == 0 && half == 0;
-        if (tr) {
-            stamp(499);
-            stamp_ns(502);
-        }
         for (int j = 0; j < n_kv && ok; ++j) {
             const int st = j % PF_SBUF;
             const uint32_t s_tmem = tmem_base + lane_base + PF_COL_S + st * PF_BN;
-            if (tr && j < 32) stamp(j * 8 + 0);
             ok = mbar_wait(s_full + st, (j / PF_SBUF) & 1, abort_flag, P.err);
             if (!ok) break;
             tc_fence_after();
-            if (tr && j < 32) stamp(j * 8 + 1);
             float s[PF_CPT];
 #pragma unroll
             for (int cc = 0; cc < PF_CPT / 32; ++cc)
                 tmem_ld32(s_tmem + half * PF_CPT + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
             tc_wait_ld();
-            if (tr && j < 32) stamp(j * 8 + 2);
-            if (trace && P.debug_values && j == 0) {
-#pragma unroll
-                for (int i = 0; i < PF_CPT; ++i) P.debug[row * PF_DEBUG_ROW + half * PF_CPT + i] = s[i];
-            }
             const int k0 = (j_begin + j) * PF_BN + half * PF_CPT;
             if (P.kmask != nullptr) {
                 // additive key mask of this batch row: (s + mask / scale) * scale = s * scale + mask; every thread of the
@@ -297,11 +260,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             for (int i = 32; i < PF_CPT; i += 16)
 #pragma unroll
                 for (int a = 0; a < 8; ++a) mx[a] = fmax3(mx[a], s[i + 2 * a], s[i + 2 * a + 1]);
-#if PF_WHATIF == 2 || PF_WHATIF == 4
-            float pmax = s[0];
-#else
             float pmax = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-#endif
             if (PF_TPR == 2) {
                 // swap partial maxima with the thread that owns the other columns of this row
                 xch[((j & 1) * 2 + half) * 128 + row] = pmax;
@@ -317,7 +276,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             // and its O row stays 0, without a NaN from (-inf) - (-inf).
             const float alpha = (m_new == -INFINITY) ? 1.0f : fast_exp2(m_ref - m_new);  // 1 when unchanged, 0 on a row's first tile
             m_ref = m_new;
-            if (tr && j < 32) stamp(j * 8 + 3);
             const float m_sub = (m_ref == -INFINITY) ? 0.0f : m_ref;
             const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_sub, -m_sub);
             float2 ps0 = make_float2(0.0f, 0.0f), ps1 = make_float2(0.0f, 0.0f);
@@ -328,28 +286,17 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 for (int i = 0; i < 16; i += 2) {
                     const float2 t0 = ffma2(make_float2(s[cc * 32 + 2 * i], s[cc * 32 + 2 * i + 1]), c2, nm2);
                     const float2 t1 = ffma2(make_float2(s[cc * 32 + 2 * i + 2], s[cc * 32 + 2 * i + 3]), c2, nm2);
-#if PF_WHATIF == 1
-                    const float2 p0 = t0, p1 = t1;
-#elif PF_WHATIF == 4
-                    const float2 p0 = make_float2(s[cc * 32 + 2 * i], s[cc * 32 + 2 * i + 1]);
-                    const float2 p1 = make_float2(s[cc * 32 + 2 * i + 2], s[cc * 32 + 2 * i + 3]);
-#else
                     const float2 p0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
                     const float2 p1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
-#endif
-#if PF_WHATIF != 4
                     ps0 = fadd2(ps0, p0);
                     ps1 = fadd2(ps1, p1);
-#endif
                     pk[i] = use_f16 ? pack_f16(p0.x, p0.y) : pack_bf16(p0.x, p0.y);
                     pk[i + 1] = use_f16 ? pack_f16(p1.x, p1.y) : pack_bf16(p1.x, p1.y);
                 }
                 tmem_st16(s_tmem + (half * PF_CPT) / 2 + cc * 16, pk);  // P overwrites the first PF_BN/2 columns of this S buffer
             }
             l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
-            if (tr && j < 32) stamp(j * 8 + 4);
             tc_wait_st();
-            if (tr && j < 32) stamp(j * 8 + 5);
             if (j > 0) {
                 // O must be complete up to tile j-1 before it is rescaled and before P_j is handed over
                 ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, P.err);
@@ -375,7 +322,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             }
             tc_fence_before();
             mbar_arrive(p_full + st);
-            if (tr && j < 32) stamp(j * 8 + 6);
         }
         // the row sum is the sum over the row's threads (they used the same sequence of reference maxima)
         if (PF_TPR == 2 && ok) {
@@ -385,7 +331,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             if (ok) l += xch[(2 * 2 + (half ^ 1)) * 128 + row];
         }
         if (ok) ok = mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, P.err);
-        if (tr) stamp(500);
         // Epilogue: O / l goes through shared memory (the Q / K / V buffers are idle once the last MMA has
         // completed) in the 128-byte-swizzled layout of the output tensor map, then out with TMA stores:
         // full 128-byte lines instead of one 16-byte piece per row per instruction.  Rows past Sq are clipped.
@@ -398,14 +343,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 float orr[32];
                 tmem_ld32(o_tmem + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[0]));
                 tc_wait_ld();
-                if (trace && P.debug_values) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) P.debug[row * PF_DEBUG_ROW + 128 + half * OC + cc * 32 + i] = orr[i];
-                    if (cc == 0 && half == 0) {
-                        P.debug[row * PF_DEBUG_ROW + 256] = m_ref;
-                        P.debug[row * PF_DEBUG_ROW + 257] = l;
-                    }
-                }
                 const int col0 = half * OC + cc * 32;  // first output column of this chunk
                 if (P.out_dtype == 0) {
                     // f32: 32 columns = one 128-byte block row = 8 chunks of 16 bytes
@@ -415,16 +352,16 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                         *reinterpret_cast<float4*>(blk + ((i ^ (row & 7)) << 4)) =
                             make_float4(orr[4 * i] * inv_l, orr[4 * i + 1] * inv_l, orr[4 * i + 2] * inv_l, orr[4 * i + 3] * inv_l);
                 } else {
-                    // bf16: 32 columns = half of a 128-byte block row = 4 chunks of 16 bytes
+                    // bf16 / f16: 32 columns = half of a 128-byte block row = 4 chunks of 16 bytes
                     uint8_t* blk = base + (col0 / 64) * BLK_BYTES + row * 128;
                     const int ch0 = (col0 % 64) / 8;
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
                         *reinterpret_cast<uint4*>(blk + (((ch0 + i) ^ (row & 7)) << 4)) =
-                            make_uint4(pack_bf16(orr[8 * i] * inv_l, orr[8 * i + 1] * inv_l),
-                                       pack_bf16(orr[8 * i + 2] * inv_l, orr[8 * i + 3] * inv_l),
-                                       pack_bf16(orr[8 * i + 4] * inv_l, orr[8 * i + 5] * inv_l),
-                                       pack_bf16(orr[8 * i + 6] * inv_l, orr[8 * i + 7] * inv_l));
+                            make_uint4(pack_16(P.out_dtype, orr[8 * i] * inv_l, orr[8 * i + 1] * inv_l),
+                                       pack_16(P.out_dtype, orr[8 * i + 2] * inv_l, orr[8 * i + 3] * inv_l),
+                                       pack_16(P.out_dtype, orr[8 * i + 4] * inv_l, orr[8 * i + 5] * inv_l),
+                                       pack_16(P.out_dtype, orr[8 * i + 6] * inv_l, orr[8 * i + 7] * inv_l));
                 }
             }
             fence_proxy_async_smem();
@@ -436,18 +373,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
             for (int kb = 0; kb < n_blk; ++kb) tma_store_4d(&tmO, base + kb * BLK_BYTES, kb * blk_cols, q0, h, b);
             tma_store_commit_and_wait_read();
         }
-        if (tr) {
-            stamp(501);
-            stamp_ns(503);
-        }
     }
     // ---- teardown: every role falls through to here, also after a timeout
     tc_fence_before();
     __syncthreads();
-    if (P.debug != nullptr && tid == 0) {  // diagnostic: sum of CTA lifetimes in cycles, and their number
-        atomicAdd(&P.debug[128 * PF_DEBUG_ROW + 504], (float)(clock64() - t_start));
-        atomicAdd(&P.debug[128 * PF_DEBUG_ROW + 505], 1.0f);
-    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, PF_TMEM_COLS);

@@ -271,6 +271,19 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+// Element access by dtype code (0 = f32, 1 = bf16, 2 = f16): loads widen to f32, stores round to nearest even.
+__device__ __forceinline__ float ld_as_float(const void* p, int dtype, long long i) {
+    if (dtype == 0) return reinterpret_cast<const float*>(p)[i];
+    if (dtype == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+    return __half2float(reinterpret_cast<const __half*>(p)[i]);
+}
+__device__ __forceinline__ void st_from_float(void* p, int dtype, long long i, float v) {
+    if (dtype == 0) reinterpret_cast<float*>(p)[i] = v;
+    else if (dtype == 1) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+    else reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+// Two f32 -> one packed 16-bit pair of the given dtype code (1 = bf16, 2 = f16).
+__device__ __forceinline__ uint32_t pack_16(int dtype, float lo, float hi) { return dtype == 2 ? pack_f16(lo, hi) : pack_bf16(lo, hi); }
 // Named barrier over `nthreads` threads that also ORs a predicate across them.
 __device__ __forceinline__ int named_bar_or(int id, int nthreads, int pred) {
     int r;

@@ -20,14 +20,8 @@
 
 namespace fusor {
 
-__device__ __forceinline__ float rope_load(const void* p, int dtype, long long idx) {
-    return dtype == 0 ? reinterpret_cast<const float*>(p)[idx]
-                      : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
-}
-__device__ __forceinline__ void rope_store(void* p, int dtype, long long idx, float v) {
-    if (dtype == 0) reinterpret_cast<float*>(p)[idx] = v;
-    else reinterpret_cast<__nv_bfloat16*>(p)[idx] = __float2bfloat16_rn(v);
-}
+__device__ __forceinline__ float rope_load(const void* p, int dtype, long long idx) { return ld_as_float(p, dtype, idx); }
+__device__ __forceinline__ void rope_store(void* p, int dtype, long long idx, float v) { st_from_float(p, dtype, idx, v); }
 
 __device__ __forceinline__ void rope_pair(float xa, float xb, float c, float s, int interleaved, float& ya, float& yb) {
     if (interleaved) {
@@ -113,13 +107,22 @@ __device__ __forceinline__ void rope_load8(const void* p, int dtype, long long i
         const float4* v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + idx);
         const float4 a = __ldg(v), b = __ldg(v + 1);
         f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-    } else {
+    } else if (dtype == 1) {
         const uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + idx));
         const unsigned w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             f[2 * j] = __uint_as_float(w[j] << 16);
             f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+    } else {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p) + idx));
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 x = __half22float2(h[j]);
+            f[2 * j] = x.x;
+            f[2 * j + 1] = x.y;
         }
     }
 }
@@ -133,8 +136,12 @@ __device__ __forceinline__ void rope_store8(void* p, int dtype, long long idx, c
         float4* v = reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + idx);
         v[0] = make_float4(f[0], f[1], f[2], f[3]);
         v[1] = make_float4(f[4], f[5], f[6], f[7]);
-    } else {
+    } else if (dtype == 1) {
         *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p) + idx) = rope_pack8(f);
+    } else {
+        uint4 u;
+        u.x = pack_f16(f[0], f[1]); u.y = pack_f16(f[2], f[3]); u.z = pack_f16(f[4], f[5]); u.w = pack_f16(f[6], f[7]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p) + idx) = u;
     }
 }
 

@@ -90,14 +90,34 @@ class PeerExchange:
         _lib.check(self._L.fusor_cuda_exchange_lse_combine(self._h, records.ptr, n_rows, d, out.ptr), self.device.handle)
         return out
 
-    def close(self):
+    def decode(self, cache, q, scale: float, out):
+        """KV-chunk decode: `cache` holds this rank's chunk of the keys, `q` [B,Hq,1,D] is the same on every rank,
+        out f32 [B,Hq,D] receives the attention over all ranks' keys.  Collective, two launches."""
+        import ctypes
+        from . import _lib
+        cq = q._c4()
+        _lib.check(self._L.fusor_cuda_exchange_decode(self._h, cache._h, ctypes.byref(cq), ctypes.c_float(scale), out.ptr),
+                   self.device.handle)
+        return out
+
+    def close(self, group=None):
+        """Collective teardown in two phases: every rank unmaps the other ranks' buffers, the ranks meet, and only then
+        does each free its own (freeing an exported buffer that a peer still has mapped is undefined in CUDA)."""
         if getattr(self, "_h", None) and self.device.handle:
+            self._L.fusor_cuda_exchange_disconnect(self._h)
+            if self.world > 1:
+                import torch.distributed as dist
+                if dist.is_available() and dist.is_initialized():
+                    dist.barrier(group=group)
             self._L.fusor_cuda_exchange_destroy(self._h)
         self._h = None
 
     def __del__(self):
+        # no collective from a finaliser: a rank that forgot close() only unmaps its peers; its own buffer stays
+        # allocated until the process ends, when no peer can still be mapped to freed memory
         try:
-            self.close()
+            if getattr(self, "_h", None) and self.device.handle:
+                self._L.fusor_cuda_exchange_disconnect(self._h)
         except Exception:
             pass
 

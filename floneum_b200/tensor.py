@@ -19,8 +19,8 @@ import numpy as np
 from . import _lib
 from .device import Device
 
-F32, BF16 = _lib.F32, _lib.BF16
-_ITEMSIZE = {F32: 4, BF16: 2}
+F32, BF16, F16 = _lib.F32, _lib.BF16, _lib.F16
+_ITEMSIZE = {F32: 4, BF16: 2, F16: 2}
 
 
 class MaskKind(enum.Enum):
@@ -38,8 +38,15 @@ def _from_bf16_bits(b: np.ndarray) -> np.ndarray:
     return (b.astype(np.uint32) << 16).view(np.float32)
 
 
+def _host_bits(a: np.ndarray, dtype: int) -> np.ndarray:
+    """f32 host values -> the array that is uploaded for `dtype` (f16: numpy's own round-to-nearest-even)."""
+    if dtype == F32:
+        return a
+    return _to_bf16_bits(a) if dtype == BF16 else np.ascontiguousarray(a.astype(np.float16)).view(np.uint16)
+
+
 class Tensor:
-    """A strided view of device memory: shape, element strides, dtype (f32 or bf16)."""
+    """A strided view of device memory: shape, element strides, dtype (f32, bf16 or f16)."""
 
     def __init__(self, device: Device, ptr: int, shape: Sequence[int], dtype: int = F32,
                  strides: Optional[Sequence[int]] = None, owner=None, owns: bool = False):
@@ -68,7 +75,7 @@ class Tensor:
     def from_slice(cls, device: Device, shape: Sequence[int], data, dtype: int = F32) -> "Tensor":
         """Upload host data (any array-like of floats) as a contiguous tensor of `shape`."""
         a = np.ascontiguousarray(np.asarray(data, dtype=np.float32).reshape(shape))
-        host = a if dtype == F32 else _to_bf16_bits(a)
+        host = _host_bits(a, dtype)
         t = cls.empty(device, shape, dtype)
         L = _lib.load()
         _lib.check(L.fusor_cuda_buffer_upload(device.handle, ctypes.c_void_p(t.ptr), host.ctypes.data_as(ctypes.c_void_p),
@@ -80,9 +87,9 @@ class Tensor:
 
     @classmethod
     def from_torch(cls, device: Device, t) -> "Tensor":
-        """Borrow a CUDA torch tensor (float32 or bfloat16) without copying."""
+        """Borrow a CUDA torch tensor (float32, bfloat16 or float16) without copying."""
         import torch
-        dt = {torch.float32: F32, torch.bfloat16: BF16}[t.dtype]
+        dt = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}[t.dtype]
         return cls(device, t.data_ptr(), tuple(t.shape), dt, tuple(t.stride()), owner=t)
 
     @classmethod
@@ -111,7 +118,11 @@ class Tensor:
         _lib.check(L.fusor_cuda_buffer_download(self.device.handle, host.ctypes.data_as(ctypes.c_void_p),
                                                 ctypes.c_void_p(self.ptr), host.nbytes), self.device.handle)
         self.device.synchronize()
-        return host if self.dtype == F32 else _from_bf16_bits(host).reshape(self._shape)
+        if self.dtype == F32:
+            return host
+        if self.dtype == F16:
+            return host.view(np.float16).astype(np.float32)
+        return _from_bf16_bits(host).reshape(self._shape)
 
     def cast(self, dtype: int) -> "Tensor":
         assert self.is_contiguous()

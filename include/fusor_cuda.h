@@ -37,6 +37,8 @@ extern "C" {
 /* ---- element types (reference DataTypeEnum is F32/F16/U32, fusor-ml/core/src/tensor.rs:112-116; bf16 is added) */
 #define FUSOR_CUDA_F32 0
 #define FUSOR_CUDA_BF16 1
+#define FUSOR_CUDA_F16 2 /* the reference GPU arm is generic over f32 / f16 with f32 accumulation
+                            (fusor-ml/core/src/composite/flash_attention.rs:28-38,189) */
 
 /* ---- mask kinds (enum MaskKind, fusor-ml/fusor/src/composite/flash_attention.rs:10-19) */
 #define FUSOR_CUDA_MASK_NONE 0
@@ -101,10 +103,10 @@ int32_t fusor_cuda_cast(fusor_cuda_ctx* ctx, void* dst, int32_t dst_dtype, const
  * (fusor-ml/core/src/composite/flash_attention.rs:28-52,56-557).
  *   q [B,Hq,Sq,D], k and v [B,Hkv,Skv,D], out [B,Hq,Sq,D]; Hq % Hkv == 0, query head h reads kv head h/(Hq/Hkv).
  *   out = softmax(q k^T * scale + mask) v, f32 accumulation.
- * Dispatch: bf16 q/k/v with D == 128 and an analytic mask (NONE / CAUSAL / SLIDING) or a [B, Skv] key mask
- * (MASK_BATCH_KEY, rows contiguous) run the tcgen05 tensor-core kernels (two query tiles per CTA from Sq = 256, one
- * below); everything else (f32 inputs, any other D <= 256, [Sq, Skv] mask tensors) runs the general kernel
- * in f32 arithmetic.  out dtype f32 or bf16.  `mask` is read only for MASK_QK / MASK_BATCH_KEY;
+ * Dispatch: q/k/v all bf16 or all f16 with D == 128 and an analytic mask (NONE / CAUSAL / SLIDING) or a [B, Skv] key
+ * mask (MASK_BATCH_KEY, rows contiguous) run the tcgen05 tensor-core kernels (two query tiles per CTA from Sq = 256,
+ * one below); everything else (f32 inputs, mixed types, any other D <= 256, [Sq, Skv] mask tensors) runs the general
+ * kernel in f32 arithmetic.  out dtype f32, bf16 or f16.  `mask` is read only for MASK_QK / MASK_BATCH_KEY;
  * `window` only for MASK_SLIDING. */
 int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
                                    const fusor_cuda_tensor4* v, float scale, const fusor_cuda_tensor2* mask,
@@ -128,11 +130,14 @@ int32_t fusor_cuda_flash_attention_general(fusor_cuda_ctx* ctx, const fusor_cuda
  * whole GPU to its own memory pool at start-up, where a cudaMalloc from inside this library would fail, or a
  * latency-critical loop that cannot afford the device-wide synchronisation cudaMalloc and cudaFree imply.
  * fusor_cuda_flash_attention grows a context-owned f16 copy of V with cudaMalloc when a larger V arrives; this
- * variant runs the same two kernels (V pre-pass + tensor-core prefill) with that copy in a fixed array inside
- * the library image (8 MiB + 256 bytes per GPU, held by every GPU that loads the library until the process exits).
+ * variant runs the V pre-pass and the 64-key tensor-core prefill kernel (whatever Sq is; the allocating entry point
+ * switches to the two-tile kernel from Sq = 256, so the two agree within the tolerance of the path, not bit for bit)
+ * with that copy in a fixed array inside the library image (8 MiB + 256 bytes per GPU, held by every GPU that loads
+ * the library until the process exits).
  *   - Needs no context: it runs on the CURRENT device, on `stream` (NULL = the default stream).
  *   - Accepts what the tensor-core kernel accepts: bf16 q, k, v with head_dim 128, rows 16-byte aligned,
- *     mask_kind NONE or CAUSAL, scale > 0, out f32 or bf16; anything else returns FUSOR_CUDA_UNSUPPORTED.
+ *     mask_kind NONE or CAUSAL, scale > 0, out f32, bf16 or f16; anything else returns FUSOR_CUDA_UNSUPPORTED.
+ *     q, k, v and out must be device memory of the current device (FUSOR_CUDA_INVALID_ARGUMENT otherwise).
  *   - Limit: B * Hkv * Skv * 128 <= 4 194 304 elements of V (for example 8 kv heads x 4096 keys); larger inputs
  *     return FUSOR_CUDA_UNSUPPORTED with a message naming the limit.
  *   - Calls no cudaMalloc / cudaFree / allocating library routine.  The first call on each device resolves the
@@ -152,16 +157,6 @@ int32_t fusor_cuda_flash_attention_noalloc(void* stream, const fusor_cuda_tensor
  * FUSOR_CUDA_TIMEOUT with wait site 99.  The context stays usable: this is how a lost producer / consumer inside
  * the attention kernels surfaces, instead of a hang. */
 int32_t fusor_cuda_selftest_wait_limit(fusor_cuda_ctx* ctx);
-
-/* Diagnostic (no reference counterpart): runs the tensor-core prefill kernel with the softmax weights kept as f16 against an
- * f16 copy of V (p_format 0, the production setting) or as bf16 against the bf16 V (p_format 1) and copies out of the first CTA, into debug_device (f32, 128*258 + 512 values), per row the raw scores of its
- * first key tile [0,128), its un-normalised O [128,256), the running max in log2 units [256] and the row sum [257],
- * followed by 512 cycle stamps of that CTA's softmax and MMA loops (a timeline for tuning).  p_format + 2 writes
- * the cycle stamps only; bits 8 and up select the traced CTA (default 0).
- * Fails with FUSOR_CUDA_UNSUPPORTED when the arguments are not eligible for that kernel. */
-int32_t fusor_cuda_prefill_probe(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
-                                 const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
-                                 const fusor_cuda_tensor4* out, int32_t p_format, float* debug_device);
 
 /* ------------------------------------------------------------------------------------------------
  * Paged bf16 KV cache.  Replaces fusor::cache::KvCache / TensorCache
@@ -199,7 +194,9 @@ int32_t fusor_cuda_kvcache_rope_append(fusor_cuda_kvcache* cache, const fusor_cu
                                        const fusor_cuda_tensor4* k_new, const fusor_cuda_tensor4* v_new, const float* cos,
                                        const float* sin, int32_t context_length, int32_t start_pos, int32_t interleaved,
                                        const fusor_cuda_tensor4* q_out);
-/* TensorCache eviction (tensor_cache.rs:55-78): keep only the newest `keep` tokens of sequence b. */
+/* TensorCache eviction (tensor_cache.rs:55-78): keep only the newest `keep` tokens of sequence b.  Whole pages fall
+ * off the table row on the host; a drop that is not a multiple of the page size moves the kept rows with two kernel
+ * launches (through a staging buffer the cache allocates on first use), whatever the length. */
 int32_t fusor_cuda_kvcache_truncate_front(fusor_cuda_kvcache* cache, int32_t b, int32_t keep);
 /* KvCache::current_seq_len (kv_cache.rs:65-67) of sequence b. */
 int32_t fusor_cuda_kvcache_seq_len(fusor_cuda_kvcache* cache, int32_t b, int32_t* len);
@@ -223,15 +220,20 @@ int32_t fusor_cuda_kvcache_gather(fusor_cuda_kvcache* cache, const fusor_cuda_te
 /* ------------------------------------------------------------------------------------------------
  * Decode: one query token per sequence against the paged cache (the Sq == 1 regime of the call site,
  * models/kalosm-llama/src/raw/attention_layer.rs:405-448; all-zero mask [1, kv_len]).
- *   q [B,Hq,1,D] (bf16 or f32), out [B,Hq,1,D] (f32 or bf16).
- * Split-KV: the pages of all (sequence, kv head) pairs are dealt evenly to a persistent grid; each CTA emits
- * a partial (m, l, O) per run of pages, and a combine kernel merges them by log-sum-exp. */
+ *   q [B,Hq,1,D] (bf16, f16 or f32; rounded to bf16, the type of the cached keys), out [B,Hq,1,D] (f32, bf16 or f16;
+ *   rows start on a multiple of four elements).
+ * Split-KV in one launch: the pages of all (sequence, kv head) pairs are dealt evenly to a persistent grid by the
+ * kernel itself, from the lengths on the device (a step after an append uploads no plan); each CTA emits a partial
+ * (m, l, O) per run of pages, and the CTA that completes a (sequence, kv head) merges its partials by log-sum-exp. */
 int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
                                           float scale, const fusor_cuda_tensor4* out);
 /* Same, but leaves the result un-normalised for a merge across GPUs that each hold a chunk of the keys:
  * partial f32 [B][Hq][D+2] = { m = max scaled score, l = sum exp(s - m), O[D] = sum exp(s - m) v }. */
 int32_t fusor_cuda_flash_attention_decode_partial(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
                                                   const fusor_cuda_tensor4* q, float scale, float* partial);
+/* Grid size of the decode kernel: 0 (default) = chosen from the number of cached pages, in whole multiples of the SM
+ * count; n > 0 = exactly n CTAs (tuning; the reference has no counterpart, its kernel has one workgroup per row). */
+int32_t fusor_cuda_kvcache_set_decode_ctas(fusor_cuda_kvcache* cache, int32_t ctas);
 /* ------------------------------------------------------------------------------------------------
  * Exchange of split-KV records between the GPUs of one node over peer memory (no counterpart in the reference, which
  * has no multi-GPU path).  Each rank owns a buffer of [2 parities][world] record slots and epoch flags; the ranks map
@@ -241,15 +243,25 @@ int32_t fusor_cuda_flash_attention_decode_partial(fusor_cuda_ctx* ctx, fusor_cud
  *   create      : allocates this rank's buffer; slot_floats = capacity of one rank's records (multiple of 4)
  *   handle      : 64-byte handle of the local buffer, to be sent to every rank by the caller's own transport
  *   connect     : handles of all ranks, [world][64] bytes in rank order (own entry ignored)
- *   lse_combine : collective, stream-ordered, graph-capturable.  records f32 [n_rows][head_dim + 2] = { m (natural-log
- *                 units), l, O[head_dim] } of this rank -> out f32 [n_rows][head_dim], merged over all ranks as
- *                 fusor_cuda_lse_combine does. */
+ *   lse_combine : collective, stream-ordered, one launch (push, publish, wait, merge).  records f32 [n_rows][head_dim + 2]
+ *                 = { m (natural-log units), l, O[head_dim] } of this rank -> out f32 [n_rows][head_dim], merged over
+ *                 all ranks as fusor_cuda_lse_combine does.
+ *   decode      : collective, stream-ordered, two launches: fusor_cuda_flash_attention_decode_partial over this rank's
+ *                 chunk of the keys with the records stored on every rank by the decode kernel itself, then the merge.
+ *                 q [B,Hq,1,D] is the same on every rank; out f32 [B*Hq][head_dim] is the attention over all ranks' keys.
+ *   disconnect / destroy : teardown in two phases.  Every rank calls disconnect (waits for its stream, closes its
+ *                 mappings of the other ranks' buffers); the caller then runs a barrier of its own over the ranks;
+ *                 only after it does each rank call destroy, which frees the exported buffer.  Freeing an exported
+ *                 buffer that another process still has mapped is undefined behaviour in CUDA. */
 typedef struct fusor_cuda_exchange fusor_cuda_exchange;
 int32_t fusor_cuda_exchange_create(fusor_cuda_ctx* ctx, int32_t world, int32_t rank, int64_t slot_floats,
                                    fusor_cuda_exchange** out);
 int32_t fusor_cuda_exchange_handle(fusor_cuda_exchange* ex, void* handle64);
 int32_t fusor_cuda_exchange_connect(fusor_cuda_exchange* ex, const void* handles);
+int32_t fusor_cuda_exchange_disconnect(fusor_cuda_exchange* ex);
 int32_t fusor_cuda_exchange_destroy(fusor_cuda_exchange* ex);
+int32_t fusor_cuda_exchange_decode(fusor_cuda_exchange* ex, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q, float scale,
+                                   float* out);
 int32_t fusor_cuda_exchange_lse_combine(fusor_cuda_exchange* ex, const float* records, int64_t n_rows, int32_t head_dim,
                                         float* out);
 
@@ -265,17 +277,17 @@ int32_t fusor_cuda_attention_out_proj(fusor_cuda_ctx* ctx, const fusor_cuda_tens
                                       const float* bias, const fusor_cuda_tensor4* out);
 /* Merge: parts f32 [n_parts][n_rows][D+2] -> out f32 [n_rows][D]  (M = max m, L = sum l e^(m-M),
  * out = sum O e^(m-M) / L; the (m, d) rule of fusor-ml/core/src/composite/softmax.rs:59-82).
- * A part with l == 0 contributes nothing. */
+ * A part with l == 0 contributes nothing; a row whose parts are all empty gives zeros. */
 int32_t fusor_cuda_lse_combine(fusor_cuda_ctx* ctx, const float* parts, int32_t n_parts, int64_t n_rows,
                                int32_t head_dim, float* out);
-/* The split-KV work plan, as pure host logic (no device needed): deals the 16-token pages of all
- * (sequence, kv head) pairs, flattened in (b, hk, page) order, evenly to `grid` CTAs.  Writes
- * segments as int32[8] records {b, hk, page_begin, page_end, kv_len, slot, cta_page_offset, 0},
- * cta_seg_start [grid + 1] and seq_slot_begin [B * num_kv_heads + 1].  No reference counterpart
- * (the reference has no split-KV); exported so the partition can be checked without a GPU. */
+/* The split-KV deal, as pure host logic (no device needed; the decode kernel runs the same functions per CTA): the
+ * 16-token pages of all (sequence, kv head) pairs, numbered in (b, hk, page) order, go to `grid` CTAs as
+ * [c T / grid, (c + 1) T / grid).  Writes segments as int32[9] records {b, hk, page_begin, page_end, kv_len, slot,
+ * cta_page_offset, n_records, first_slot} in CTA order and cta_seg_start [grid + 1].  `slot` = b * num_kv_heads + hk + c
+ * is where CTA c's partial record of that (sequence, kv head) lives; its records are [first_slot, first_slot + n_records).
+ * No reference counterpart (the reference has no split-KV); exported so the partition can be checked without a GPU. */
 int32_t fusor_cuda_decode_plan(const int32_t* kv_len, int32_t B, int32_t num_kv_heads, int32_t grid, int32_t* segments,
-                               int32_t segment_capacity, int32_t* n_segments, int32_t* cta_seg_start,
-                               int32_t* seq_slot_begin);
+                               int32_t segment_capacity, int32_t* n_segments, int32_t* cta_seg_start);
 /* Host-memory variant of decode: uploads q, runs, downloads out, synchronises. */
 int32_t fusor_cuda_flash_attention_decode_host(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
                                                const fusor_cuda_tensor4* q, float scale,

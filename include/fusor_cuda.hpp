@@ -28,7 +28,7 @@
 namespace fusor_cuda {
 
 enum class MaskKind { QKMask, BatchKeyMask };
-enum class DType : int32_t { F32 = FUSOR_CUDA_F32, BF16 = FUSOR_CUDA_BF16 };
+enum class DType : int32_t { F32 = FUSOR_CUDA_F32, BF16 = FUSOR_CUDA_BF16, F16 = FUSOR_CUDA_F16 };
 
 class Device {
   public:
@@ -96,6 +96,8 @@ class Tensor {
         if (dt == DType::F32) {
             dev->check(fusor_cuda_buffer_upload(dev->raw(), t.data(), data.data(), data.size() * 4));
             dev->synchronize();
+        } else if (dt == DType::F16) {  // rounded on the device (round to nearest even), like any other cast
+            return from_slice(dev, shape, data, DType::F32).cast(DType::F16);
         } else {
             std::vector<uint16_t> h(data.size());
             for (size_t i = 0; i < data.size(); ++i) h[i] = detail::to_bf16(data[i]);
@@ -122,6 +124,8 @@ class Tensor {
         std::vector<float> out(numel());
         if (dtype_ == DType::F32) {
             dev_->check(fusor_cuda_buffer_download(dev_->raw(), out.data(), data(), out.size() * 4));
+        } else if (dtype_ == DType::F16) {
+            return cast(DType::F32).as_slice();
         } else {
             std::vector<uint16_t> h(out.size());
             dev_->check(fusor_cuda_buffer_download(dev_->raw(), h.data(), data(), h.size() * 2));
@@ -392,6 +396,40 @@ inline Tensor<4> CachedKv::to_tensor(DType dt) const {
     auto kv = cache->dense(dt);
     return is_k ? kv.first : kv.second;
 }
+
+// LlamaCache (models/kalosm-llama/src/raw/cache.rs:14-54): one KvCache per layer, concatenating along axis 2.  With a
+// sliding-window model, layer i keeps `sliding_window_size` tokens unless (i + 1) % sliding_window_type == 0, in which
+// case (and for models without a window) it keeps `context_length` tokens.  The layer loop hands blocks[i] to layer i
+// (models/kalosm-llama/src/raw/mod.rs:614-627).
+struct LlamaCacheConfig {
+    size_t n_layer = 0;
+    size_t context_length = 0;
+    std::optional<size_t> sliding_window_type;
+    std::optional<size_t> sliding_window_size;
+};
+
+class LlamaCache {
+  public:
+    static constexpr size_t CONCAT_DIMENSION = 2;
+    explicit LlamaCache(const LlamaCacheConfig& config) {
+        blocks.reserve(config.n_layer);
+        for (size_t layer_idx = 0; layer_idx < config.n_layer; ++layer_idx)
+            blocks.push_back(std::make_unique<KvCache>(CONCAT_DIMENSION, layer_max_seq_len(config, layer_idx)));
+    }
+    static size_t layer_max_seq_len(const LlamaCacheConfig& config, size_t layer_idx) {
+        if (config.sliding_window_type && config.sliding_window_size) {
+            const bool is_sliding = (layer_idx + 1) % *config.sliding_window_type != 0;
+            if (is_sliding) return *config.sliding_window_size;
+        }
+        return config.context_length;
+    }
+    void clear() {
+        for (auto& b : blocks) b->reset();
+    }
+    uint32_t start_time = 0;
+    std::vector<uint32_t> tokens;
+    std::vector<std::unique_ptr<KvCache>> blocks;
+};
 
 // q.flash_attention(k, v, ...) on the views KvCache::append returned
 inline Tensor<4> flash_attention(const Tensor<4>& q, const CachedKv& k, const CachedKv& v, float scale, const MaskArg& mask = std::nullopt,

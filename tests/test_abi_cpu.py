@@ -54,32 +54,39 @@ def _plan(kv_len, Hkv, grid):
     kv = np.ascontiguousarray(kv_len, np.int32)
     B = kv.size
     cap = B * Hkv + grid
-    segs = np.zeros((cap, 8), np.int32)
+    segs = np.zeros((cap, 9), np.int32)
     n = ctypes.c_int32()
     cta = np.zeros(grid + 1, np.int32)
-    seq = np.zeros(B * Hkv + 1, np.int32)
     p = ctypes.POINTER(ctypes.c_int32)
     rc = L.fusor_cuda_decode_plan(kv.ctypes.data_as(p), B, Hkv, grid, segs.ctypes.data_as(p), cap, ctypes.byref(n),
-                                  cta.ctypes.data_as(p), seq.ctypes.data_as(p))
+                                  cta.ctypes.data_as(p))
     assert rc == 0, L.fusor_cuda_last_error(None)
-    return segs[:n.value], cta, seq
+    return segs[:n.value], cta
 
 
 @pytest.mark.parametrize("kv_len,Hkv,grid", [([1], 1, 1), ([17, 5, 300], 2, 7), ([1024, 8192, 4000, 1025], 8, 296),
-                                             ([131072], 8, 296), (list(range(1, 70)), 3, 148)])
+                                             ([131072], 8, 296), (list(range(1, 70)), 3, 148), ([16] * 5, 2, 10),
+                                             ([33, 1, 1, 2000], 1, 592), ([7], 4, 3)])
 def test_decode_plan_partitions_every_page_once_and_evenly(kv_len, Hkv, grid):
+    """The deal the decode kernel computes per CTA (same functions, walked on the host): every page exactly once, shares
+    within one page of each other, and the partial records of one (sequence, kv head) in a contiguous run of slots that
+    no other (sequence, kv head) touches."""
     pages = [(n + 15) // 16 for n in kv_len]
     total = sum(pages) * Hkv
     grid = min(grid, total)
-    segs, cta, seq = _plan(kv_len, Hkv, grid)
+    segs, cta = _plan(kv_len, Hkv, grid)
     seen = {}
     per_cta = np.zeros(grid, np.int64)
     assert cta[0] == 0 and cta[-1] == len(segs) and np.all(np.diff(cta) >= 0)
+    slots = {}
     for c in range(grid):
         off = 0
         for i in range(cta[c], cta[c + 1]):
-            b, hk, p0, p1, n, slot, coff, _ = segs[i]
-            assert slot == i and n == kv_len[b] and 0 <= p0 < p1 <= pages[b] and coff == off
+            b, hk, p0, p1, n, slot, coff, n_rec, first = segs[i]
+            assert n == kv_len[b] and 0 <= p0 < p1 <= pages[b] and coff == off
+            assert slot == b * Hkv + hk + c and first <= slot < first + n_rec and slot < len(kv_len) * Hkv + grid
+            assert slot not in slots, "two segments share a record slot"
+            slots[slot] = (b, hk)
             for pg in range(p0, p1):
                 assert (b, hk, pg) not in seen
                 seen[(b, hk, pg)] = c
@@ -87,14 +94,17 @@ def test_decode_plan_partitions_every_page_once_and_evenly(kv_len, Hkv, grid):
         per_cta[c] = off
     assert len(seen) == total
     assert per_cta.max() - per_cta.min() <= 1  # even split
-    # partial records of one (sequence, kv head) are contiguous and in page order
-    for b in range(len(kv_len)):
-        for hk in range(Hkv):
-            s0, s1 = seq[b * Hkv + hk], seq[b * Hkv + hk + 1]
-            assert s1 > s0
-            rng = [(segs[i][2], segs[i][3]) for i in range(s0, s1)]
-            assert all(segs[i][0] == b and segs[i][1] == hk for i in range(s0, s1))
-            assert rng[0][0] == 0 and rng[-1][1] == pages[b] and all(rng[i][1] == rng[i + 1][0] for i in range(len(rng) - 1))
+    # per (sequence, kv head): n_records segments, in page order, filling exactly [first_slot, first_slot + n_records)
+    by_seq = {}
+    for sg in segs:
+        by_seq.setdefault((sg[0], sg[1]), []).append(sg)
+    assert len(by_seq) == len(kv_len) * Hkv
+    for (b, hk), lst in by_seq.items():
+        lst.sort(key=lambda s: s[2])
+        assert lst[0][2] == 0 and lst[-1][3] == pages[b] and all(lst[i][3] == lst[i + 1][2] for i in range(len(lst) - 1))
+        n_rec, first = lst[0][7], lst[0][8]
+        assert all(s[7] == n_rec and s[8] == first for s in lst) and len(lst) == n_rec
+        assert sorted(s[5] for s in lst) == list(range(first, first + n_rec))
 
 
 def test_decode_plan_rejects_bad_input():
@@ -105,7 +115,7 @@ def test_decode_plan_rejects_bad_input():
     buf = np.zeros(64, np.int32)
     n = ctypes.c_int32()
     rc = L.fusor_cuda_decode_plan(kv.ctypes.data_as(p), 1, 1, 1, buf.ctypes.data_as(p), 8, ctypes.byref(n),
-                                  buf.ctypes.data_as(p), buf.ctypes.data_as(p))
+                                  buf.ctypes.data_as(p))
     assert rc == _lib.INVALID_ARGUMENT
 
 
