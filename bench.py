@@ -1,14 +1,19 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path.  One JSON line on stdout (rank 0).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg2|cfg3|cfg4|cfg5|oproj|rope] [--impl reference]
 
 Workload at N = 1 (default): BASELINE config 2, causal flash-attention prefill, B4 S4096 Hq32 Hkv8 D128,
 bf16 inputs, f32 output; metric = attention TFLOP/s from the algorithmic causal FLOPs 4 B Hq D S(S+1)/2.
 A "step" is one pass of the kernel over the batch.  With N > 1 (torchrun, one rank per GPU) the kv heads are split
-over the ranks (strong scaling, no collective); `--workload cfg4` runs the long-context KV-chunk decode whose partials
-are combined over NCCL.  `value` is timed with inputs resident in HBM; `e2e` is the same metric through the host-buffer
-C-ABI entry point with the copies inside the timed region.  The line also carries the decode (config 3) GB/s at N = 1.
+over the ranks (strong scaling, no collective).  `value` is timed with inputs resident in HBM; `e2e` is the same metric
+through the host-buffer C-ABI entry point with the copies inside the timed region.  At every N the line also carries
+  decode       config 3 (paged GQA decode, kv heads split over the ranks, no collective), KV GB/s
+  decode_long  config 4 (131072-key decode, KV sequence split into contiguous chunks over the ranks; the ranks' partial
+               records are exchanged over peer memory and merged: the one collective of the path), KV GB/s
+  oproj        (N > 1) the head-sharded output projection with the library's all-reduce
+each with its own roofline, parity block against the oracle and per-rank times.
+`--workload cfg1` runs the CPU-reference configuration (f32, general kernel) with the CPU port timed in full.
 `--impl reference` times the CPU restatement of the reference's attention (oracle/) on the host cores instead.
 """
 from __future__ import annotations
@@ -16,6 +21,7 @@ from __future__ import annotations
 import argparse
 import ctypes
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -28,6 +34,7 @@ sys.path.insert(0, ROOT)
 import numpy as np  # noqa: E402
 
 METRIC = "attention TFLOP/s (prefill) and KV GB/s (decode) at 1/2/4/8 B200 vs roofline"
+DATA = "synthetic (seeded N(0,1) rounded to bf16; random values, no weights)"
 
 
 def load_peaks():
@@ -37,6 +44,39 @@ def load_peaks():
         return {"hbm": d["hbm_gbs"], "tensor_burst": d["bf16_tflops"], "tensor_sustained": d["bf16_tflops_sustained"],
                 "source": "measured"}
     return {"hbm": 6650.0, "tensor_burst": 1590.0, "tensor_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------- workload descriptions
+# The `config` object of a line depends on the workload and the number of ranks only, so that both arms print the same one.
+def workload_config(name: str, world: int) -> dict:
+    if name == "cfg1":
+        return {"workload": "cfg1: causal attention B1 S512 Hq32 Hkv8 D64, f32 in, f32 out (the CPU-reference configuration)",
+                "flops_per_step": 4.0 * 32 * 64 * 512 * 513 / 2, "sharding": f"kv heads split over {world} rank(s), no collective",
+                "l2": "inputs rotate over copies; at 1.3 MB per copy the working set is L2-resident by nature"}
+    if name in ("cfg2", "cfg5"):
+        B, S, Hq, Hkv = (4, 4096, 32, 8) if name == "cfg2" else (1, 16384, 64, 8)
+        return {"workload": f"{name}: causal flash-attention prefill B{B} S{S} Hq{Hq} Hkv{Hkv} D128, bf16 in, f32 out",
+                "flops_per_step": 4.0 * B * Hq * 128 * S * (S + 1) / 2, "sharding": f"kv heads split over {world} rank(s), no collective",
+                "l2": "inputs rotate over copies larger than L2 in total, so each launch reads HBM-cold data"}
+    if name == "cfg3":
+        return {"workload": "cfg3: paged GQA decode B64 Hq32 Hkv8 D128, 16-token pages, kv_len ~ U[1024, 8192], permuted page table",
+                "sharding": f"kv heads split over {world} rank(s), no collective",
+                "l2": "the KV cache rotates over copies larger than L2 in total, so each launch reads HBM-cold data"}
+    if name == "cfg4":
+        return {"workload": "cfg4: long-context decode B1 Hq64 Hkv8 D128, 131072 keys, 16-token pages",
+                "sharding": (f"KV sequence split into {world} contiguous chunks; partial (m, l, O) records stored on every rank over "
+                             "peer memory by the decode kernel and merged by log-sum-exp" if world > 1 else "one GPU holds the whole sequence"),
+                "l2": "the KV cache rotates over copies larger than L2 in total, so each launch reads HBM-cold data"}
+    if name == "oproj":
+        return {"workload": "oproj: out = attn[B4,Hq32,S4096,D128] (read in place) x W[4096,4096]^T, bf16 in, f32 out",
+                "flops_per_step": 2.0 * 4 * 4096 * 4096 * 32 * 128,
+                "sharding": f"query heads split over {world} rank(s)" + (", partial sums all-reduced (NCCL behind the C ABI)" if world > 1 else ""),
+                "l2": "the attention input rotates over copies"}
+    if name == "rope":
+        return {"workload": "rope: fused RoPE + KV-cache append, B4 Hq32 Hkv8 S4096 D128, bf16 in, bf16 pages",
+                "sharding": f"heads split over {world} rank(s), no collective",
+                "l2": "300 MB buffer written between timed launches; table uploads are inside the timed region"}
+    raise ValueError(name)
 
 
 class ClockSampler:
@@ -68,7 +108,8 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.f.close()
-        mhz, mx, reasons, allmhz = [], [], set(), []
+        self.proc = None
+        mhz, mx, reasons = [], [], set()
         for line in open(self.path):
             c = [x.strip() for x in line.split(",")]
             if len(c) < 9:
@@ -79,7 +120,6 @@ class ClockSampler:
                 m = float(c[2])
             except ValueError:
                 continue
-            allmhz.append(f)
             if not (t0 - 0.05 <= ts <= t1 + 0.05):
                 continue
             mhz.append(f)
@@ -97,9 +137,9 @@ class ClockSampler:
         return out
 
 
-# ------------------------------------------------------------------------------------------- CPU baseline
+# ------------------------------------------------------------------------------------------- CPU baseline (oracle port)
 def cpu_prefill_sample(w):
-    """Bounded sample of the prefill workload for the CPU arm: batch 0, kv head 0 with its g query heads, every row,
+    """Bounded sample of a prefill workload for the CPU arm: batch 0, kv head 0 with its g query heads, every row,
     evaluated densely with a [S,S] 0/-inf mask tensor exactly as the reference CPU composite does."""
     from oracle import oracle as O
     g = w.q.shape[1] // w.k.shape[1]
@@ -107,8 +147,18 @@ def cpu_prefill_sample(w):
     S = q.shape[2]
     mask = O.causal_mask(S)
     flops = 4.0 * g * q.shape[3] * S * (S + 1) / 2
-    desc = f"batch 0, kv head 0 ({g} query heads), all {S} rows, dense f32 composite with a [{S},{S}] mask tensor"
+    desc = (f"batch 0, kv head 0 ({g} query heads), all {S} rows, dense f32 composite with a [{S},{S}] mask tensor; causal FLOPs are "
+            "counted for the dense evaluation the reference performs")
     return (lambda: O.flash_attention(q, k, v, w.scale, mask, O.MASK_QK)), flops, desc
+
+
+def cpu_full_prefill(w):
+    """The whole tensor through the composite, as the reference runs it (config 1)."""
+    from oracle import oracle as O
+    S = w.q.shape[2]
+    mask = O.causal_mask(S)
+    return (lambda: O.flash_attention(w.q, w.k, w.v, w.scale, mask, O.MASK_QK)), w.flops, \
+        f"the full tensor, dense f32 composite with a [{S},{S}] mask tensor"
 
 
 def cpu_decode_sample(w, n_seq=8):
@@ -116,10 +166,11 @@ def cpu_decode_sample(w, n_seq=8):
     n_seq = min(n_seq, w.q.shape[0])
     Hkv, D = w.k_pages.shape[1], w.k_pages.shape[3]
     nbytes = float(np.sum(w.kv_len[:n_seq])) * 2 * Hkv * D * 2
+
     def run():
         for b in range(n_seq):
             O.flash_attention(w.q[b:b + 1], w.k_dense[b][None], w.v_dense[b][None], w.scale)
-    return run, nbytes, f"first {n_seq} sequences, all heads, dense f32 composite on de-paged K/V"
+    return run, nbytes, f"first {n_seq} sequence(s), all heads, dense f32 composite on de-paged K/V"
 
 
 def time_cpu(fn, steps, warmup):
@@ -134,54 +185,50 @@ def time_cpu(fn, steps, warmup):
 
 
 def reference_arm(args, rank):
-    """The reference's CPU implementation of the path (oracle port; the Rust sources cannot be built here)."""
+    """The reference's CPU implementation of the path (oracle port; the Rust sources cannot be built here), on all the
+    host cores this process may use.  Imports nothing of the product."""
     if rank != 0:
         return
-    from floneum_b200 import workloads as W
     from oracle import oracle as O
+    from oracle import workloads as W
     O.build()
-    if args.workload in ("cfg2", "cfg5"):
-        w = W.cfg2() if args.workload == "cfg2" else W.cfg5()
-        fn, work, desc = cpu_prefill_sample(w)
-        unit, scale_div = "TFLOP/s", 1e12
-        cfg = {"workload": f"{args.workload}: causal flash-attention prefill B{w.q.shape[0]} S{w.q.shape[2]} Hq{w.q.shape[1]} "
-                           f"Hkv{w.k.shape[1]} D128, bf16 in, f32 out", "flops_per_step": w.flops,
-               "note": "CPU arm: each step is the bounded sample named in cpu_baseline.sample"}
-    elif args.workload == "oproj":
-        B, Hq, S, D, N, rows = 4, 32, 4096, 128, 4096, 256
+    cores = O.use_all_cores()
+    name = args.workload
+    cfg = workload_config(name, args.gpus)
+    if name in ("cfg1", "cfg2", "cfg5"):
+        w = {"cfg1": W.cfg1, "cfg2": W.cfg2, "cfg5": W.cfg5}[name]()
+        fn, work, desc = cpu_full_prefill(w) if name == "cfg1" else cpu_prefill_sample(w)
+        unit, div, dtype = "TFLOP/s", 1e12, "f32"
+    elif name == "oproj":
+        Hq, D, N, rows = 32, 128, 4096, 256
         rng = np.random.default_rng(21)
         x = W.bf16_round(rng.standard_normal((1, Hq, rows, D)).astype(np.float32))
         wt = W.bf16_round((rng.standard_normal((N, Hq * D)) / 64).astype(np.float32))
         fn = lambda: O.out_proj(x, wt)
-        work, desc = 2.0 * rows * N * Hq * D, f"{rows} of the {B * S} rows, all {N} outputs (f32 transpose + matmul)"
-        unit, scale_div = "TFLOP/s", 1e12
-        cfg = {"workload": f"oproj: out = attn[B{B},Hq{Hq},S{S},D{D}] (read in place) x W[{N},{Hq * D}]^T, bf16 in, f32 out",
-               "flops_per_step": 2.0 * B * S * N * Hq * D, "note": "CPU arm: each step is the bounded sample named in cpu_baseline.sample"}
-    elif args.workload == "rope":
-        B, Hq, Hkv, S, D = 4, 32, 8, 4096, 128
+        work, desc = 2.0 * rows * N * Hq * D, f"{rows} of the 16384 rows, all {N} outputs (f32 transpose + matmul)"
+        unit, div, dtype = "TFLOP/s", 1e12, "f32"
+    elif name == "rope":
+        Hq, Hkv, S, D = 32, 8, 4096, 128
         rng = np.random.default_rng(22)
         x = rng.standard_normal((1, Hq + Hkv, S, D)).astype(np.float32)
         cos, sin = O.rope_tables(D, S, 10000.0)
         fn = lambda: O.rope(x, cos, sin, 0, False)
         work, desc = float(x.nbytes * 2), "one batch entry: all 40 heads rotated, f32 (read + write bytes counted)"
-        unit, scale_div = "GB/s", 1e9
-        cfg = {"workload": f"rope: fused RoPE + KV-cache append, B{B} Hq{Hq} Hkv{Hkv} S{S} D{D}, bf16 in, bf16 pages",
-               "note": "CPU arm: rotation only, on f32 copies; each step is the bounded sample named in cpu_baseline.sample"}
+        unit, div, dtype = "GB/s", 1e9, "f32"
     else:
-        w = W.cfg3() if args.workload == "cfg3" else W.cfg4()
+        w = W.cfg3(B=8) if name == "cfg3" else W.cfg4(Skv=16384)
         fn, work, desc = cpu_decode_sample(w)
-        unit, scale_div = "GB/s", 1e9
-        cfg = {"workload": f"{args.workload}: paged GQA decode B{w.q.shape[0]} Hq{w.q.shape[1]} Hkv{w.k_pages.shape[1]} D128, "
-                           f"16-token pages, kv tokens {int(np.sum(w.kv_len))}", "bytes_per_step": w.bytes,
-               "note": "CPU arm: each step is the bounded sample named in cpu_baseline.sample"}
-    sec = time_cpu(fn, args.steps, min(args.warmup, 1))
-    val = work / sec / scale_div
-    cores = O.num_threads()
+        if name == "cfg4":
+            desc = "the first 16384 of the 131072 keys, all heads, dense f32 composite"
+        unit, div, dtype = "GB/s", 1e9, "f32"
+    sec = time_cpu(fn, args.steps, args.warmup)
+    val = work / sec / div
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded N(0,1), bf16-rounded)", "config": cfg,
-        "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": dtype, "data": DATA, "config": cfg,
+        "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port",
+                         "sample": desc + "; each step of this arm is one such sample"},
         "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -200,41 +247,17 @@ def t4(ptr, shape, dtype, strides=None):
     return t
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "oproj", "rope"],
-                    help="cfg2-cfg5: the attention configurations; oproj / rope: the steps after and before attention "
-                    "(output projection GEMM, fused RoPE + cache append) at config 2's sizes")
-    ap.add_argument("--no-extras", action="store_true", help="skip the decode line and the CPU baseline")
-    ap.add_argument("--shard-of", type=int, default=0, help="for profiler captures on one GPU: run rank 0's shard of an "
-                    "N-rank job (no process group; the line is marked as a shard)")
-    ap.add_argument("--nccl-gather", action="store_true", help="cfg4 on several GPUs: exchange the split-KV records with an NCCL "
-                    "all-gather between two kernels instead of the library's own peer-memory push + merge")
-    ap.add_argument("--no-graph", action="store_true", help="decode workloads: time eager launches instead of a CUDA graph replay")
-    ap.add_argument("--quick", action="store_true", help="for profiler captures: no clock-settling loop, no e2e, no extras")
-    ap.add_argument("--small", action="store_true", help="for profiler captures: a scaled-down case of the workload "
-                    "(prefill B2 Hq16 Hkv4 S4096; decode B16)")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    fake_world = args.shard_of if (world == 1 and args.shard_of > 1) else 0
-    if args.impl == "reference":
-        reference_arm(args, rank)
-        return
-
+def gpu_arm(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
     import floneum_b200 as fb
-    from floneum_b200 import _lib, sharding, workloads as W
+    from floneum_b200 import _lib, sharding
     from floneum_b200.cache import lse_combine
+    from oracle import oracle as O  # checker + CPU baseline only
+    from oracle import workloads as W
     L = _lib.load()
     torch.cuda.set_device(local_rank)
+    fake_world = args.shard_of if (world == 1 and args.shard_of > 1) else 0
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
@@ -245,6 +268,7 @@ def main():
     dev = fb.Device.gpu(local_rank, stream.cuda_stream)
     peaks = load_peaks()
     cuda = torch.device(f"cuda:{local_rank}")
+    sampler = ClockSampler(local_rank)
 
     def barrier():
         if use_dist:
@@ -258,31 +282,65 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def all_ranks(x: float) -> list:
+        if not use_dist:
+            return [x]
+        t = torch.tensor([x], dtype=torch.float64, device=cuda)
+        out = torch.empty(world, dtype=torch.float64, device=cuda)
+        dist.all_gather_into_tensor(out, t)
+        return [float(v) for v in out.cpu()]
+
     def bf16_dev(a):  # numpy f32 (bf16-representable) -> torch bf16 on the GPU
         return torch.from_numpy(np.ascontiguousarray(a)).to(cuda).to(torch.bfloat16)
 
     def bf16_pinned(a):
         return torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).pin_memory()
 
-    result = {}
-    sampler = ClockSampler(local_rank)
+    def settle_clocks(step, seconds=0.5):
+        """Untimed steps until the GPU has been under load for `seconds` (the clocks settle under the power cap)."""
+        if args.quick:
+            return
+        t_end = time.time() + seconds
+        i = 0
+        while time.time() < t_end:
+            for _ in range(16):
+                step(i)
+                i += 1
+            torch.cuda.synchronize()
 
-    # ======================================================================= prefill (cfg2 / cfg5)
-    def run_prefill(w, tag):
+    def timed(step, steps):
+        """K steps back to back on the stream between two barriers; returns (total ms max over ranks, this rank's total ms,
+        per-step ms of this rank)."""
+        barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record(stream)
+        for i in range(steps):
+            step(i)
+            ev[i + 1].record(stream)
+        barrier()
+        mine = ev[0].elapsed_time(ev[-1])
+        return max_over_ranks(mine), mine, [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+
+    # ======================================================================= prefill (cfg1 / cfg2 / cfg5)
+    def run_prefill(w, name, tag=""):
         B, Hq, S, D = w.q.shape
         Hkv = w.k.shape[1]
+        f32_in = not w.bf16
         q0, q1 = sharding.q_head_range(Hq, Hkv, rank, world)
         k0, k1 = sharding.kv_head_range(Hkv, rank, world)
         q, k, v = w.q[:, q0:q1], w.k[:, k0:k1], w.v[:, k0:k1]
-        in_bytes = (q.size + k.size + v.size) * 2
-        copies = max(1, int(np.ceil(256e6 / in_bytes)))  # rotate inputs so that the working set exceeds L2
+        esz = 4 if f32_in else 2
+        in_bytes = (q.size + k.size + v.size) * esz
+        copies = max(1, min(64, int(np.ceil(256e6 / in_bytes))))  # rotate inputs so that the working set exceeds L2
+        to_dev = (lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)) if f32_in else bf16_dev
+        dt = _lib.F32 if f32_in else _lib.BF16
         dq, dk, dv = [], [], []
         for _ in range(copies):
-            dq.append(bf16_dev(q)); dk.append(bf16_dev(k)); dv.append(bf16_dev(v))
+            dq.append(to_dev(q)); dk.append(to_dev(k)); dv.append(to_dev(v))
         out = torch.empty(q.shape, dtype=torch.float32, device=cuda)
-        cq = [t4(t.data_ptr(), t.shape, _lib.BF16) for t in dq]
-        ck = [t4(t.data_ptr(), t.shape, _lib.BF16) for t in dk]
-        cv = [t4(t.data_ptr(), t.shape, _lib.BF16) for t in dv]
+        cq = [t4(t.data_ptr(), t.shape, dt) for t in dq]
+        ck = [t4(t.data_ptr(), t.shape, dt) for t in dk]
+        cv = [t4(t.data_ptr(), t.shape, dt) for t in dv]
         co = t4(out.data_ptr(), out.shape, _lib.F32)
 
         def step(i):
@@ -296,37 +354,25 @@ def main():
             for i in range(args.warmup):
                 step(i)
             torch.cuda.synchronize()
-            # keep the GPU busy with untimed steps until the clocks have been under load for 0.5 s
-            i = args.warmup
-            while not args.quick and time.time() - t_busy0 < 0.5:
-                for _ in range(20):
-                    step(i)
-                    i += 1
-                torch.cuda.synchronize()
-            barrier()
+            settle_clocks(step)
             launches0 = dev.launch_count()
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-            ev[0].record(stream)
-            for i in range(args.steps):
-                step(i)
-                ev[i + 1].record(stream)
-            barrier()
+            total_ms, _, per_launch_ms = timed(step, args.steps)
             clocks = sampler.stop(t_busy0, time.time())
             launches = dev.launch_count() - launches0
             dev.synchronize()
-        total_ms = max_over_ranks(ev[0].elapsed_time(ev[-1]))
-        per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
         flops_rank = 4.0 * B * (q1 - q0) * D * S * (S + 1) / 2
         flops_all = w.flops
         value = flops_all * args.steps / (total_ms * 1e-3) / 1e12
         achieved = flops_rank / (statistics.mean(per_launch_ms) * 1e-3) / 1e12
-        # parity spot check of the timed configuration (last output, sampled rows)
         got = out.cpu().numpy()
 
         # ---- e2e: host buffers through the C ABI, copies inside the timed region
-        hq, hk, hv = bf16_pinned(q), bf16_pinned(k), bf16_pinned(v)
+        if f32_in:
+            hq, hk, hv = (torch.from_numpy(np.ascontiguousarray(a)).pin_memory() for a in (q, k, v))
+        else:
+            hq, hk, hv = bf16_pinned(q), bf16_pinned(k), bf16_pinned(v)
         hout = torch.empty(q.shape, dtype=torch.float32).pin_memory()
-        eq, ek, evv = (t4(t.data_ptr(), t.shape, _lib.BF16) for t in (hq, hk, hv))
+        eq, ek, evv = (t4(t.data_ptr(), t.shape, dt) for t in (hq, hk, hv))
         eo = t4(hout.data_ptr(), hout.shape, _lib.F32)
 
         def e2e_step():
@@ -344,179 +390,234 @@ def main():
             e2e_s = max_over_ranks(time.perf_counter() - t0)
         e2e_val = flops_all * e2e_steps / e2e_s / 1e12
         e2e_ok = bool(np.array_equal(hout.numpy(), got))
-        # K launches back to back after a 0.5 s busy loop run under the power cap: the sustained cuBLAS figure is the
-        # denominator; the fraction of the burst figure is given beside it.
-        peak = peaks["tensor_sustained"]
+        if f32_in:
+            # the general kernel runs f32 FMAs on the CUDA cores: 2 x 128 lanes x 148 SMs x clock, against which it is
+            # latency- and shared-memory-bound; the fraction says how far a CUDA-core kernel is from that bound
+            peak = 2 * 128 * 148 * 1.965e9 / 1e12
+            roof = {"bound": "fp32 CUDA cores (no tensor-core path for f32 tensors)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak, "traffic": None, "peak_source": "nominal: 2 flop x 128 lanes x 148 SMs x 1.965 GHz"}
+        else:
+            # K launches back to back after a 0.5 s busy loop run under the power cap: the sustained cuBLAS figure is the
+            # denominator; the fraction of the burst figure is given beside it.
+            peak = peaks["tensor_sustained"]
+            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    # no figure: a profiler capture of this kernel ends with most of its f32 output still in L2, so its
+                    # DRAM byte count says nothing about re-reads
+                    "traffic": None,
+                    "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
+                    "frac_of_burst_peak": achieved / peaks["tensor_burst"], "burst_peak": peaks["tensor_burst"],
+                    "frac_of_nominal_2250": achieved / 2250.0,
+                    "note": "achieved counts the V pre-pass kernel's time as well (both kernels of a step)"}
+        cfg = workload_config(name, world)
+        if tag:
+            cfg = dict(cfg, workload=cfg["workload"] + tag, flops_per_step=flops_all)
         return {
             "value": value, "unit": "TFLOP/s", "ms_per_step": total_ms / args.steps, "gpu_launches": launches,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         # dram read+write of one launch, scaled by (batch, head) pairs from the ncu capture of the
-                         # B2 Hq16 case (68.2 MB for 32 pairs)
-                         "traffic": 68.2e6 * (B * (q1 - q0)) / 32.0 if D == 128 and S == 4096 else None,
-                         "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
-                         "frac_of_burst_peak": achieved / peaks["tensor_burst"], "burst_peak": peaks["tensor_burst"],
-                         "frac_of_nominal_2250": achieved / 2250.0,
-                         "note": "achieved counts the V pre-pass kernel's time as well (both kernels of a step)"},
+            "roofline": roof,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": int(in_bytes * world),
                     "d2h_bytes_per_step": int(out.numel() * 4 * world), "matches_device_path": e2e_ok},
-            "clocks": clocks,
-            "config": {"workload": f"{tag}: causal flash-attention prefill B{B} S{S} Hq{Hq} Hkv{Hkv} D{D}, bf16 in, f32 out",
-                       "sharding": f"kv heads split over {world} rank(s)", "l2": f"inputs rotate over {copies} copies "
-                       f"({in_bytes * copies / 1e6:.0f} MB) so each launch reads HBM-cold data", "flops_per_step": flops_all},
+            "clocks": clocks, "config": cfg, "input_copies": copies,
             "_got": got, "_slice": (q, k, v),
         }
 
     # ======================================================================= decode (cfg3 / cfg4)
-    def run_decode(w, tag, shard_heads=True, chunked=False):
+    def run_decode(w, name, chunked, tag="", with_variants=True):
+        """cfg3: `w` is the whole workload, this rank takes its kv heads.  cfg4: `w` is this rank's chunk of the keys."""
         B, Hq, _, D = w.q.shape
         Hkv_all = w.k_pages.shape[1]
-        if shard_heads:
+        if not chunked:
             k0, k1 = sharding.kv_head_range(Hkv_all, rank, world)
             q0, q1 = sharding.q_head_range(Hq, Hkv_all, rank, world)
         else:
             k0, k1, q0, q1 = 0, Hkv_all, 0, Hq
         kp, vp = np.ascontiguousarray(w.k_pages[:, k0:k1]), np.ascontiguousarray(w.v_pages[:, k0:k1])
         qn = np.ascontiguousarray(w.q[:, q0:q1])
-        cache = fb.PagedKvCache(dev, B, k1 - k0, D, kp.shape[0], w.page_table.shape[1])
-        cache.write_pages(0, kp, vp)
-        cache.set_page_table(w.page_table, w.kv_len)
+        kv_bytes_rank = float(np.sum(w.kv_len)) * 2 * (k1 - k0) * D * 2
+        copies = max(1, min(8, int(math.ceil(512e6 / kv_bytes_rank))))  # rotate so that the working set is several x L2
+        caches = []
+        for _ in range(copies):
+            c = fb.PagedKvCache(dev, B, k1 - k0, D, kp.shape[0], w.page_table.shape[1])
+            c.write_pages(0, kp, vp)
+            c.set_page_table(w.page_table, w.kv_len)
+            if args.decode_ctas:
+                c.set_decode_ctas(args.decode_ctas)
+            caches.append(c)
         dq = bf16_dev(qn)
         out = torch.empty(qn.shape, dtype=torch.float32, device=cuda)
         tq, to = fb.Tensor.from_torch(dev, dq), fb.Tensor.from_torch(dev, out)
-        kv_bytes_rank = float(np.sum(w.kv_len)) * 2 * (k1 - k0) * D * 2
-        flush = torch.empty(int(300e6), dtype=torch.uint8, device=cuda) if kv_bytes_rank < 400e6 else None
-
-        if chunked and use_dist:
-            # fixed buffers so that the step can be captured in a CUDA graph
-            part = torch.empty((B, q1 - q0, D + 2), dtype=torch.float32, device=cuda)
-            gathered = torch.empty((world, B, q1 - q0, D + 2), dtype=torch.float32, device=cuda)
-            out3 = torch.empty((B, q1 - q0, D), dtype=torch.float32, device=cuda)
+        collective = chunked and use_dist
+        exchange = None
+        if collective:
+            part = torch.empty((B, Hq, D + 2), dtype=torch.float32, device=cuda)
+            gathered = torch.empty((world, B, Hq, D + 2), dtype=torch.float32, device=cuda)
+            out3 = torch.empty((B, Hq, D), dtype=torch.float32, device=cuda)
             tpart, tgath, tout3 = (fb.Tensor.from_torch(dev, t) for t in (part, gathered, out3))
-            exchange = None if args.nccl_gather else sharding.PeerExchange(dev, rank, world, B * (q1 - q0) * (D + 2))
+            exchange = sharding.PeerExchange(dev, rank, world, B * Hq * (D + 2))
 
-        def step():
-            if chunked and use_dist:
-                cache.decode_partial(tq, w.scale, tpart)
-                if exchange is not None:
-                    exchange.lse_combine(tpart, tout3)  # peer stores + epoch flags + merge, inside the library's kernels
-                else:
-                    dist.all_gather_into_tensor(gathered, part)
-                    lse_combine(dev, tgath, tout3)
-                return out3
-            cache.decode(tq, w.scale, to)
-            return out
-        with torch.cuda.stream(stream):
-            for _ in range(args.warmup):
-                if flush is not None:
-                    flush.zero_()
-                res = step()
-            barrier()
-            # A decode step is launch-bound at small shard sizes: capture it once in a CUDA graph and replay it.
-            graph = None
-            if not args.no_graph and not args.quick:
-                try:
-                    graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph, stream=stream):
-                        res = step()
-                    graph.replay()
-                    torch.cuda.synchronize()
-                except Exception as e:  # capture is an optimisation only
-                    sys.stderr.write(f"CUDA graph capture failed ({e}); timing eager launches\n")
-                    graph = None
-                    torch.cuda.synchronize()
-            barrier()
-            launches0 = dev.launch_count()
-            evs = []
-            for _ in range(args.steps):
-                if flush is not None:
-                    flush.zero_()  # write a buffer larger than L2 between timed launches
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream)
-                if graph is not None:
-                    graph.replay()
-                else:
-                    res = step()
-                b.record(stream)
-                evs.append((a, b))
-            barrier()
-            launches = dev.launch_count() - launches0
-            if graph is not None:
-                # kernels of ours inside each replay: split-KV + combine (+ push + merge, or + merge after the NCCL gather)
-                launches = args.steps * ((4 if exchange is not None else 3) if (chunked and use_dist) else 2)
-            dev.synchronize()
-        ms = [a.elapsed_time(b) for a, b in evs]
-        mean_ms = max_over_ranks(statistics.mean(ms))
-        # e2e: the host-buffer entry point (q up, result down; the KV cache is the library's device-resident object)
-        e2e = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
-        if not (chunked and use_dist) and not args.quick:
-            # pinned host buffers through the C ABI: q up, result down, one synchronous call per step
-            qh = torch.from_numpy(np.ascontiguousarray(qn, dtype=np.float32)).pin_memory()
-            host_out = torch.empty(qh.shape, dtype=torch.float32).pin_memory()
-            hq4, ho4 = t4(qh.data_ptr(), qh.shape, _lib.F32), t4(host_out.data_ptr(), host_out.shape, _lib.F32)
+        def step_main(i):
+            c = caches[i % copies]
+            if collective:
+                exchange.decode(c, tq, w.scale, tout3)  # split-KV kernel pushing its records to every rank, then the merge
+            else:
+                c.decode(tq, w.scale, to)
 
-            def e2e_step():
-                _lib.check(L.fusor_cuda_flash_attention_decode_host(dev.handle, cache._h, ctypes.byref(hq4), ctypes.c_float(w.scale),
-                                                                    ctypes.byref(ho4)), dev.handle)
-            for _ in range(2):
-                e2e_step()
-            barrier()
-            t0 = time.perf_counter()
-            n_e2e = max(3, min(args.steps, 20))
-            for _ in range(n_e2e):
-                e2e_step()
-            e2e_s = max_over_ranks(time.perf_counter() - t0)
-            e2e = {"unit": "GB/s", "h2d_bytes_per_step": int(qh.numel() * 4 * world), "d2h_bytes_per_step": int(host_out.numel() * 4 * world),
-                   "matches_device_path": bool(np.array_equal(host_out.numpy().reshape(-1), (res if isinstance(res, torch.Tensor) else out).float().cpu().numpy().reshape(-1)))}
+        def step_local(i):  # this rank's chunk alone, no exchange
+            caches[i % copies].decode_partial(tq, w.scale, tpart)
+
+        def step_nccl(i):  # the same step with a library all-gather between the partial and the merge kernels
+            caches[i % copies].decode_partial(tq, w.scale, tpart)
+            dist.all_gather_into_tensor(gathered, part)
+            lse_combine(dev, tgath, tout3)
+
+        def measure(step, kernels_per_step):
+            """Warm-up, one CUDA graph per cache copy (a decode step is launch-bound at small shard sizes), K timed steps."""
+            with torch.cuda.stream(stream):
+                for i in range(max(args.warmup, copies)):
+                    step(i)
+                barrier()
+                graphs = None
+                if not args.no_graph and not args.quick:
+                    try:
+                        graphs = []
+                        for j in range(copies):
+                            g = torch.cuda.CUDAGraph()
+                            with torch.cuda.graph(g, stream=stream):
+                                step(j)
+                            graphs.append(g)
+                        for g in graphs:
+                            g.replay()
+                        torch.cuda.synchronize()
+                    except Exception as e:  # capture is an optimisation only
+                        sys.stderr.write(f"CUDA graph capture failed ({e}); timing eager launches\n")
+                        graphs = None
+                        torch.cuda.synchronize()
+                run = (lambda i: graphs[i % copies].replay()) if graphs is not None else step
+                settle_clocks(run, 0.3)
+                launches0 = dev.launch_count()
+                total_ms, mine_ms, per_step = timed(run, args.steps)
+                launches = dev.launch_count() - launches0 if graphs is None else args.steps * kernels_per_step
+                dev.synchronize()
+            return total_ms / args.steps, mine_ms / args.steps, per_step, launches, graphs is not None
+
+        sampler.start()
+        t_busy0 = time.time()
+        ms, ms_mine, per_step, launches, graphed = measure(step_main, 2 if collective else 1)
+        clocks = sampler.stop(t_busy0, time.time())
+        res = (out3 if collective else out).float().cpu().numpy().copy()
         bytes_rank = kv_bytes_rank + B * (q1 - q0) * D * 6 + 4 * float(np.sum((w.kv_len + 15) // 16))
         bytes_all = bytes_rank * world
-        achieved = bytes_rank / (statistics.mean(ms) * 1e-3) / 1e9
-        if "value" not in e2e:
-            e2e["value"] = bytes_all * n_e2e / e2e_s / 1e9
-        return {"value": bytes_all / (mean_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": mean_ms, "gpu_launches": launches, "e2e": e2e,
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                             "frac": achieved / peaks["hbm"],
-                             # ncu capture of the B16 case: dram read+write = 1.02 x the algorithmic bytes, scaled by bytes
-                             "traffic": bytes_rank * 1.02, "peak_source": f"{peaks['source']} (device copy)",
-                             "frac_of_nominal_8000": achieved / 8000.0},
-                "config": {"workload": f"{tag}: paged GQA decode B{B} Hq{Hq} Hkv{Hkv_all} D{D}, 16-token pages, "
-                           f"kv tokens {int(np.sum(w.kv_len))}", "bytes_per_step": bytes_all,
-                           "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
-                           "l2": "KV working set exceeds L2" if flush is None else "300 MB buffer written between timed launches"},
-                "_got": (res if isinstance(res, torch.Tensor) else out).cpu().numpy(), "_q": qn, "_krange": (k0, k1)}
+        achieved = bytes_rank / (ms_mine * 1e-3) / 1e9
+        r = {"value": bytes_all / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "gpu_launches": launches,
+             "rank_ms_per_step": all_ranks(ms_mine),
+             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s", "frac": achieved / peaks["hbm"],
+                          # profiler capture of a scaled-down case: dram read + write = 1.02 x the algorithmic bytes
+                          "traffic": bytes_rank * 1.02, "peak_source": f"{peaks['source']} (device copy)",
+                          "frac_of_nominal_8000": achieved / 8000.0},
+             "config": workload_config(name, world), "bytes_per_step": bytes_all, "kv_copies": copies,
+             "launch": "CUDA graph replay, one step per graph" if graphed else "eager launches", "clocks": clocks,
+             "_got": res, "_q": qn, "_krange": (k0, k1)}
+        if tag:
+            r["config"]["workload"] += tag
+        if collective and with_variants:
+            loc_ms, _, _, _, _ = measure(step_local, 1)
+            r["collective"] = {"local_chunk_only_ms": loc_ms, "step_ms": ms, "share_of_step": max(0.0, 1.0 - loc_ms / ms),
+                               "what": "step = split-KV kernel (records pushed to every rank by its last CTAs) + merge kernel that "
+                                       "waits for all ranks; local_chunk_only = the same split-KV kernel writing its records locally"}
+            n_ms, _, _, _, _ = measure(step_nccl, 3)
+            r["nccl_gather"] = {"value": bytes_all / (n_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": n_ms,
+                                "what": "decode_partial + NCCL all_gather_into_tensor + lse_combine (three launches)"}
+        # e2e: host q up, result down, through the C ABI
+        if not args.quick:
+            qh = torch.from_numpy(np.ascontiguousarray(qn, dtype=np.float32)).pin_memory()
+            host_out = torch.empty(qn.shape if not collective else (B, Hq, D), dtype=torch.float32).pin_memory()
+            if not collective:
+                hq4, ho4 = t4(qh.data_ptr(), qh.shape, _lib.F32), t4(host_out.data_ptr(), host_out.shape, _lib.F32)
+
+                def e2e_step():
+                    _lib.check(L.fusor_cuda_flash_attention_decode_host(dev.handle, caches[0]._h, ctypes.byref(hq4), ctypes.c_float(w.scale),
+                                                                        ctypes.byref(ho4)), dev.handle)
+            else:
+                dq32 = torch.empty(qn.shape, dtype=torch.float32, device=cuda)
+                tq32 = fb.Tensor.from_torch(dev, dq32)
+
+                def e2e_step():
+                    _lib.check(L.fusor_cuda_buffer_upload(dev.handle, dq32.data_ptr(), qh.data_ptr(), qh.numel() * 4), dev.handle)
+                    exchange.decode(caches[0], tq32, w.scale, tout3)
+                    _lib.check(L.fusor_cuda_buffer_download(dev.handle, host_out.data_ptr(), out3.data_ptr(), out3.numel() * 4), dev.handle)
+            with torch.cuda.stream(stream):
+                for _ in range(2):
+                    e2e_step()
+                barrier()
+                t0 = time.perf_counter()
+                n_e2e = max(3, min(args.steps, 20))
+                for _ in range(n_e2e):
+                    e2e_step()
+                torch.cuda.synchronize()
+                e2e_s = max_over_ranks(time.perf_counter() - t0)
+            r["e2e"] = {"value": bytes_all * n_e2e / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(qh.numel() * 4 * world),
+                        "d2h_bytes_per_step": int(host_out.numel() * 4 * world),
+                        "matches_device_path": bool(np.array_equal(host_out.numpy().reshape(-1), res.reshape(-1)))}
+        else:
+            r["e2e"] = None
+        if exchange is not None:
+            exchange.close()  # collective: unmap, barrier, free
+        for c in caches:
+            c.close()
+        return r
+
+    def decode_parity(r, w, name, w_full=None):
+        got = r.pop("_got"); qn = r.pop("_q"); k0, k1 = r.pop("_krange")
+        par = {"finite": bool(np.isfinite(got).all())}
+        if rank == 0 and not args.quick:
+            if name == "cfg3":
+                nb = min(8, qn.shape[0])
+                want = np.stack([O.flash_attention(qn[b:b + 1], w.k_dense[b][None, k0:k1], w.v_dense[b][None, k0:k1], w.scale)[0]
+                                 for b in range(nb)])
+                err = np.abs(got[:nb] - want)
+                par["sequences_checked"] = nb
+            else:
+                wf = w_full if w_full is not None else w  # the whole sequence, whatever the number of chunks
+                want = O.flash_attention(wf.q, wf.k_dense[0][None], wf.v_dense[0][None], wf.scale)
+                err = np.abs(got.reshape(want.shape) - want)
+                par["against"] = "the oracle on the unsplit sequence"
+            par.update(max_abs=float(err.max()), mean_abs=float(err.mean()), tolerance="max 2e-3, mean 2e-4")
+        r["parity"] = par
+        return r
+
+    def load_cfg3():
+        return W.cfg3(B=16) if args.small else W.cfg3()
+
+    def load_cfg4():
+        """(this rank's chunk, the whole sequence on rank 0 for the parity check)"""
+        skv = 16384 if args.small else 131072
+        full = W.cfg4(Skv=skv) if (rank == 0 or world == 1 or fake_world) else None
+        mine = full if (world == 1 and not fake_world) else W.cfg4(Skv=skv, rank=rank, world=world, keep_dense=False)
+        return mine, full
 
     # ======================================================================= the neighbours of the path
-    def time_steps(step, n_copies_note):
+    def time_steps(step):
         for _ in range(args.warmup):
             step(0)
         barrier()
-        if not args.quick:  # let the clocks settle under load, as the attention legs do
-            t_end = time.time() + 0.5
-            i = 0
-            while time.time() < t_end:
-                step(i); i += 1
-                if i % 16 == 0:
-                    torch.cuda.synchronize()
-        barrier()
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        settle_clocks(step)
         sampler.start()
         t0 = time.time()
         with torch.cuda.stream(stream):
-            for i, (a, b) in enumerate(evs):
-                a.record(stream)
-                step(i)
-                b.record(stream)
-        barrier()
-        t1 = time.time()
-        clocks = sampler.stop(t0, t1)
-        ms = max_over_ranks(float(np.mean([a.elapsed_time(b) for a, b in evs])))
-        return ms, clocks
+            total_ms, _, _ = timed(step, args.steps)
+        clocks = sampler.stop(t0, time.time())
+        return total_ms / args.steps, clocks
 
     def run_oproj():
         B, Hq_all, S, D, N = (2, 16, 2048, 128, 2048) if args.small else (4, 32, 4096, 128, 4096)
         Hq = Hq_all // world
         rng = np.random.default_rng(21)
         n_copies = 2
-        attn = [torch.randn((B, Hq, S, D), device=cuda, dtype=torch.bfloat16, generator=None) for _ in range(n_copies)]
+        gen = torch.Generator(device=cuda)
+        gen.manual_seed(21)  # the same attention tensor on every rank: each rank takes its heads of it
+        attn_all = [torch.randn((B, Hq_all, S, D), device=cuda, dtype=torch.float32, generator=gen).to(torch.bfloat16) for _ in range(n_copies)]
+        attn = [a[:, rank * Hq:(rank + 1) * Hq].contiguous() for a in attn_all]
+        full0 = attn_all[0].float().cpu().numpy() if rank == 0 else None
+        del attn_all
         w_all = W.bf16_round((rng.standard_normal((N, Hq_all * D)) / np.sqrt(Hq_all * D)).astype(np.float32))
         c0, c1 = (rank * Hq * D, (rank + 1) * Hq * D)
         w_dev = bf16_dev(w_all[:, c0:c1])
@@ -524,39 +625,52 @@ def main():
         ta = [fb.Tensor.from_torch(dev, a) for a in attn]
         tw = fb.Tensor.from_torch(dev, w_dev)
         to = fb.Tensor.from_torch(dev, out)
-        flush = torch.empty(300 << 20, dtype=torch.uint8, device=cuda)
+        comm = sharding.Communicator(dev, rank, world) if use_dist else None
 
         def step(i):
-            ta[i % n_copies].out_proj(tw, None, out=to)
-            if use_dist:
-                dist.all_reduce(out)
+            if comm is not None:
+                comm.out_proj(ta[i % n_copies], tw, None, to)  # GEMM + all-reduce, one library call
+            else:
+                ta[i % n_copies].out_proj(tw, None, out=to)
         with torch.cuda.stream(stream):
             l0 = dev.launch_count()
-            ms, clocks = time_steps(step, n_copies)
+            ms, clocks = time_steps(step)
             launches = dev.launch_count() - l0
+            gemm_ms = None
+            if comm is not None:
+                gemm_ms, _ = time_steps(lambda i: ta[i % n_copies].out_proj(tw, None, out=to))
             step(0)
         stream.synchronize()
         got = out.cpu().numpy()
         flops = 2.0 * B * S * N * Hq_all * D
-        achieved = flops / world / (ms * 1e-3) / 1e12
-        # parity on sampled rows: rank 0 rebuilds the full-K rows only on one GPU (N > 1: the shards' random inputs differ)
+        achieved = flops / world / ((gemm_ms or ms) * 1e-3) / 1e12
         par = {"finite": bool(np.isfinite(got).all())}
-        if world == 1:
+        if rank == 0:
             rows = np.random.default_rng(1).integers(0, B * S, 64)
-            a0 = attn[0].float().cpu().numpy()
-            x = np.stack([a0[r // S, :, r % S, :].reshape(-1) for r in rows])
-            want = O.out_proj(x.reshape(len(rows), Hq, 1, D), w_all)[:, 0]  # each sampled row as a batch of one token
+            x = np.stack([full0[r // S, :, r % S, :].reshape(-1) for r in rows])
+            want = O.out_proj(x.reshape(len(rows), Hq_all, 1, D), w_all)[:, 0]  # each sampled row as a batch of one token
             err = np.abs(got.reshape(B * S, N)[rows] - want)
-            par.update(max_abs=float(err.max()), mean_abs=float(err.mean()), rows_checked=int(len(rows)), tolerance="max 2e-4")
-        return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "gpu_launches": launches,
-                "clocks": clocks, "parity": par, "e2e": None,
-                "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"], "unit": "TFLOP/s",
-                             "frac": achieved / peaks["tensor_sustained"], "traffic": None,
-                             "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
-                             "frac_of_burst_peak": achieved / peaks["tensor_burst"]},
-                "config": {"workload": f"oproj: out = attn[B{B},Hq{Hq_all},S{S},D{D}] (read in place) x W[{N},{Hq_all * D}]^T, bf16 in, f32 out",
-                           "sharding": f"query heads split over {world} rank(s)" + (", partial sums all-reduced over NCCL" if use_dist else ""),
-                           "l2": f"attention input rotates over {n_copies} copies", "flops_per_step": flops}}
+            par.update(max_abs=float(err.max()), mean_abs=float(err.mean()), rows_checked=int(len(rows)),
+                       tolerance="max 2e-4" if world == 1 else "max 4e-4 (the sum over ranks adds one f32 rounding per rank)")
+        if comm is not None:
+            comm.close()
+        cfg = workload_config("oproj", world)
+        if args.small:
+            cfg = dict(cfg, workload=cfg["workload"] + " (scaled down: B2 Hq16 S2048 N2048)", flops_per_step=flops)
+        r = {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "gpu_launches": launches,
+             "clocks": clocks, "parity": par, "e2e": None,
+             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"], "unit": "TFLOP/s",
+                          "frac": achieved / peaks["tensor_sustained"], "traffic": None,
+                          "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained loop under the power cap)",
+                          "frac_of_burst_peak": achieved / peaks["tensor_burst"],
+                          "note": "the GEMM kernel alone; the step's value includes the all-reduce" if comm is not None else None},
+             "config": cfg}
+        if gemm_ms is not None:
+            out_bytes = out.numel() * 4
+            r["collective"] = {"gemm_only_ms": gemm_ms, "step_ms": ms, "share_of_step": max(0.0, 1.0 - gemm_ms / ms),
+                               "all_reduce_bytes_per_rank": out_bytes,
+                               "what": "NCCL all-reduce of the f32 partial sums behind fusor_cuda_attention_out_proj_all_reduce"}
+        return r
 
     def run_rope():
         B, Hq_all, Hkv_all, S, D = (2, 16, 4, 4096, 128) if args.small else (4, 32, 8, 4096, 128)
@@ -610,77 +724,75 @@ def main():
         par = {"q_bit_exact": bool(np.array_equal(got_q.view(np.uint32), want_q.view(np.uint32))),
                "k_bit_exact": bool(np.array_equal(gk.as_slice()[0, 0].view(np.uint32), want_k[0, 0].view(np.uint32)))}
         achieved = nbytes_rank / (ms * 1e-3) / 1e9
+        cfg = dict(workload_config("rope", world), bytes_per_step=nbytes_rank * world)
+        if args.small:
+            cfg["workload"] += " (scaled down: B2 Hq16 Hkv4)"
         return {"value": nbytes_rank * world / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "gpu_launches": args.steps,
                 "clocks": clocks, "parity": par, "e2e": None,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s", "frac": achieved / peaks["hbm"],
                              "traffic": None, "peak_source": f"{peaks['source']} (device copy)"},
-                "config": {"workload": f"rope: fused RoPE + KV-cache append, B{B} Hq{Hq_all} Hkv{Hkv_all} S{S} D{D}, bf16 in, bf16 pages",
-                           "sharding": f"heads split over {world} rank(s), no collective", "bytes_per_step": nbytes_rank * world,
-                           "l2": "300 MB buffer written between timed launches; table uploads are inside the timed region"}}
+                "config": cfg}
 
     # ----------------------------------------------------------------------- run the selected workload
-    from oracle import oracle as O  # checker + CPU baseline only
     extras = {}
-    if args.workload in ("oproj", "rope"):
-        r = run_oproj() if args.workload == "oproj" else run_rope()
+    name = args.workload
+    if name in ("oproj", "rope"):
+        r = run_oproj() if name == "oproj" else run_rope()
         dtype = "bf16"
-    elif args.workload in ("cfg2", "cfg5"):
-        if args.small:
-            w = W.cfg2(B=2, Hq=16, Hkv=4) if args.workload == "cfg2" else W.cfg5(S=8192, Hq=8, Hkv=2)
+    elif name in ("cfg1", "cfg2", "cfg5"):
+        tag = ""
+        if args.small and name != "cfg1":
+            w = W.cfg2(B=2, Hq=16, Hkv=4) if name == "cfg2" else W.cfg5(S=8192, Hq=8, Hkv=2)
+            tag = " (scaled down: B2 Hq16 Hkv4)" if name == "cfg2" else " (scaled down: S8192 Hq8 Hkv2)"
         else:
-            w = W.cfg2() if args.workload == "cfg2" else W.cfg5()
-        r = run_prefill(w, args.workload + (" (scaled down)" if args.small else ""))
+            w = {"cfg1": W.cfg1, "cfg2": W.cfg2, "cfg5": W.cfg5}[name]()
+        r = run_prefill(w, name, tag)
         q, k, v = r.pop("_slice")
         got = r.pop("_got")
-        rows = np.unique(np.random.default_rng(0).integers(0, q.shape[0] * q.shape[1] * q.shape[2], 400))
-        want = O.flash_attention(q, k, v, w.scale, mask_kind=O.MASK_CAUSAL, rows=rows, skip_masked=True)
-        err = np.abs(got.reshape(-1, q.shape[3])[rows] - want)
-        r["parity"] = {"max_abs": float(err.max()), "mean_abs": float(err.mean()), "rows_checked": int(rows.size),
-                       "tolerance": "max 2e-3, mean 2e-4"}
-        dtype = "bf16"
-        if rank == 0 and world == 1 and not args.no_extras and not args.quick:
-            fn, flops, desc = cpu_prefill_sample(w)
-            sec = time_cpu(fn, 3, 1)
-            r["cpu_baseline"] = {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
-                                 "sample": desc, "seconds_per_sample": sec}
-            if args.workload == "cfg2":
-                wd = W.cfg3()
-                d = run_decode(wd, "cfg3")
-                gotd = d.pop("_got"); d.pop("_q"); d.pop("_krange")
-                wantd = np.stack([O.flash_attention(wd.q[b:b + 1], wd.k_dense[b][None], wd.v_dense[b][None], wd.scale)[0] for b in range(8)])
-                errd = np.abs(gotd[:8] - wantd)
-                d["parity"] = {"max_abs": float(errd.max()), "mean_abs": float(errd.mean()), "sequences_checked": 8}
-                extras["decode"] = d
-    else:
-        if args.workload == "cfg3":
-            w = W.cfg3(B=16) if args.small else W.cfg3()
-            r = run_decode(w, "cfg3" + (" (scaled down)" if args.small else ""))
+        if name == "cfg1":
+            want = O.flash_attention(q, k, v, w.scale, mask_kind=O.MASK_CAUSAL)
+            err = np.abs(got - want)
+            r["parity"] = {"max_abs": float(err.max()), "mean_abs": float(err.mean()), "rows_checked": int(q.shape[1] * q.shape[2]),
+                           "tolerance": "max 2e-5, mean 2e-6 (f32 tensors, f32 arithmetic)"}
         else:
-            w = W.cfg4(rank=rank, world=world)
-            r = run_decode(w, "cfg4", shard_heads=False, chunked=True)
-            if world > 1:
-                r["config"]["sharding"] = (f"KV sequence split into {world} contiguous chunks, " +
-                                           ("partials all-gathered over NCCL" if args.nccl_gather else
-                                            "partial records pushed to every rank over peer memory and merged (no collective call)"))
-                r["value"] = r["value"]  # bytes_all already counts every rank's chunk
-        got = r.pop("_got"); qn = r.pop("_q"); k0, k1 = r.pop("_krange")
-        r["parity"] = {"finite": bool(np.isfinite(got).all())}
-        if rank == 0 and not args.quick:
-            if args.workload == "cfg3":
-                nb = min(8, qn.shape[0])
-                want = np.stack([O.flash_attention(qn[b:b + 1], w.k_dense[b][None, k0:k1], w.v_dense[b][None, k0:k1], w.scale)[0]
-                                 for b in range(nb)])
-                err = np.abs(got[:nb] - want)
-            else:
-                wf = w if (world == 1 or fake_world) else W.cfg4()  # rank 0 rebuilds the whole sequence for the check
-                want = O.flash_attention(wf.q, wf.k_dense[0][None], wf.v_dense[0][None], wf.scale)
-                err = np.abs(got.reshape(want.shape) - want)
-            r["parity"].update(max_abs=float(err.max()), mean_abs=float(err.mean()), tolerance="max 2e-3, mean 2e-4")
-            if world == 1:
-                fn, nbytes, desc = cpu_decode_sample(w, 4 if args.workload == "cfg3" else 1)
-                sec = time_cpu(fn, 2, 1)
-                r["cpu_baseline"] = {"value": nbytes / sec / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
-                                     "sample": desc, "seconds_per_sample": sec}
+            rows = np.unique(np.random.default_rng(0).integers(0, q.shape[0] * q.shape[1] * q.shape[2], 400))
+            want = O.flash_attention(q, k, v, w.scale, mask_kind=O.MASK_CAUSAL, rows=rows, skip_masked=True)
+            err = np.abs(got.reshape(-1, q.shape[3])[rows] - want)
+            r["parity"] = {"max_abs": float(err.max()), "mean_abs": float(err.mean()), "rows_checked": int(rows.size),
+                           "tolerance": "max 2e-3, mean 2e-4"}
+        dtype = "f32" if name == "cfg1" else "bf16"
+        if rank == 0 and world == 1 and not fake_world and not args.no_extras and not args.quick:
+            cores = O.use_all_cores()
+            fn, flops, desc = cpu_full_prefill(w) if name == "cfg1" else cpu_prefill_sample(w)
+            sec = time_cpu(fn, 3, 1)
+            r["cpu_baseline"] = {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                 "sample": desc, "seconds_per_sample": sec}
+        if name == "cfg2" and not args.no_extras and not args.quick and not fake_world:
+            # the decode configurations and the step after attention ride on the same line, at every N
+            wd = load_cfg3()
+            d = decode_parity(run_decode(wd, "cfg3", chunked=False), wd, "cfg3")
+            extras["decode"] = d
+            del wd
+            mine, full = load_cfg4()
+            d4 = decode_parity(run_decode(mine, "cfg4", chunked=True), mine, "cfg4", full)
+            extras["decode_long"] = d4
+            del mine, full
+            if use_dist:
+                extras["oproj"] = run_oproj()
+    else:
+        if name == "cfg3":
+            w = load_cfg3()
+            r = decode_parity(run_decode(w, "cfg3", chunked=False, tag=" (scaled down: B16)" if args.small else ""), w, "cfg3")
+        else:
+            mine, full = load_cfg4()
+            r = decode_parity(run_decode(mine, "cfg4", chunked=True, tag=" (scaled down: 16384 keys)" if args.small else ""), mine, "cfg4", full)
+            w = mine
+        if rank == 0 and world == 1 and not fake_world and not args.quick and not args.no_extras:
+            cores = O.use_all_cores()
+            fn, nbytes, desc = cpu_decode_sample(w, 4 if name == "cfg3" else 1)
+            sec = time_cpu(fn, 2, 1)
+            r["cpu_baseline"] = {"value": nbytes / sec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                                 "sample": desc, "seconds_per_sample": sec}
         dtype = "bf16"
 
     if rank == 0:
@@ -688,15 +800,44 @@ def main():
             r["config"]["shard_of"] = f"rank 0 of a {fake_world}-rank job on one GPU: value is extrapolated as {fake_world} x this shard"
         line = {"metric": METRIC, "value": r["value"], "unit": r["unit"], "n_gpus": 1 if fake_world else world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": dtype, "data": "synthetic (seeded N(0,1) rounded to bf16; random values, no weights)",
+                "vs_baseline": None, "dtype": dtype, "data": DATA,
                 "config": r["config"], "roofline": r["roofline"], "e2e": r.get("e2e"), "clocks": r.get("clocks"),
                 "gpu_launches": r["gpu_launches"], "parity": r.get("parity")}
-        if "cpu_baseline" in r:
-            line["cpu_baseline"] = r["cpu_baseline"]
+        for key in ("cpu_baseline", "rank_ms_per_step", "collective", "nccl_gather", "input_copies", "bytes_per_step", "kv_copies", "launch"):
+            if key in r:
+                line[key] = r[key]
         line.update(extras)
         print(json.dumps(line))
     if use_dist:
         dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "oproj", "rope"],
+                    help="cfg1-cfg5: the attention configurations; oproj / rope: the steps after and before attention "
+                    "(output projection GEMM, fused RoPE + cache append) at config 2's sizes")
+    ap.add_argument("--no-extras", action="store_true", help="skip the decode / oproj entries and the CPU baseline")
+    ap.add_argument("--shard-of", type=int, default=0, help="for profiler captures on one GPU: run rank 0's shard of an "
+                    "N-rank job (no process group; the line is marked as a shard)")
+    ap.add_argument("--no-graph", action="store_true", help="decode workloads: time eager launches instead of CUDA graph replays")
+    ap.add_argument("--decode-ctas", type=int, default=0, help="decode workloads: grid size of the split-KV kernel (0 = automatic)")
+    ap.add_argument("--quick", action="store_true", help="for profiler captures: no clock-settling loop, no e2e, no extras")
+    ap.add_argument("--small", action="store_true", help="for profiler captures: a scaled-down case of the workload "
+                    "(prefill B2 Hq16 Hkv4 S4096; decode B16 / 16384 keys)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+    gpu_arm(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":

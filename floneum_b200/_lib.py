@@ -11,12 +11,12 @@ from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_voi
 
 from . import build as _build
 
-OK, INVALID_ARGUMENT, SHAPE_MISMATCH, UNSUPPORTED, CUDA_ERROR, NO_DEVICE, TIMEOUT, OUT_OF_PAGES, INTERNAL = range(9)
+OK, INVALID_ARGUMENT, SHAPE_MISMATCH, UNSUPPORTED, CUDA_ERROR, NO_DEVICE, TIMEOUT, OUT_OF_PAGES, INTERNAL, NCCL_ERROR = range(10)
 F32, BF16, F16 = 0, 1, 2
 MASK_NONE, MASK_QK, MASK_BATCH_KEY, MASK_CAUSAL, MASK_SLIDING = range(5)
 
 STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "SHAPE_MISMATCH", "UNSUPPORTED", "CUDA_ERROR", "NO_DEVICE", "TIMEOUT",
-                "OUT_OF_PAGES", "INTERNAL"]
+                "OUT_OF_PAGES", "INTERNAL", "NCCL_ERROR"]
 
 
 class Tensor4(ctypes.Structure):
@@ -72,6 +72,13 @@ SIGNATURES = {
     "fusor_cuda_kvcache_set_decode_ctas": (c_int32, [c_void_p, c_int32]),
     "fusor_cuda_exchange_lse_combine": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "fusor_cuda_attention_out_proj": (c_int32, [c_void_p, _T4, _T4, c_void_p, _T4]),
+    "fusor_cuda_comm_unique_id": (c_int32, [c_void_p]),
+    "fusor_cuda_comm_init": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, POINTER(c_void_p)]),
+    "fusor_cuda_comm_poll": (c_int32, [c_void_p]),
+    "fusor_cuda_comm_abort": (c_int32, [c_void_p]),
+    "fusor_cuda_comm_destroy": (c_int32, [c_void_p]),
+    "fusor_cuda_comm_all_reduce_sum": (c_int32, [c_void_p, c_void_p, c_int64, c_int32]),
+    "fusor_cuda_attention_out_proj_all_reduce": (c_int32, [c_void_p, c_void_p, _T4, _T4, c_void_p, _T4]),
     "fusor_cuda_rope": (c_int32, [c_void_p, _T4, c_void_p, c_void_p, c_int32, c_int32, c_int32, _T4]),
     "fusor_cuda_kvcache_rope_append": (c_int32, [c_void_p, _T4, _T4, _T4, c_void_p, c_void_p, c_int32, c_int32, c_int32, _T4]),
     "fusor_cuda_kvcache_truncate_front": (c_int32, [c_void_p, c_int32, c_int32]),

@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(_HERE, "libfusor_cuda.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--compiler-options", "-fPIC", "-shared",
+    "--compiler-options", "-fPIC", "-shared", "-ldl",
 ]
 
 

@@ -516,7 +516,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
     }
 }
 
-// parts [n_parts][n_rows][D+2] (m in natural-log units) -> out [n_rows][D]
+// parts [n_parts][n_rows][D+2] (m in natural-log units) -> out [n_rows][D]; a row whose parts are all empty gives zeros
 __global__ void lse_combine_kernel(const float* parts, int n_parts, long long n_rows, int D, float* out) {
     const long long row = blockIdx.x;
     const long long rec = D + 2;
@@ -536,7 +536,7 @@ __global__ void lse_combine_kernel(const float* parts, int n_parts, long long n_
             const float* pr = parts + ((long long)p * n_rows + row) * rec;
             if (pr[1] != 0.0f) acc += pr[2 + d] * __expf(pr[0] - M);
         }
-        out[row * D + d] = acc / L;
+        out[row * D + d] = L > 0.0f ? acc / L : 0.0f;
     }
 }
 

@@ -5,8 +5,11 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>  // types only: the library is resolved with dlopen when a communicator is first asked for
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -14,6 +17,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/fusor_cuda.h"
@@ -1414,6 +1418,188 @@ extern "C" int32_t fusor_cuda_exchange_decode(fusor_cuda_exchange* ex, fusor_cud
     const unsigned blocks = (unsigned)std::min<long long>(n_rows, ctx->num_sms);
     peer_merge_kernel<<<blocks, std::max(32, std::min(cache->D, 256)), 0, ctx->stream>>>(M);
     return launch_check(ctx, "peer_merge_kernel");
+}
+
+// =============================================================================== communicator (tensor-parallel output projection)
+// The one collective the head partition needs: the output projection right after attention sums partial results over the
+// ranks (models/kalosm-llama/src/raw/attention_layer.rs:450-454 with the heads split).  NCCL does the all-reduce (its
+// in-switch reduction runs at link speed); what the library owns is the plumbing a Rust binding cannot get from Python:
+// non-blocking initialisation with a host deadline, asynchronous error polling, abort, and the fused call.
+// libnccl is not linked: it is resolved at first use, the copy already mapped into the process first.
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    std::string error;
+};
+static NcclApi g_nccl;
+static std::mutex g_nccl_mutex;
+
+static const NcclApi* nccl_api() {
+    std::lock_guard<std::mutex> lock(g_nccl_mutex);
+    if (g_nccl.handle) return &g_nccl;
+    void* h = nullptr;
+    if (const char* path = std::getenv("FUSOR_CUDA_NCCL_LIB")) h = dlopen(path, RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // the copy the host program already uses
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) {
+        g_nccl.error = std::string("libnccl.so.2 cannot be loaded: ") + (dlerror() ? dlerror() : "unknown error");
+        return nullptr;
+    }
+    auto sym = [&](const char* name) { return dlsym(h, name); };
+    g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(sym("ncclGetUniqueId"));
+    g_nccl.CommInitRankConfig = reinterpret_cast<decltype(g_nccl.CommInitRankConfig)>(sym("ncclCommInitRankConfig"));
+    g_nccl.CommGetAsyncError = reinterpret_cast<decltype(g_nccl.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
+    g_nccl.CommAbort = reinterpret_cast<decltype(g_nccl.CommAbort)>(sym("ncclCommAbort"));
+    g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(sym("ncclCommDestroy"));
+    g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(sym("ncclAllReduce"));
+    g_nccl.GetErrorString = reinterpret_cast<decltype(g_nccl.GetErrorString)>(sym("ncclGetErrorString"));
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRankConfig || !g_nccl.CommGetAsyncError || !g_nccl.CommAbort || !g_nccl.CommDestroy ||
+        !g_nccl.AllReduce || !g_nccl.GetErrorString) {
+        g_nccl.error = "libnccl.so.2 lacks an entry point this library needs";
+        return nullptr;
+    }
+    g_nccl.handle = h;
+    return &g_nccl;
+}
+
+struct fusor_cuda_comm {
+    fusor_cuda_ctx* ctx = nullptr;
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 0;
+    int timeout_ms = 0;
+    bool aborted = false;
+};
+
+extern "C" int32_t fusor_cuda_comm_unique_id(void* id128) {
+    if (!id128) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "id buffer is null");
+    static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
+    const NcclApi* api = nccl_api();
+    if (!api) return fail(nullptr, FUSOR_CUDA_NCCL_ERROR, "%s", g_nccl.error.c_str());
+    ncclUniqueId id;
+    const ncclResult_t r = api->GetUniqueId(&id);
+    if (r != ncclSuccess) return fail(nullptr, FUSOR_CUDA_NCCL_ERROR, "ncclGetUniqueId: %s", api->GetErrorString(r));
+    std::memcpy(id128, &id, 128);
+    return FUSOR_CUDA_OK;
+}
+
+// Polls the communicator until its pending operation has completed, failed, or the deadline has passed (then: abort).
+static int32_t comm_settle(fusor_cuda_comm* cm, const char* what) {
+    const NcclApi* api = nccl_api();
+    const auto t0 = std::chrono::steady_clock::now();
+    while (true) {
+        ncclResult_t state = ncclSuccess;
+        const ncclResult_t r = api->CommGetAsyncError(cm->comm, &state);
+        if (r != ncclSuccess) return fail(cm->ctx, FUSOR_CUDA_NCCL_ERROR, "%s: ncclCommGetAsyncError: %s", what, api->GetErrorString(r));
+        if (state == ncclSuccess) return FUSOR_CUDA_OK;
+        if (state != ncclInProgress) {
+            api->CommAbort(cm->comm);
+            cm->comm = nullptr;
+            cm->aborted = true;
+            return fail(cm->ctx, FUSOR_CUDA_NCCL_ERROR, "%s: %s (communicator aborted)", what, api->GetErrorString(state));
+        }
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > cm->timeout_ms) {
+            api->CommAbort(cm->comm);
+            cm->comm = nullptr;
+            cm->aborted = true;
+            return fail(cm->ctx, FUSOR_CUDA_TIMEOUT, "%s did not complete within %d ms (a rank is missing or stuck); communicator aborted", what,
+                        cm->timeout_ms);
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    }
+}
+
+extern "C" int32_t fusor_cuda_comm_init(fusor_cuda_ctx* ctx, const void* id128, int32_t rank, int32_t world, int32_t timeout_ms,
+                                        fusor_cuda_comm** out) {
+    if (!ctx || !id128 || !out) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (world < 1 || rank < 0 || rank >= world || timeout_ms <= 0)
+        return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "rank %d outside world %d, or non-positive timeout", rank, world);
+    const NcclApi* api = nccl_api();
+    if (!api) return fail(ctx, FUSOR_CUDA_NCCL_ERROR, "%s", g_nccl.error.c_str());
+    DeviceGuard g(ctx->device);
+    fusor_cuda_comm* cm = new fusor_cuda_comm();
+    cm->ctx = ctx; cm->rank = rank; cm->world = world; cm->timeout_ms = timeout_ms;
+    ncclUniqueId id;
+    std::memcpy(&id, id128, 128);
+    ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+    config.blocking = 0;  // every call returns at once; completion is polled against the caller's deadline
+    const ncclResult_t r = api->CommInitRankConfig(&cm->comm, world, id, rank, &config);
+    if (r != ncclSuccess && r != ncclInProgress) {
+        const int32_t rc = fail(ctx, FUSOR_CUDA_NCCL_ERROR, "ncclCommInitRankConfig: %s", api->GetErrorString(r));
+        delete cm;
+        return rc;
+    }
+    const int32_t rc = comm_settle(cm, "communicator initialisation");
+    if (rc != FUSOR_CUDA_OK) {
+        delete cm;
+        return rc;
+    }
+    *out = cm;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_comm_poll(fusor_cuda_comm* cm) {
+    if (!cm) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "communicator is null");
+    if (cm->aborted || !cm->comm) return fail(cm->ctx, FUSOR_CUDA_NCCL_ERROR, "the communicator has been aborted");
+    const NcclApi* api = nccl_api();
+    ncclResult_t state = ncclSuccess;
+    const ncclResult_t r = api->CommGetAsyncError(cm->comm, &state);
+    if (r != ncclSuccess) return fail(cm->ctx, FUSOR_CUDA_NCCL_ERROR, "ncclCommGetAsyncError: %s", api->GetErrorString(r));
+    if (state == ncclSuccess || state == ncclInProgress) return FUSOR_CUDA_OK;
+    return fail(cm->ctx, FUSOR_CUDA_NCCL_ERROR, "asynchronous communicator error: %s", api->GetErrorString(state));
+}
+
+extern "C" int32_t fusor_cuda_comm_abort(fusor_cuda_comm* cm) {
+    if (!cm) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "communicator is null");
+    if (cm->comm) {
+        DeviceGuard g(cm->ctx->device);
+        nccl_api()->CommAbort(cm->comm);
+        cm->comm = nullptr;
+    }
+    cm->aborted = true;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_comm_destroy(fusor_cuda_comm* cm) {
+    if (!cm) return FUSOR_CUDA_OK;
+    if (cm->comm) {
+        DeviceGuard g(cm->ctx->device);
+        cudaStreamSynchronize(cm->ctx->stream);
+        nccl_api()->CommDestroy(cm->comm);
+    }
+    delete cm;
+    return FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_comm_all_reduce_sum(fusor_cuda_comm* cm, void* data, int64_t count, int32_t dtype) {
+    if (!cm || !data || count <= 0) return fail(cm ? cm->ctx : nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument or non-positive count");
+    if (cm->aborted || !cm->comm) return fail(cm->ctx, FUSOR_CUDA_NCCL_ERROR, "the communicator has been aborted");
+    if (!dtype_ok(dtype)) return fail(cm->ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
+    const NcclApi* api = nccl_api();
+    DeviceGuard g(cm->ctx->device);
+    const ncclDataType_t dt = dtype == FUSOR_CUDA_F32 ? ncclFloat32 : dtype == FUSOR_CUDA_F16 ? ncclFloat16 : ncclBfloat16;
+    const ncclResult_t r = api->AllReduce(data, data, (size_t)count, dt, ncclSum, cm->comm, cm->ctx->stream);
+    if (r != ncclSuccess && r != ncclInProgress) return fail(cm->ctx, FUSOR_CUDA_NCCL_ERROR, "ncclAllReduce: %s", api->GetErrorString(r));
+    // the launch of a non-blocking communicator may still be in progress on the host: settle it (not the collective itself,
+    // which completes on the stream)
+    return r == ncclInProgress ? comm_settle(cm, "all-reduce launch") : FUSOR_CUDA_OK;
+}
+
+extern "C" int32_t fusor_cuda_attention_out_proj_all_reduce(fusor_cuda_ctx* ctx, fusor_cuda_comm* cm, const fusor_cuda_tensor4* attn,
+                                                            const fusor_cuda_tensor4* weight, const float* bias,
+                                                            const fusor_cuda_tensor4* out) {
+    if (!cm || cm->ctx != ctx) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "the communicator belongs to another context");
+    if (!out || out->stride[3] != 1 || out->stride[2] != out->shape[3] || (out->shape[0] > 1 && out->stride[0] != out->shape[2] * out->shape[3]))
+        return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "the all-reduced output must be contiguous");
+    TRY(fusor_cuda_attention_out_proj(ctx, attn, weight, cm->rank == 0 ? bias : nullptr, out));
+    return fusor_cuda_comm_all_reduce_sum(cm, out->data, out->shape[0] * out->shape[2] * out->shape[3], out->dtype);
 }
 
 // =============================================================================== wait-limit self test

@@ -146,6 +146,75 @@ def out_proj_weight_columns(num_q_heads: int, num_kv_heads: int, head_dim: int, 
     return q0 * head_dim, q1 * head_dim
 
 
+class Communicator:
+    """The library's own communicator (`fusor_cuda_comm_*`): NCCL behind the C ABI, initialised without blocking and
+    polled against a host deadline, so that a rank that never joins ends in a TIMEOUT error instead of a hang.
+    The 128-byte id is made on rank 0 and reaches the others through `broadcast_bytes` (default: torch.distributed's
+    object broadcast, which works on the gloo backend too)."""
+
+    def __init__(self, device, rank: int, world: int, timeout_ms: int = 30000, unique_id: bytes | None = None, group=None):
+        import ctypes
+        from . import _lib
+        self.device, self.rank, self.world = device, rank, world
+        self._L = _lib.load()
+        if unique_id is None:
+            import torch.distributed as dist
+            box = [self.make_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0, group=group)
+            unique_id = box[0]
+        assert len(unique_id) == 128
+        h = ctypes.c_void_p()
+        _lib.check(self._L.fusor_cuda_comm_init(device.handle, unique_id, rank, world, int(timeout_ms), ctypes.byref(h)),
+                   device.handle)
+        self._h = h
+
+    @staticmethod
+    def make_unique_id() -> bytes:
+        import ctypes
+        from . import _lib
+        buf = ctypes.create_string_buffer(128)
+        _lib.check(_lib.load().fusor_cuda_comm_unique_id(buf), None)
+        return bytes(buf.raw)
+
+    def poll(self):
+        from . import _lib
+        _lib.check(self._L.fusor_cuda_comm_poll(self._h), self.device.handle)
+
+    def all_reduce_sum(self, t):
+        """In-place sum over the ranks of a contiguous library Tensor, on the device's stream."""
+        from . import _lib
+        assert t.is_contiguous()
+        _lib.check(self._L.fusor_cuda_comm_all_reduce_sum(self._h, t.ptr, t.numel(), t.dtype), self.device.handle)
+        return t
+
+    def out_proj(self, attn, weight_shard, bias, out):
+        """This rank's heads x weight columns, then the sum over ranks, in one library call.  attn [B, Hq/N, S, D] bf16,
+        weight_shard [out, Hq/N * D] bf16, bias f32 [out] or None (used on rank 0), out [B, S, out] contiguous."""
+        import ctypes
+        from . import _lib
+        from .tensor import Tensor
+        B, _, S, _ = attn.shape()
+        ws = weight_shard.shape()
+        w4 = Tensor(self.device, weight_shard.ptr, (1, 1, ws[0], ws[1]), weight_shard.dtype,
+                    (ws[0] * weight_shard.strides[0], ws[0] * weight_shard.strides[0], weight_shard.strides[0], weight_shard.strides[1]),
+                    owner=weight_shard)
+        o4 = Tensor(self.device, out.ptr, (B, 1, S, ws[0]), out.dtype, (S * ws[0], S * ws[0], ws[0], 1), owner=out)
+        ca, cw, co = attn._c4(), w4._c4(), o4._c4()
+        _lib.check(self._L.fusor_cuda_attention_out_proj_all_reduce(self.device.handle, self._h, ctypes.byref(ca), ctypes.byref(cw),
+                                                                    bias.ptr if bias is not None else None, ctypes.byref(co)),
+                   self.device.handle)
+        return out
+
+    def abort(self):
+        if getattr(self, "_h", None):
+            self._L.fusor_cuda_comm_abort(self._h)
+
+    def close(self):
+        if getattr(self, "_h", None) and self.device.handle:
+            self._L.fusor_cuda_comm_destroy(self._h)
+        self._h = None
+
+
 def all_reduce_sum(t, group=None):
     """In-place sum over ranks of a torch tensor (NCCL on GPUs, gloo in the CPU tests)."""
     import torch.distributed as dist

@@ -33,6 +33,7 @@ extern "C" {
 #define FUSOR_CUDA_TIMEOUT 6          /* a bounded device-side wait ran out; the context stays usable */
 #define FUSOR_CUDA_OUT_OF_PAGES 7     /* KV cache page pool exhausted */
 #define FUSOR_CUDA_INTERNAL 8
+#define FUSOR_CUDA_NCCL_ERROR 9       /* the NCCL library is missing or a communicator call failed */
 
 /* ---- element types (reference DataTypeEnum is F32/F16/U32, fusor-ml/core/src/tensor.rs:112-116; bf16 is added) */
 #define FUSOR_CUDA_F32 0
@@ -275,6 +276,32 @@ int32_t fusor_cuda_exchange_lse_combine(fusor_cuda_exchange* ex, const float* re
  * the ranks then add their results (all-reduce). */
 int32_t fusor_cuda_attention_out_proj(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* attn, const fusor_cuda_tensor4* weight,
                                       const float* bias, const fusor_cuda_tensor4* out);
+/* ------------------------------------------------------------------------------------------------
+ * Communicator for the one collective the head partition needs (no counterpart in the reference, which has no
+ * multi-GPU path): with the query heads split over GPUs the output projection yields partial sums, and the layer's
+ * result (models/kalosm-llama/src/raw/attention_layer.rs:450-454) is their sum over the ranks.  NCCL (resolved with
+ * dlopen at first use: FUSOR_CUDA_NCCL_LIB, else the libnccl.so.2 already mapped into the process, else the loader's
+ * search path) runs the all-reduce on the context's stream.
+ *   unique_id  : rank 0 creates the 128-byte id; the caller sends it to every rank by its own transport
+ *   init       : non-blocking initialisation polled against `timeout_ms` on the host; a rank that never joins ends in
+ *                FUSOR_CUDA_TIMEOUT with the communicator aborted, not in a hang.  The same deadline bounds the host
+ *                side of every later call on the communicator
+ *   poll       : FUSOR_CUDA_NCCL_ERROR when NCCL has recorded an asynchronous error (a peer died, a link failed)
+ *   abort      : gives up on the communicator from the host; no later call succeeds; destroy frees it
+ *   all_reduce_sum : in place, count elements of dtype f32 / bf16 / f16, stream-ordered
+ *   attention_out_proj_all_reduce : fusor_cuda_attention_out_proj with this rank's heads and weight columns (bias on
+ *                rank 0 only), then the all-reduce of `out` (contiguous), in one call */
+typedef struct fusor_cuda_comm fusor_cuda_comm;
+int32_t fusor_cuda_comm_unique_id(void* id128);
+int32_t fusor_cuda_comm_init(fusor_cuda_ctx* ctx, const void* id128, int32_t rank, int32_t world, int32_t timeout_ms,
+                             fusor_cuda_comm** out);
+int32_t fusor_cuda_comm_poll(fusor_cuda_comm* comm);
+int32_t fusor_cuda_comm_abort(fusor_cuda_comm* comm);
+int32_t fusor_cuda_comm_destroy(fusor_cuda_comm* comm);
+int32_t fusor_cuda_comm_all_reduce_sum(fusor_cuda_comm* comm, void* data, int64_t count, int32_t dtype);
+int32_t fusor_cuda_attention_out_proj_all_reduce(fusor_cuda_ctx* ctx, fusor_cuda_comm* comm, const fusor_cuda_tensor4* attn,
+                                                 const fusor_cuda_tensor4* weight, const float* bias,
+                                                 const fusor_cuda_tensor4* out);
 /* Merge: parts f32 [n_parts][n_rows][D+2] -> out f32 [n_rows][D]  (M = max m, L = sum l e^(m-M),
  * out = sum O e^(m-M) / L; the (m, d) rule of fusor-ml/core/src/composite/softmax.rs:59-82).
  * A part with l == 0 contributes nothing; a row whose parts are all empty gives zeros. */

@@ -49,6 +49,15 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* A launcher may have exported OMP_NUM_THREADS=1 (torchrun does); the timed CPU baseline sets its thread count itself. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* K^T for one (batch, kv head): kt[d * Skv + j] = k[j * D + d].
  * (k.transpose(2,3) is made contiguous before the gemm, cpu/src/tensor.rs:1063-1072.) */
 static void transpose_k(const float* k, float* kt, int Skv, int D) {
@@ -247,7 +256,9 @@ void oracle_lse_combine(const float* parts, int n_parts, int64_t n_rows, int D, 
             L += pr[1] * w;
             for (int d = 0; d < D; ++d) out[(size_t)r * D + d] += pr[2 + d] * w;
         }
-        for (int d = 0; d < D; ++d) out[(size_t)r * D + d] = out[(size_t)r * D + d] / L;
+        /* a row whose parts are all empty attends to no key: zeros (the merge has no reference counterpart; this is
+           the rule the library documents) */
+        for (int d = 0; d < D; ++d) out[(size_t)r * D + d] = L > 0.0f ? out[(size_t)r * D + d] / L : 0.0f;
     }
 }
 

@@ -70,6 +70,18 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def use_all_cores() -> int:
+    """Sets the OpenMP thread count to the cores this process may run on (a launcher such as torchrun exports
+    OMP_NUM_THREADS=1, which would make the CPU baseline single-threaded) and returns it."""
+    import os
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.float32)
 

@@ -14,7 +14,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import oracle as O  # noqa: E402
-from floneum_b200 import workloads as W  # noqa: E402
+from oracle import workloads as W  # noqa: E402
 
 NEG = float("-inf")
 

@@ -147,7 +147,7 @@ def test_sliding_window_and_offset_masks(device):
 def test_cfg1_cpu_reference_config_f32(device):
     """BASELINE config 1 in full: B1 S512 Hq32 Hkv8 D64 f32, causal, scale 1/8."""
     fb = _mods()
-    from floneum_b200 import workloads as W
+    from oracle import workloads as W
     w = W.cfg1()
     want = O.flash_attention(w.q, w.k, w.v, w.scale, O.causal_mask(512), O.MASK_QK)
     got = _run(device, w.q, w.k, w.v, w.scale, (fb.AttentionMask.causal(device, 512), fb.MaskKind.QKMask))
@@ -181,7 +181,7 @@ def test_host_entry_point(device):
 
 # ----------------------------------------------------------------------------- tensor-core prefill (bf16, D = 128)
 def _bf16_case(seed, B, Hq, Hkv, Sq, Skv, sigma=1.0):
-    from floneum_b200 import workloads as W
+    from oracle import workloads as W
     rng = np.random.default_rng(seed)
     q = W.bf16_round(sigma * rng.standard_normal((B, Hq, Sq, 128), dtype=np.float32))
     k = W.bf16_round(sigma * rng.standard_normal((B, Hkv, Skv, 128), dtype=np.float32))
@@ -258,7 +258,7 @@ def test_prefill_strided_views_and_bf16_out(device):
 def test_prefill_cfg5_value_distribution(device):
     """cfg5's distribution at reduced length: N(0, 0.5^2) with 5% of K rows x8 (softmax range stress)."""
     fb = _mods()
-    from floneum_b200 import workloads as W
+    from oracle import workloads as W
     w = W.cfg5(S=1536, Hq=8, Hkv=2)
     got = _run(device, w.q, w.k, w.v, w.scale, (fb.AttentionMask.causal(device, 1536), fb.MaskKind.QKMask), dtype=1)
     want = O.flash_attention(w.q, w.k, w.v, w.scale, mask_kind=O.MASK_CAUSAL, skip_masked=True)
@@ -269,7 +269,7 @@ def test_prefill_cfg2_full_size_sampled_rows(device):
     """BASELINE config 2 at full size (B4 S4096 Hq32 Hkv8 D128): sampled rows against the oracle, plus
     size-independent properties: row 0 of every head equals V row 0, and permuting batches permutes outputs."""
     fb = _mods()
-    from floneum_b200 import workloads as W
+    from oracle import workloads as W
     w = W.cfg2()
     B, Hq, S, D = w.q.shape
     tq, tk, tv = (fb.Tensor.from_slice(device, a.shape, a, 1) for a in (w.q, w.k, w.v))
@@ -402,3 +402,54 @@ def test_prefill_two_tile_kernel_shape_fuzz(device, it):
         got = _run(device, q, k, v, scale, (fb.Tensor.from_slice(device, mask.shape, mask), fb.MaskKind.BatchKeyMask), dtype=1)
         want = O.flash_attention(q, k, v, scale, mask, O.MASK_BATCH_KEY)
     assert_close(got, want, what=f"two-tile fuzz {it}: B{B} Hq{Hkv * g}/{Hkv} Sq{Sq} Skv{Skv} {kind}")
+
+
+def test_prefill_cfg5_full_size_sampled_rows(device):
+    """BASELINE config 5 at full size (B1 S16384 Hq64 Hkv8 D128, N(0, 0.5^2), 5 % of the K rows x 8): sampled rows against
+    the oracle, among them the first and last row of every head and the rows either side of every 256-row item edge of
+    a few heads; row 0 of every head equals V row 0."""
+    fb = _mods()
+    from oracle import workloads as W
+    w = W.cfg5()
+    B, Hq, S, D = w.q.shape
+    tq, tk, tv = (fb.Tensor.from_slice(device, a.shape, a, 1) for a in (w.q, w.k, w.v))
+    got = tq.flash_attention(tk, tv, w.scale, (fb.AttentionMask.causal(device, S), fb.MaskKind.QKMask)).as_slice()
+    assert np.isfinite(got).all()
+    rng = np.random.default_rng(5)
+    edges = np.concatenate([np.arange(255, S, 256), np.arange(256, S, 256), np.arange(127, S, 256), np.arange(128, S, 256)])
+    rows = np.unique(np.concatenate([rng.integers(0, Hq * S, 700), np.arange(0, Hq * S, S), np.arange(S - 1, Hq * S, S)] +
+                                    [h * S + edges for h in (0, 9, 37, 63)]))
+    want = O.flash_attention(w.q, w.k, w.v, w.scale, mask_kind=O.MASK_CAUSAL, rows=rows, skip_masked=True)
+    assert_close(got.reshape(-1, D)[rows], want, what="cfg5 sampled rows")
+    g = Hq // w.k.shape[1]
+    for h in range(Hq):
+        assert np.abs(got[0, h, 0] - w.v[0, h // g, 0]).max() <= 2e-3
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,causal", [(1, 4, 2, 130, 130, True), (2, 8, 2, 512, 512, True), (1, 4, 4, 300, 777, False),
+                                                     (1, 2, 1, 1024, 1024, True)])
+def test_prefill_f16_tensors(device, B, Hq, Hkv, Sq, Skv, causal):
+    """f16 q, k, v (the reference's GPU arm is generic over f32 / f16 with f32 accumulation,
+    fusor-ml/core/src/composite/flash_attention.rs:28-38,189): both tensor-core kernels, f32 and f16 outputs, against the
+    oracle on the same f16-rounded inputs; and the general kernel on a head_dim the tensor-core kernels do not take."""
+    fb = _mods()
+    rng = np.random.default_rng(1000 * Sq + Skv)
+    h = lambda a: a.astype(np.float16).astype(np.float32)
+    q, k, v = (h(rng.standard_normal(s, dtype=np.float32)) for s in ((B, Hq, Sq, 128), (B, Hkv, Skv, 128), (B, Hkv, Skv, 128)))
+    scale = 128 ** -0.5
+    if causal:
+        mask = (fb.AttentionMask.causal(device, Sq), fb.MaskKind.QKMask) if Sq == Skv else None
+        want = O.flash_attention(q, k, v, scale, mask_kind=O.MASK_CAUSAL)
+    else:
+        mask, want = None, O.flash_attention(q, k, v, scale)
+    before = device.launch_count()
+    got = _run(device, q, k, v, scale, mask, dtype=2)
+    assert device.launch_count() - before == 1  # no copy of V: the weights are f16 against V itself
+    assert_close(got, want, what="f16 in, f32 out")
+    got16 = _run(device, q, k, v, scale, mask, dtype=2, out_dtype=2)
+    assert_close(got16, h(want), max_tol=2e-3 + 2.0 ** -10, mean_tol=4e-4, what="f16 in, f16 out")
+    if Sq == 130:
+        q64, k64, v64 = q[..., :64].copy(), k[..., :64].copy(), v[..., :64].copy()
+        got64 = _run(device, q64, k64, v64, 0.125, mask, dtype=2, out_dtype=2)
+        assert_close(got64, h(O.flash_attention(q64, k64, v64, 0.125, mask_kind=O.MASK_CAUSAL)), max_tol=2.0 ** -10 + 2e-5, mean_tol=2e-4,
+                     what="f16 through the general kernel")

@@ -32,7 +32,7 @@ def _oracle_decode(w):
 def test_paged_decode_ragged(device, B, Hq, Hkv, lo, hi):
     """Ragged lengths (including partial last pages and 1-token sequences), permuted page table, g = 1..8."""
     fb = _fb()
-    from floneum_b200 import workloads as W
+    from oracle import workloads as W
     w = W.cfg3(B=B, Hq=Hq, Hkv=Hkv, lo=lo, hi=hi)
     cache = _install(device, w)
     q = fb.Tensor.from_slice(device, w.q.shape, w.q, 1)
@@ -57,7 +57,7 @@ def test_paged_decode_golden_fixture(device):
 
 def test_decode_head_dim_64(device):
     fb = _fb()
-    from floneum_b200 import workloads as W
+    from oracle import workloads as W
     rng = np.random.default_rng(12)
     B, Hq, Hkv, D = 2, 8, 2, 64
     lens = np.array([75, 130])
@@ -85,7 +85,7 @@ def test_decode_partial_and_lse_combine(device):
     """KV-sequence chunks: per-chunk partials {m, l, O} merged by log-sum-exp equal attention over all keys,
     and each partial matches the oracle's partial of that key range."""
     fb = _fb()
-    from floneum_b200 import workloads as W
+    from oracle import workloads as W
     from floneum_b200.cache import lse_combine
     world = 4
     full = W.cfg4(Skv=4096 + 160, Hq=16, Hkv=2)
@@ -193,7 +193,7 @@ def test_bad_page_table_is_rejected_on_the_host(device):
 def test_cfg3_full_size(device):
     """BASELINE config 3 at full size: B64, Hq32, Hkv8, D128, kv_len ~ U[1024, 8192], permuted pages."""
     fb = _fb()
-    from floneum_b200 import workloads as W
+    from oracle import workloads as W
     w = W.cfg3()
     cache = _install(device, w)
     got = cache.decode(fb.Tensor.from_slice(device, w.q.shape, w.q, 1), w.scale).as_slice()
@@ -260,3 +260,158 @@ def test_peer_exchange_world_of_one_merges_like_lse_combine(device):
         want = O.lse_combine(rec[None])
         assert np.abs(got - want).max() < 1e-5, step
     ex.close()
+
+
+@pytest.mark.parametrize("ctas", [1, 3, 37, 148, 592])
+def test_decode_grid_sizes_give_the_same_answer(device, ctas):
+    """The deal of pages to CTAs is computed inside the kernel from the lengths on the device: any grid size must merge to
+    the same attention (1 CTA: every sequence-head is whole inside it; 592: most are spread over several CTAs and merged
+    by the CTA that finishes last)."""
+    fb = _fb()
+    from oracle import workloads as W
+    w = W.cfg3(B=6, Hq=16, Hkv=4, lo=30, hi=2500)
+    cache = _install(device, w)
+    cache.set_decode_ctas(ctas)
+    q = fb.Tensor.from_slice(device, w.q.shape, w.q, 1)
+    want = _oracle_decode(w)
+    for _ in range(2):  # twice: the per-sequence counters must be back at zero after a launch
+        assert_close(cache.decode(q, w.scale).as_slice(), want, what=f"decode with {ctas} CTAs")
+    # 16-bit outputs and an f16 query tensor
+    got_bf16 = cache.decode(q, w.scale, out_dtype=1).as_slice()
+    assert_close(got_bf16, O.bf16_round(want), max_tol=2e-3 + 2.0 ** -7, mean_tol=2e-3, what="bf16 out")
+    # the bf16-representable q values are f16-representable too (normal range): same inputs, f16 output rounding on top
+    got_f16 = cache.decode(fb.Tensor.from_slice(device, w.q.shape, w.q, 2), w.scale, out_dtype=2).as_slice()
+    assert_close(got_f16, want, max_tol=2e-3 + 2.0 ** -10, mean_tol=4e-4, what="f16 q and out")
+
+
+def test_live_decode_steps_need_no_plan(device):
+    """Append one token per sequence and decode, 40 times, lengths crossing page boundaries at different steps: the kernel
+    reads the lengths the append uploaded, nothing else is planned or uploaded per step."""
+    fb = _fb()
+    rng = np.random.default_rng(77)
+    B, Hq, Hkv, D = 3, 8, 2, 128
+    cache = fb.PagedKvCache(device, B, Hkv, D, num_pages=64, max_pages_per_seq=16)
+    n0 = 9
+    ks = [O.bf16_round(rng.standard_normal((B, Hkv, n0, D)).astype(np.float32))]
+    vs = [O.bf16_round(rng.standard_normal((B, Hkv, n0, D)).astype(np.float32))]
+    cache.append(fb.Tensor.from_slice(device, ks[0].shape, ks[0]), fb.Tensor.from_slice(device, vs[0].shape, vs[0]))
+    for step in range(40):
+        k1 = O.bf16_round(rng.standard_normal((B, Hkv, 1, D)).astype(np.float32))
+        v1 = O.bf16_round(rng.standard_normal((B, Hkv, 1, D)).astype(np.float32))
+        ks.append(k1); vs.append(v1)
+        cache.append(fb.Tensor.from_slice(device, k1.shape, k1), fb.Tensor.from_slice(device, v1.shape, v1))
+        q = O.bf16_round(rng.standard_normal((B, Hq, 1, D)).astype(np.float32))
+        got = cache.decode(fb.Tensor.from_slice(device, q.shape, q, 1), D ** -0.5).as_slice()
+        want = O.flash_attention(q, np.concatenate(ks, 2), np.concatenate(vs, 2), D ** -0.5)
+        assert_close(got, want, what=f"live decode step {step}")
+
+
+def test_cfg4_full_size_eight_chunks_on_one_gpu(device):
+    """BASELINE config 4 at full size (B1 Hq64 Hkv8 D128, 131072 keys) on one GPU: the whole sequence in one call, and as
+    the 8 contiguous KV chunks of the multi-GPU partition, each through decode_partial, merged by lse_combine and by the
+    peer exchange's own merge (world of one per chunk is not a merge: the records go through fusor_cuda_lse_combine)."""
+    fb = _fb()
+    from oracle import workloads as W
+    from floneum_b200.cache import lse_combine
+    w = W.cfg4()
+    want = O.flash_attention(w.q, w.k_dense[0][None], w.v_dense[0][None], w.scale)
+    cache = _install(device, w)
+    q = fb.Tensor.from_slice(device, w.q.shape, w.q, 1)
+    got = cache.decode(q, w.scale).as_slice()
+    assert_close(got, want, what="cfg4 whole sequence")
+    cache.close()
+    world, npg = 8, w.k_pages.shape[0]
+    per = npg // world
+    parts = []
+    for r in range(world):
+        c = fb.PagedKvCache(device, 1, 8, 128, per, per)
+        c.write_pages(0, w.k_pages[r * per:(r + 1) * per], w.v_pages[r * per:(r + 1) * per])
+        c.set_page_table(np.arange(per, dtype=np.int32)[None], np.array([per * 16], np.int32))
+        parts.append(c.decode_partial(q, w.scale).as_slice())
+        c.close()
+    stacked = fb.Tensor.from_slice(device, (world,) + parts[0].shape, np.stack(parts))
+    merged = lse_combine(device, stacked).as_slice()
+    assert_close(merged, want[:, :, 0], what="cfg4 in 8 chunks")
+    # an oracle restatement of the same merge on the records the GPU produced
+    assert np.abs(merged - O.lse_combine(np.stack(parts).reshape(world, -1, 130)).reshape(merged.shape)).max() < 1e-5
+
+
+def test_lse_combine_of_empty_rows_gives_zeros(device):
+    """A row whose parts are all empty (l == 0) has no keys to attend to: the merge writes zeros, not 0/0."""
+    fb = _fb()
+    from floneum_b200.cache import lse_combine
+    from floneum_b200.sharding import PeerExchange
+    parts = np.zeros((3, 4, 18), np.float32)
+    parts[..., 0] = -np.inf
+    parts[1, 2] = np.arange(18, dtype=np.float32) + 1  # one live record in row 2
+    got = lse_combine(device, fb.Tensor.from_slice(device, parts.shape, parts)).as_slice()
+    assert np.array_equal(got[[0, 1, 3]], np.zeros((3, 16), np.float32))
+    assert np.allclose(got[2], parts[1, 2, 2:] / parts[1, 2, 1])
+    ex = PeerExchange(device, 0, 1, 4 * 18 + 0)
+    out = fb.Tensor.from_slice(device, (4, 16), np.ones((4, 16), np.float32))
+    ex.lse_combine(fb.Tensor.from_slice(device, (4, 18), parts[0]), out)
+    assert np.array_equal(out.as_slice(), np.zeros((4, 16), np.float32))
+    ex.close()
+
+
+def test_exchange_decode_world_of_one(device):
+    """fusor_cuda_exchange_decode with a single rank: the decode kernel's last CTA per (sequence, kv head) stores the
+    merged records into the rank's own slot, the merge kernel waits for its own epoch.  Three steps: both slot parities."""
+    fb = _fb()
+    from oracle import workloads as W
+    from floneum_b200.sharding import PeerExchange
+    w = W.cfg4(Skv=6000, Hq=32, Hkv=4)
+    cache = _install(device, w)
+    B, Hq, _, D = w.q.shape
+    ex = PeerExchange(device, 0, 1, B * Hq * (D + 2))
+    q = fb.Tensor.from_slice(device, w.q.shape, w.q, 1)
+    want = O.flash_attention(w.q, w.k_dense[0][None], w.v_dense[0][None], w.scale)[:, :, 0]
+    for ctas in (0, 5, 0):
+        cache.set_decode_ctas(ctas)
+        out = fb.Tensor.zeros(device, (B, Hq, D))
+        ex.decode(cache, q, w.scale, out)
+        assert_close(out.as_slice(), want, what=f"exchange decode, {ctas} CTAs")
+    ex.close()
+
+
+def test_token_granular_eviction_is_two_launches(device):
+    """TensorCache eviction at full cache (tensor_cache.rs:55-78) drops one token per decode step: the kept rows move
+    with two kernel launches whatever the length, and the cache then holds the newest rows."""
+    fb = _fb()
+    rng = np.random.default_rng(5)
+    B, Hkv, D, n = 2, 4, 128, 200
+    cache = fb.PagedKvCache(device, B, Hkv, D, num_pages=40, max_pages_per_seq=16)
+    k = O.bf16_round(rng.standard_normal((B, Hkv, n, D)).astype(np.float32))
+    v = O.bf16_round(rng.standard_normal((B, Hkv, n, D)).astype(np.float32))
+    cache.append(fb.Tensor.from_slice(device, k.shape, k), fb.Tensor.from_slice(device, v.shape, v))
+    cache.truncate_front(0, n - 3)  # first use allocates the staging buffer
+    before = device.launch_count()
+    cache.truncate_front(1, n - 3)
+    assert device.launch_count() - before == 2
+    gk, gv = cache.gather(B, n - 3)
+    assert np.array_equal(gk.as_slice(), k[:, :, 3:]) and np.array_equal(gv.as_slice(), v[:, :, 3:])
+    before = device.launch_count()
+    cache.truncate_front(0, n - 3 - 32)  # whole pages: table edit only
+    assert device.launch_count() == before
+    assert np.array_equal(cache.gather(B, n - 3)[0].as_slice()[0, :, :n - 35], k[0, :, 35:])
+
+
+def test_llama_cache_layers_keep_their_own_lengths(device):
+    """LlamaCache (models/kalosm-llama/src/raw/cache.rs:14-54): sliding layers keep `sliding_window_size` tokens, every
+    `sliding_window_type`-th layer the whole context."""
+    from floneum_b200 import LlamaCache, Tensor
+    rng = np.random.default_rng(9)
+    cache = LlamaCache(n_layer=4, context_length=96, sliding_window_type=2, sliding_window_size=24)
+    assert [b.max_sequence_len for b in cache.blocks] == [24, 96, 24, 96]
+    ks = []
+    for step_len in (20, 10, 1, 1):
+        k = O.bf16_round(rng.standard_normal((1, 2, step_len, 128)).astype(np.float32))
+        ks.append(k)
+        for block in cache.blocks:
+            block.append(device, Tensor.from_slice(device, k.shape, k), Tensor.from_slice(device, k.shape, k))
+    allk = np.concatenate(ks, 2)
+    assert [b.current_seq_len() for b in cache.blocks] == [24, 32, 24, 32]
+    assert np.array_equal(cache.blocks[0].k().as_slice(), allk[:, :, -24:])
+    assert np.array_equal(cache.blocks[1].k().as_slice(), allk)
+    cache.clear()
+    assert [b.current_seq_len() for b in cache.blocks] == [0, 0, 0, 0]

@@ -1,7 +1,8 @@
-"""Two-GPU checks (skipped when fewer than two GPUs are visible): the peer-memory exchange of split-KV records and the
-KV-chunk decode built on it, one process per GPU, against the oracle on the unsplit sequence.
-No rank is made to fail here: a peer that never publishes is covered by the bounded wait (TIMEOUT status) that
-tests/test_gpu_decode.py exercises on one GPU."""
+"""Two-GPU checks (skipped when fewer than two GPUs are visible): the peer-memory exchange of split-KV records, the
+KV-chunk decode built on it and the library's communicator with the head-sharded output projection, one process per GPU,
+against the oracle on the unsplit problem.  No GPU is made to fault or hang: a peer that never publishes is covered by the
+bounded wait (TIMEOUT status) that tests/test_gpu_decode.py exercises on one GPU, and a rank that never joins a
+communicator is a host-side deadline (last test, one GPU)."""
 import os
 import socket
 
@@ -29,7 +30,8 @@ def _worker(rank, world, port, ret):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
     try:
         import floneum_b200 as fb
-        from floneum_b200 import sharding, workloads as W
+        from floneum_b200 import sharding
+        from oracle import workloads as W
         from oracle import oracle as O
         stream = torch.cuda.Stream()
         with torch.cuda.stream(stream):
@@ -46,16 +48,42 @@ def _worker(rank, world, port, ret):
             worst = 0.0
             full = W.cfg4(Skv=8192)
             want = O.flash_attention(full.q, full.k_dense[0][None], full.v_dense[0][None], full.scale)[:, :, 0]
-            for step in range(3):  # several steps: both slot parities, epochs 1..3
-                cache.decode_partial(q, w.scale, fb.Tensor.from_torch(dev, part))
-                ex.lse_combine(fb.Tensor.from_torch(dev, part), fb.Tensor.from_torch(dev, out))
+            for step in range(4):  # several steps: both slot parities, epochs 1..4; both producers of the records
+                if step % 2 == 0:  # the decode kernel stores its records on every rank itself, then the merge
+                    ex.decode(cache, q, w.scale, fb.Tensor.from_torch(dev, out))
+                else:              # records the caller holds: push, publish, wait and merge in one launch
+                    cache.decode_partial(q, w.scale, fb.Tensor.from_torch(dev, part))
+                    ex.lse_combine(fb.Tensor.from_torch(dev, part), fb.Tensor.from_torch(dev, out))
                 dev.synchronize()
                 worst = max(worst, float(np.abs(out.cpu().numpy() - want).max()))
-            ex.close()
-        t = torch.tensor([worst], dtype=torch.float64, device=f"cuda:{rank}")
+                out.zero_()
+            ex.close()  # collective: unmap, barrier, free
+            # the library's communicator: all-reduce of a known tensor, then the head-sharded output projection
+            comm = sharding.Communicator(dev, rank, world, timeout_ms=60000)
+            t = torch.full((1000,), float(rank + 1), dtype=torch.float32, device=f"cuda:{rank}")
+            comm.all_reduce_sum(fb.Tensor.from_torch(dev, t))
+            dev.synchronize()
+            assert float(t[0]) == world * (world + 1) / 2 and float(t[-1]) == world * (world + 1) / 2
+            rng = np.random.default_rng(3)
+            Bp, Hq_all, S, Dh, N = 1, 8, 256, 128, 256
+            attn = W.bf16_round(rng.standard_normal((Bp, Hq_all, S, Dh)).astype(np.float32))
+            wt = W.bf16_round((rng.standard_normal((N, Hq_all * Dh)) / 32).astype(np.float32))
+            bias = rng.standard_normal(N).astype(np.float32)
+            hq = Hq_all // world
+            a_shard = np.ascontiguousarray(attn[:, rank * hq:(rank + 1) * hq])
+            w_shard = np.ascontiguousarray(wt[:, rank * hq * Dh:(rank + 1) * hq * Dh])
+            o = torch.empty((Bp, S, N), dtype=torch.float32, device=f"cuda:{rank}")
+            comm.out_proj(fb.Tensor.from_slice(dev, a_shard.shape, a_shard, 1), fb.Tensor.from_slice(dev, w_shard.shape, w_shard, 1),
+                          fb.Tensor.from_slice(dev, bias.shape, bias), fb.Tensor.from_torch(dev, o))
+            dev.synchronize()
+            comm.poll()
+            worst_proj = float(np.abs(o.cpu().numpy() - O.out_proj(attn, wt, bias)).max())
+            comm.close()
+        t = torch.tensor([worst, worst_proj], dtype=torch.float64, device=f"cuda:{rank}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if rank == 0:
-            ret["err"] = float(t.item())
+            ret["err"] = float(t[0].item())
+            ret["err_proj"] = float(t[1].item())
     finally:
         dist.destroy_process_group()
 
@@ -69,3 +97,5 @@ def test_kv_chunk_decode_over_peer_exchange_two_gpus():
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     assert ret["err"] <= 2e-3, dict(ret)
+    assert ret["err_proj"] <= 4e-4, dict(ret)
+

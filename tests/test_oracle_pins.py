@@ -171,6 +171,8 @@ def test_split_kv_partials_combine_to_full():
     empty = np.zeros_like(parts[:1])
     empty[..., 0] = NEG
     assert np.array_equal(O.lse_combine(np.concatenate([parts, empty])), O.lse_combine(parts))
+    # a row whose parts are all empty attends to nothing: zeros, not 0 / 0
+    assert np.array_equal(O.lse_combine(np.concatenate([empty, empty])), np.zeros_like(O.lse_combine(parts)))
 
 
 def test_bf16_rounding_helper():

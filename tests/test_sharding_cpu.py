@@ -67,11 +67,18 @@ def _worker(rank, world, port, ret):
         part_o = O.out_proj(attn_full[:, q0:q1], np.ascontiguousarray(w[:, c0:c1]), bias if rank == 0 else None)
         summed = sharding.all_reduce_sum(torch.from_numpy(part_o)).numpy()
         ok_proj = float(np.abs(summed - O.out_proj(attn_full, w, bias)).max())
+        # (4) the library communicator's rendezvous: rank 0 makes the 128-byte id, every rank ends up with the same bytes;
+        # without a GPU the initialisation itself must refuse with a status code, not crash or fall back
+        box = [sharding.Communicator.make_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ids = [None] * world
+        dist.all_gather_object(ids, box[0])
+        same_id = float(len(box[0]) == 128 and all(i == ids[0] for i in ids))
         # max over ranks, as the benchmark does for its timings
-        t = torch.tensor([ok_chunks, ok_heads, ok_proj], dtype=torch.float64)
+        t = torch.tensor([ok_chunks, ok_heads, ok_proj, 1.0 - same_id], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if rank == 0:
-            ret["chunks"], ret["heads"], ret["proj"] = float(t[0]), float(t[1]), float(t[2])
+            ret["chunks"], ret["heads"], ret["proj"], ret["id_mismatch"] = float(t[0]), float(t[1]), float(t[2]), float(t[3])
     finally:
         dist.destroy_process_group()
 
@@ -85,3 +92,35 @@ def test_kv_chunk_allgather_and_head_shards_world2():
     assert ret["chunks"] < 2e-6, ret
     assert ret["heads"] == 0.0, ret
     assert ret["proj"] < 1e-4, ret  # f32 sums of 256 terms of size ~1 in two different orders
+    assert ret["id_mismatch"] == 0.0, ret
+
+
+def test_llama_cache_layer_rule():
+    """LlamaCache::new (models/kalosm-llama/src/raw/cache.rs:23-46): with sliding_window_type t and size w, layer i keeps w
+    tokens unless (i + 1) % t == 0; without both settings every layer keeps the context length.  No device is touched
+    until a layer's first append."""
+    from floneum_b200 import LlamaCache
+    assert [b.max_sequence_len for b in LlamaCache(6, 8192, 3, 512).blocks] == [512, 512, 8192, 512, 512, 8192]
+    assert [b.max_sequence_len for b in LlamaCache(4, 4096).blocks] == [4096] * 4
+    assert [b.max_sequence_len for b in LlamaCache(3, 4096, sliding_window_type=2).blocks] == [4096] * 3  # size missing: no window
+    assert [b.max_sequence_len for b in LlamaCache(3, 4096, 1, 128).blocks] == [4096] * 3             # every layer is global
+    c = LlamaCache.new(2, 100, 2, 10)
+    assert c.start_time == 0 and c.tokens == [] and all(b.concat_dim == 2 and b.current_seq_len() == 0 for b in c.blocks)
+    c.clear()
+
+
+def test_communicator_needs_a_device_and_checks_arguments():
+    import ctypes
+    import torch
+    from floneum_b200 import _lib
+    L = _lib.load()
+    h = ctypes.c_void_p()
+    assert L.fusor_cuda_comm_init(None, b"x" * 128, 0, 1, 1000, ctypes.byref(h)) == _lib.INVALID_ARGUMENT
+    assert L.fusor_cuda_comm_unique_id(None) == _lib.INVALID_ARGUMENT
+    assert L.fusor_cuda_comm_poll(None) == _lib.INVALID_ARGUMENT
+    assert L.fusor_cuda_comm_destroy(None) == _lib.OK
+    assert L.fusor_cuda_exchange_disconnect(None) == _lib.OK
+    if not torch.cuda.is_available():
+        from floneum_b200 import Device, FusorCudaError
+        with pytest.raises(FusorCudaError):
+            Device.gpu(0)  # no context, hence no communicator: there is no CPU path behind the C ABI
