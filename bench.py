@@ -457,7 +457,7 @@ def gpu_arm(args, rank, world, local_rank):
         def step_main(i):
             c = caches[i % copies]
             if collective:
-                exchange.decode(c, tq, w.scale, tout3)  # split-KV kernel pushing its records to every rank, then the merge
+                exchange.decode(c, tq, w.scale, tout3)  # split-KV kernel, then merge + store on every rank + wait + merge
             else:
                 c.decode(tq, w.scale, to)
 
@@ -501,7 +501,7 @@ def gpu_arm(args, rank, world, local_rank):
 
         sampler.start()
         t_busy0 = time.time()
-        ms, ms_mine, per_step, launches, graphed = measure(step_main, 2 if collective else 1)
+        ms, ms_mine, per_step, launches, graphed = measure(step_main, 2)
         clocks = sampler.stop(t_busy0, time.time())
         res = (out3 if collective else out).float().cpu().numpy().copy()
         bytes_rank = kv_bytes_rank + B * (q1 - q0) * D * 6 + 4 * float(np.sum((w.kv_len + 15) // 16))
@@ -519,13 +519,13 @@ def gpu_arm(args, rank, world, local_rank):
         if tag:
             r["config"]["workload"] += tag
         if collective and with_variants:
-            loc_ms, _, _, _, _ = measure(step_local, 1)
+            loc_ms, _, _, _, _ = measure(step_local, 2)
             r["collective"] = {"local_chunk_only_ms": loc_ms, "step_ms": ms, "share_of_step": max(0.0, 1.0 - loc_ms / ms),
-                               "what": "step = split-KV kernel (records pushed to every rank by its last CTAs) + merge kernel that "
-                                       "waits for all ranks; local_chunk_only = the same split-KV kernel writing its records locally"}
+                               "what": "step = split-KV kernel + one kernel that merges the rank's records, stores them on every rank, "
+                                       "waits for all ranks and merges; local_chunk_only = split-KV kernel + local merge, no exchange"}
             n_ms, _, _, _, _ = measure(step_nccl, 3)
             r["nccl_gather"] = {"value": bytes_all / (n_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": n_ms,
-                                "what": "decode_partial + NCCL all_gather_into_tensor + lse_combine (three launches)"}
+                                "what": "decode_partial (two launches) + NCCL all_gather_into_tensor + lse_combine"}
         # e2e: host q up, result down, through the C ABI
         if not args.quick:
             qh = torch.from_numpy(np.ascontiguousarray(qn, dtype=np.float32)).pin_memory()
@@ -590,8 +590,11 @@ def gpu_arm(args, rank, world, local_rank):
     def load_cfg4():
         """(this rank's chunk, the whole sequence on rank 0 for the parity check)"""
         skv = 16384 if args.small else 131072
-        full = W.cfg4(Skv=skv) if (rank == 0 or world == 1 or fake_world) else None
-        mine = full if (world == 1 and not fake_world) else W.cfg4(Skv=skv, rank=rank, world=world, keep_dense=False)
+        if fake_world:  # one rank's chunk alone on one GPU: it is checked against the attention over that chunk
+            mine = W.cfg4(Skv=skv, rank=0, world=fake_world)
+            return mine, mine
+        full = W.cfg4(Skv=skv) if (rank == 0 or world == 1) else None
+        mine = full if world == 1 else W.cfg4(Skv=skv, rank=rank, world=world, keep_dense=False)
         return mine, full
 
     # ======================================================================= the neighbours of the path

@@ -12,9 +12,12 @@
 // round-robin, compute S = Q K^T and O += P V with warp-level tensor-core MMAs
 // (m16n8k16, the g query heads padded to the 16-row tile), keep an online-softmax state
 // per warp, and merge their states at the end of each segment into one partial
-// (m, l, O) record.  The CTA that completes the last record of a sequence-head (a device
-// counter per sequence-head) merges that head's records by log-sum-exp (the (m, d) rule of
-// fusor-ml/core/src/composite/softmax.rs:59-82) and writes the result: one launch per step.
+// (m, l, O) record (a CTA that holds every page of a sequence-head writes the result itself).
+// decode_combine_kernel merges the records of a sequence-head by log-sum-exp (the (m, d) rule
+// of fusor-ml/core/src/composite/softmax.rs:59-82); it finds each head's records with the same
+// deal functions.  (Merging inside the first kernel, by the CTA that completes a head's last
+// record, was measured slower: 206 against 196 us on the B64 configuration and 140 against
+// 94 us on the 131072-key one, whose 74 records per head then meet in one CTA at the kernel's end.)
 //
 // Replaces the Sq == 1 regime of the reference's fused kernel
 // (fusor-ml/core/src/composite/flash_attention.rs:147-331), which walks all keys serially
@@ -98,6 +101,19 @@ __host__ __device__ inline bool decode_next_segment(const int* kv_len, int B, in
     return false;
 }
 
+// Result of the merged records of a (sequence, query head):
+//   mode 0: out[b][h][0][:] = O / L                         (dtype f32, bf16 or f16, strided)
+//   mode 1: out[b][h][:] = { M ln2, L, O }                  (f32, packed [B][Hq][D+2]; merged across GPUs later)
+//   mode 2: nothing is written by the split-KV kernel; the merge kernel of the exchange produces the mode-1 record and
+//           stores it on every rank
+struct DecodeOutput {
+    void* out;
+    int out_dtype;
+    long long o_sb, o_sh;
+    int Hq;
+    int mode;
+};
+
 struct DecodeParams {
     const void* q;
     int q_dtype;           // 0 f32, 1 bf16, 2 f16
@@ -109,37 +125,47 @@ struct DecodeParams {
     int B;
     float* part_o;             // [slots][DEC_GP][D], slots >= B * Hkv + grid
     float* part_ml;            // [slots][DEC_GP][2]  (m in log2 units, l)
-    unsigned int* seq_done;    // [B * Hkv] finished records per sequence-head, zero between launches
     int Hkv, g;
     float scale_log2;
     int ring;
     int* err;
-    // result of the merged records:
-    //   mode 0: out[b][h][0][:] = O / L                         (dtype f32 or bf16, strided)
-    //   mode 1: out[b][h][:] = { M ln2, L, O }                  (f32, packed [B][Hq][D+2]; merged across GPUs later)
-    //   mode 2: the mode-1 record, stored into this rank's slot on every rank of `push` (and published once all
-    //           sequence-heads of this rank are in place)
-    void* out;
-    int out_dtype;
-    long long o_sb, o_sh;
-    int Hq;
-    int mode;
-    PeerTargets push;
+    // where a CTA that holds a whole sequence-head writes its result (every other head is merged from its records by
+    // decode_combine_kernel or decode_combine_exchange_kernel, which take the same description):
+    DecodeOutput res;
 };
+
+// Result of one (sequence-head, query row, column group) after all its records have been merged (modes 0 and 1).
+__device__ __forceinline__ void decode_emit(const DecodeOutput& R, int D, int g, int b, int hk, int rr, int dg, float M, float L, float4 acc) {
+    const int h = hk * g + rr, d = dg * 4;
+    if (R.mode == 0) {
+        const long long idx = (long long)b * R.o_sb + (long long)h * R.o_sh + d;
+        const float inv = 1.0f / L;
+        if (R.out_dtype == 0) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(R.out) + idx) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        } else {
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(R.out) + idx) =
+                make_uint2(pack_16(R.out_dtype, acc.x * inv, acc.y * inv), pack_16(R.out_dtype, acc.z * inv, acc.w * inv));
+        }
+    } else {
+        float* rec = reinterpret_cast<float*>(R.out) + ((long long)b * R.Hq + h) * (D + 2);
+        rec[2 + d] = acc.x; rec[3 + d] = acc.y; rec[4 + d] = acc.z; rec[5 + d] = acc.w;
+        if (dg == 0) { rec[0] = M * 0.6931471805599453f; rec[1] = L; }
+    }
+}
 
 template <int D>
 struct DecodeSmem {
     static constexpr int PAGE_BYTES = DEC_PT * D * 2;
     static constexpr int MERGE_FLOATS = DEC_NW * DEC_GP * (D + 2);
     static size_t bytes(int ring) {
-        return 1024 + (size_t)ring * 2 * PAGE_BYTES + MERGE_FLOATS * 4 + (size_t)ring * 16 + 64;
+        return 1024 + (size_t)ring * 2 * PAGE_BYTES + MERGE_FLOATS * 4 + (size_t)ring * 16 + 128;
     }
 };
 
 template <int D>
 __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK,
                                                                      const __grid_constant__ CUtensorMap tmV,
-                                                                     const DecodeParams P) {
+                                                                     const __grid_constant__ DecodeParams P) {
     constexpr int PAGE_BYTES = DecodeSmem<D>::PAGE_BYTES;
     constexpr int HALF_BYTES = DEC_PT * 128;  // one 64-column half of a page tile
     extern __shared__ uint8_t dec_smem_raw[];
@@ -152,8 +178,12 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
     uint64_t* full = reinterpret_cast<uint64_t*>(merge_ml + DEC_NW * DEC_GP * 2);
     uint64_t* empty = full + R;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + R);
-    volatile int* last_flag = abort_flag + 1;
     int* walk0 = const_cast<int*>(abort_flag) + 2;  // [3]: T, first sequence, pages before it
+    // the consumers' walk and current segment live in shared memory (thread 0 advances them between segments), so that
+    // they cost the page loop no registers
+    volatile int* have_seg = walk0 + 3;
+    DecodeWalk* walk_s = reinterpret_cast<DecodeWalk*>(walk0 + 4);          // 5 ints
+    DecodeSegment* seg_s = reinterpret_cast<DecodeSegment*>(walk0 + 9);     // 9 ints
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -208,11 +238,11 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
     }
     __syncthreads();
     const int T = walk0[0];
-    DecodeWalk W;
-    decode_walk_init(W, T, (int)gridDim.x, (int)blockIdx.x, walk0[1], walk0[2]);
-    DecodeSegment S;
 
     if (warp == DEC_NW) {
+        DecodeWalk W;
+        decode_walk_init(W, T, (int)gridDim.x, (int)blockIdx.x, walk0[1], walk0[2]);
+        DecodeSegment S;
         // ------------------------------------------------------------------ producer warp
         // Lane 0 owns the ring bookkeeping; the 2*(D/64) TMA copies of a page (K and V, 64 columns each) are
         // issued by as many lanes in one warp instruction.
@@ -268,39 +298,20 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
         const uint32_t ksm_u = smem_u32(ksm), vsm_u = smem_u32(vsm);
         constexpr int NC = DEC_NW * 32;   // consumer threads
         constexpr int DG = D / 4;         // float4 column groups of a row
-        // mode 2: the epoch this step publishes (the counter only moves in the merge kernel that follows)
-        const unsigned long long e_push = P.mode == 2 ? *reinterpret_cast<volatile unsigned long long*>(P.push.epoch) + 1 : 0ull;
 
-        // Result of one (sequence-head, query row, column group) after all its records have been merged.
-        auto emit = [&](int b, int hk, int rr, int dg, float M, float L, float4 acc) {
-            const int h = hk * P.g + rr, d = dg * 4;
-            if (P.mode == 0) {
-                const long long idx = (long long)b * P.o_sb + (long long)h * P.o_sh + d;
-                const float inv = 1.0f / L;
-                if (P.out_dtype == 0) {
-                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + idx) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-                } else {
-                    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(P.out) + idx) =
-                        make_uint2(pack_16(P.out_dtype, acc.x * inv, acc.y * inv), pack_16(P.out_dtype, acc.z * inv, acc.w * inv));
-                }
-                return;
-            }
-            const long long off = ((long long)b * P.Hq + h) * (D + 2);
-            const float m_ln = M * 0.6931471805599453f;
-            if (P.mode == 1) {
-                float* rec = reinterpret_cast<float*>(P.out) + off;
-                rec[2 + d] = acc.x; rec[3 + d] = acc.y; rec[4 + d] = acc.z; rec[5 + d] = acc.w;
-                if (dg == 0) { rec[0] = m_ln; rec[1] = L; }
-            } else {
-                for (int pr = 0; pr < P.push.world; ++pr) {
-                    float* rec = peer_slot(P.push, pr, e_push) + off;
-                    rec[2 + d] = acc.x; rec[3 + d] = acc.y; rec[4 + d] = acc.z; rec[5 + d] = acc.w;
-                    if (dg == 0) { rec[0] = m_ln; rec[1] = L; }
-                }
-            }
-        };
-
-        while (decode_next_segment(P.kv_len, P.B, P.Hkv, T, (int)gridDim.x, (int)blockIdx.x, W, S)) {
+        if (tid == 0) {
+            DecodeWalk w0;
+            decode_walk_init(w0, T, (int)gridDim.x, (int)blockIdx.x, walk0[1], walk0[2]);
+            DecodeSegment s0;
+            *have_seg = decode_next_segment(P.kv_len, P.B, P.Hkv, T, (int)gridDim.x, (int)blockIdx.x, w0, s0) ? 1 : 0;
+            *walk_s = w0;
+            *seg_s = s0;
+        }
+        named_bar_sync(1, NC);
+        while (*have_seg) {
+            // what the page loop needs of the segment; the rest is read again from shared memory afterwards
+            const int seg_page_begin = seg_s->page_begin, seg_off = seg_s->cta_page_off, seg_kv_len = seg_s->kv_len;
+            const int n_pages = seg_s->page_end - seg_page_begin;
             // Q fragments: rows >= g are zero.
             uint32_t qa[D / 16][2];
 #pragma unroll
@@ -309,7 +320,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
                 qa[ks][1] = 0;
             }
             if (row_valid) {
-                const long long qoff = (long long)S.b * P.q_sb + (long long)(S.hk * P.g + r) * P.q_sh;
+                const long long qoff = (long long)seg_s->b * P.q_sb + (long long)(seg_s->hk * P.g + r) * P.q_sh;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const int d0 = ks * 16 + cq;
@@ -328,12 +339,11 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
 #pragma unroll
             for (int nd = 0; nd < D / 8; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.0f;
 
-            const int n_pages = S.page_end - S.page_begin;
             // Every consumer warp waits for every page of the CTA's stream in order and releases the slot once it
             // has seen it (the owner: once it has used it).  The producer refills a slot only after all DEC_NW
             // releases, so no warp can meet a slot's barrier two phases later, which a parity wait cannot tell
             // from "ready".
-            for (int i = S.cta_page_off; i < S.cta_page_off + n_pages; ++i) {
+            for (int i = seg_off; i < seg_off + n_pages; ++i) {
                 if (aborted) break;
                 const int slot = cslot;
                 const bool got = mbar_wait(full + slot, cphase, abort_flag, P.err, 2 + (i % DEC_NW == warp ? 1 : 0));
@@ -349,7 +359,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
                     if (lane == 0) mbar_arrive(empty + slot);
                     continue;
                 }
-                const int tok0 = (S.page_begin + (i - S.cta_page_off)) * DEC_PT;
+                const int tok0 = (seg_page_begin + (i - seg_off)) * DEC_PT;
                 const uint32_t kb = ksm_u + slot * PAGE_BYTES, vb = vsm_u + slot * PAGE_BYTES;
 
                 // ---- S = Q K^T for 16 tokens (two 8-token tiles)
@@ -379,7 +389,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int tok = tok0 + nt * 8 + cq + e;
-                        t[nt * 2 + e] = tok < S.kv_len ? s[nt][e] * P.scale_log2 : -INFINITY;
+                        t[nt * 2 + e] = tok < seg_kv_len ? s[nt][e] * P.scale_log2 : -INFINITY;
                     }
                 float tmax = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3]));
                 tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
@@ -434,7 +444,9 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
                 }
             }
             named_bar_sync(1, NC);
-            const bool whole = S.n_rec == 1;  // this CTA saw every page of the sequence-head: no record leaves the CTA
+            const int sb = seg_s->b, shk = seg_s->hk, my_slot = seg_s->slot;
+            // a CTA that saw every page of the sequence-head writes the result itself: no record leaves the CTA
+            const bool whole = seg_s->n_rec == 1 && P.res.mode != 2;
             for (int item = tid; item < P.g * DG; item += NC) {
                 const int rr = item / DG, dg = item - rr * DG;
                 float M = -INFINITY;
@@ -452,68 +464,183 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_CTAS) decode_splitkv_kernel(c
                 }
                 if (aborted) continue;
                 if (whole) {
-                    emit(S.b, S.hk, rr, dg, M, L, acc);
+                    decode_emit(P.res, D, P.g, sb, shk, rr, dg, M, L, acc);
                 } else {
-                    *reinterpret_cast<float4*>(P.part_o + ((long long)S.slot * DEC_GP + rr) * D + dg * 4) = acc;
-                    if (dg == 0) *reinterpret_cast<float2*>(P.part_ml + ((long long)S.slot * DEC_GP + rr) * 2) = make_float2(M, L);
+                    *reinterpret_cast<float4*>(P.part_o + ((long long)my_slot * DEC_GP + rr) * D + dg * 4) = acc;
+                    if (dg == 0) *reinterpret_cast<float2*>(P.part_ml + ((long long)my_slot * DEC_GP + rr) * 2) = make_float2(M, L);
                 }
             }
-            bool finished = whole;  // true in the CTA that completes the sequence-head
-            if (!whole) {
-                // The CTA that adds the last record of a sequence-head merges them all.  Every thread fences its own
-                // record stores before the barrier; the counter is bumped after it, and the merging CTA reads the
-                // records of the other CTAs from L2.  The counter is back at zero when the kernel ends.
-                __threadfence();
-                named_bar_sync(1, NC);
-                if (tid == 0) {
-                    const int seq = S.b * P.Hkv + S.hk;
-                    const unsigned prev = atomicAdd(P.seq_done + seq, 1u);
-                    const int last = prev == (unsigned)(S.n_rec - 1);
-                    if (last) {
-                        P.seq_done[seq] = 0;
-                        __threadfence();
-                    }
-                    *last_flag = last;
-                }
-                named_bar_sync(1, NC);
-                finished = *last_flag != 0;
-                if (finished) {
-                    for (int item = tid; item < P.g * DG; item += NC) {
-                        const int rr = item / DG, dg = item - rr * DG;
-                        float M = -INFINITY, L = 0.0f;
-                        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll 4
-                        for (int rec = 0; rec < S.n_rec; ++rec) {
-                            const long long sl = S.first_slot + rec;
-                            const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml + (sl * DEC_GP + rr) * 2));
-                            const float4 ow = __ldcg(reinterpret_cast<const float4*>(P.part_o + (sl * DEC_GP + rr) * D + dg * 4));
-                            if (ml.x == -INFINITY) continue;
-                            const float Mn = fmaxf(M, ml.x);
-                            const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
-                            L = L * a0 + ml.y * a1;
-                            acc.x = acc.x * a0 + ow.x * a1;
-                            acc.y = acc.y * a0 + ow.y * a1;
-                            acc.z = acc.z * a0 + ow.z * a1;
-                            acc.w = acc.w * a0 + ow.w * a1;
-                            M = Mn;
-                        }
-                        if (!aborted) emit(S.b, S.hk, rr, dg, M, L, acc);
-                    }
-                }
+            named_bar_sync(1, NC);  // everybody is done with the segment record and the merge area
+            if (tid == 0) {
+                DecodeWalk w1 = *walk_s;
+                DecodeSegment s1;
+                *have_seg = decode_next_segment(P.kv_len, P.B, P.Hkv, T, (int)gridDim.x, (int)blockIdx.x, w1, s1) ? 1 : 0;
+                *walk_s = w1;
+                *seg_s = s1;
             }
-            if (P.mode == 2 && finished) {
-                // the records of this sequence-head are on their way to every rank; the CTA that completes the rank's
-                // last sequence-head publishes the epoch
-                __threadfence_system();
-                named_bar_sync(1, NC);
-                if (tid == 0 && atomicAdd(P.push.done, 1u) == (unsigned)(P.B * P.Hkv) - 1) {
-                    *P.push.done = 0;
-                    peer_publish(P.push, e_push);
-                }
-            }
-            named_bar_sync(1, NC);  // the merge area is rewritten by the next segment
+            named_bar_sync(1, NC);
         }
     }
+}
+
+// ---------------------------------------------------------------------------------- merge of a head's records
+struct CombineParams {
+    const float* part_o;
+    const float* part_ml;
+    const int* kv_len;   // [B]
+    int B, Hkv, g, D;
+    int grid;            // CTAs of the split-KV launch whose records these are
+    DecodeOutput res;
+};
+
+constexpr int DEC_CL = 16;  // most record lanes a block may have (the host picks 2, 8 or 16 by the records per kv head)
+
+// Where the records of (b, hk) are: the deal of decode_splitkv_kernel, recomputed by the block (the lengths are a few
+// hundred bytes in L2).  Every thread of the block calls it; `red` is 66 ints of shared memory.
+__device__ __forceinline__ void decode_head_records(const int* kv_len, int B, int Hkv, int grid, int b, int hk, int* red, int& first_slot,
+                                                    int& n_rec) {
+    int before = 0, total = 0;
+    for (int i = threadIdx.x; i < B; i += blockDim.x) {
+        const int pg = (kv_len[i] + DEC_PT - 1) / DEC_PT;
+        total += pg;
+        if (i < b) before += pg;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        before += __shfl_xor_sync(0xffffffffu, before, o);
+        total += __shfl_xor_sync(0xffffffffu, total, o);
+    }
+    const int warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();  // `red` may still be read from the previous call
+    if ((threadIdx.x & 31) == 0) {
+        red[2 * warp] = before;
+        red[2 * warp + 1] = total;
+    }
+    __syncthreads();
+    before = 0;
+    total = 0;
+    for (int w = 0; w < nw; ++w) {
+        before += red[2 * w];
+        total += red[2 * w + 1];
+    }
+    const int T = total * Hkv;
+    const int pages = (kv_len[b] + DEC_PT - 1) / DEC_PT;
+    const int p0 = Hkv * before + hk * pages;
+    const int c_first = decode_page_owner(T, grid, p0), c_last = decode_page_owner(T, grid, p0 + pages - 1);
+    first_slot = b * Hkv + hk + c_first;
+    n_rec = c_last - c_first + 1;
+}
+
+// Merge of the records [s0, s0 + n) of query row rr by a block of (D / 4 column groups) x (record lanes) threads: lane r
+// merges records r, r + lanes, ... with an online rescale (independent loads, no pass over the maxima first); the lanes'
+// states meet in shared memory and the threads of lane 0 fold them.  A long sequence split over hundreds of CTAs (the
+// 128 K-token configuration: ~74 records per kv head) is merged by 16 lanes in parallel.  Returns true in the threads
+// of lane 0, which then hold (M, L, acc) of their column group dg.
+__device__ __forceinline__ bool decode_merge_rows(const float* part_o, const float* part_ml, int D, int s0, int n, int rr, float4 (*sh_acc)[64],
+                                                  float2 (*sh_ml)[64], int& dg, float& M, float& L, float4& acc) {
+    const int groups = D >> 2;  // <= 64
+    dg = threadIdx.x % groups;
+    const int lane = threadIdx.x / groups, lanes = blockDim.x / groups;
+    M = -INFINITY;
+    L = 0.0f;
+    acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 2
+    for (int s = s0 + lane; s < s0 + n; s += lanes) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((long long)s * DEC_GP + rr) * 2);
+        const float4 o = *reinterpret_cast<const float4*>(part_o + ((long long)s * DEC_GP + rr) * D + dg * 4);
+        if (ml.x == -INFINITY) continue;
+        const float Mn = fmaxf(M, ml.x);
+        const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
+        L = L * a0 + ml.y * a1;
+        acc.x = acc.x * a0 + o.x * a1;
+        acc.y = acc.y * a0 + o.y * a1;
+        acc.z = acc.z * a0 + o.z * a1;
+        acc.w = acc.w * a0 + o.w * a1;
+        M = Mn;
+    }
+    sh_acc[lane][dg] = acc;
+    sh_ml[lane][dg] = make_float2(M, L);
+    __syncthreads();
+    if (lane != 0) return false;
+    for (int r = 1; r < lanes; ++r) {
+        const float2 ml = sh_ml[r][dg];
+        if (ml.x == -INFINITY) continue;
+        const float4 o = sh_acc[r][dg];
+        const float Mn = fmaxf(M, ml.x);
+        const float a0 = fast_exp2(M - Mn), a1 = fast_exp2(ml.x - Mn);
+        L = L * a0 + ml.y * a1;
+        acc.x = acc.x * a0 + o.x * a1;
+        acc.y = acc.y * a0 + o.y * a1;
+        acc.z = acc.z * a0 + o.z * a1;
+        acc.w = acc.w * a0 + o.w * a1;
+        M = Mn;
+    }
+    return true;
+}
+
+// One block per (query head, sequence).  A head whose pages all went to one CTA was written by that CTA already.
+__global__ void decode_combine_kernel(const CombineParams P) {
+    __shared__ float4 sh_acc[DEC_CL][64];
+    __shared__ float2 sh_ml[DEC_CL][64];
+    __shared__ int red[66];
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int hk = h / P.g, rr = h % P.g;
+    int first_slot, n_rec;
+    decode_head_records(P.kv_len, P.B, P.Hkv, P.grid, b, hk, red, first_slot, n_rec);
+    if (n_rec == 1) return;
+    int dg;
+    float M, L;
+    float4 acc;
+    if (decode_merge_rows(P.part_o, P.part_ml, P.D, first_slot, n_rec, rr, sh_acc, sh_ml, dg, M, L, acc))
+        decode_emit(P.res, P.D, P.g, b, hk, rr, dg, M, L, acc);
+}
+
+// The same merge for the KV-chunk decode over several GPUs, followed in the same launch by the exchange: every block
+// merges the records of its (query head, sequence) rows and stores the result {M ln2, L, O} straight into this rank's slot
+// on every rank; the last block to finish publishes the epoch; then every block waits (bounded) for all ranks' epochs and
+// merges its rows over the ranks.  The grid is at most one block per SM, so every block is resident: a block only waits
+// for the peers after all of this rank's blocks have stored their share, and no block waits on one that has not started.
+struct CombineExchangeParams {
+    CombineParams C;   // res.mode = 2: nothing but the exchange consumes the merged records
+    PeerTargets T;
+    PeerMergeParams M;
+};
+
+__global__ void decode_combine_exchange_kernel(const CombineExchangeParams P) {
+    __shared__ float4 sh_acc[DEC_CL][64];
+    __shared__ float2 sh_ml[DEC_CL][64];
+    __shared__ int red[66];
+    const unsigned long long e = *reinterpret_cast<volatile unsigned long long*>(P.T.epoch) + 1;
+    const int Hq = P.C.Hkv * P.C.g, D = P.C.D;
+    const long long n_rows = (long long)P.C.B * Hq;
+    for (long long row = blockIdx.x; row < n_rows; row += gridDim.x) {
+        const int b = (int)(row / Hq), h = (int)(row % Hq);
+        const int hk = h / P.C.g, rr = h % P.C.g;
+        int first_slot, n_rec;
+        decode_head_records(P.C.kv_len, P.C.B, P.C.Hkv, P.C.grid, b, hk, red, first_slot, n_rec);
+        int dg;
+        float M, L;
+        float4 acc;
+        if (decode_merge_rows(P.C.part_o, P.C.part_ml, D, first_slot, n_rec, rr, sh_acc, sh_ml, dg, M, L, acc)) {
+            const long long off = row * (D + 2);
+            const int d = dg * 4;
+            for (int pr = 0; pr < P.T.world; ++pr) {
+                float* rec = peer_slot(P.T, pr, e) + off;
+                rec[2 + d] = acc.x; rec[3 + d] = acc.y; rec[4 + d] = acc.z; rec[5 + d] = acc.w;
+                if (dg == 0) { rec[0] = M * 0.6931471805599453f; rec[1] = L; }
+            }
+        }
+        __syncthreads();  // the shared staging is reused by the next row
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(P.T.done, 1u) == gridDim.x - 1) {
+        *P.T.done = 0;
+        peer_publish(P.T, e);
+    }
+    if (peer_wait_all(P.M.flags, P.M.world, e, P.M.err, P.M.wait_limit_cycles))
+        for (long long row = blockIdx.x; row < n_rows; row += gridDim.x) peer_merge_row(P.M.slots, P.M.slot_floats, P.M.world, e, row, D, P.M.out);
+    peer_step_done(P.M.epoch, P.M.done, e);
 }
 
 // parts [n_parts][n_rows][D+2] (m in natural-log units) -> out [n_rows][D]; a row whose parts are all empty gives zeros

@@ -25,6 +25,7 @@
 #include "general_attention.cuh"
 #include "prefill_sm100.cuh"
 #include "prefill2_sm100.cuh"
+#include "prefill3_sm100.cuh"
 #include "oproj_sm100.cuh"
 #include "peer_exchange.cuh"
 #include "rope_append.cuh"
@@ -53,6 +54,8 @@ struct fusor_cuda_ctx {
     unsigned flag_counter = 0;
     // copy streams of the _host entry points (host -> device, device -> host), created on first use
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+    int max_pairs = 0;      // CTA pairs of prefill3_sm100_kernel that can be resident at once
+    int prefill_kernel = 0; // DEVELOPMENT SWITCH (to be removed): 0 = automatic, 2 = two-tile kernel, 3 = CTA-pair kernel
 };
 
 static thread_local std::string g_last_error;
@@ -152,6 +155,23 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
     // opt in to large dynamic shared memory once per context
     cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
     cudaFuncSetAttribute(prefill2_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM_BYTES);
+    cudaFuncSetAttribute(prefill3_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P3_SMEM_BYTES);
+    {
+        // how many CTA pairs fit at once (a pair needs two SMs of one GPC): the persistent grid is sized to that
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (unsigned)prop.multiProcessorCount, 1, 1);
+        cfg.blockDim = dim3(P3_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = P3_SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, prefill3_sm100_kernel, &cfg) == cudaSuccess && n > 0) ctx->max_pairs = n;
+        else { cudaGetLastError(); ctx->max_pairs = prop.multiProcessorCount / 2; }
+    }
+    if (const char* pk = std::getenv("FUSOR_DEV_PREFILL_KERNEL")) ctx->prefill_kernel = std::atoi(pk);
     cudaFuncSetAttribute(oproj_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)OP_SMEM_BYTES);
     cudaFuncSetAttribute(decode_splitkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(decode_splitkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -412,12 +432,13 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     // Two query tiles per CTA with 128-key blocks once a (batch, head) has 256 rows or more; the 64-key kernel with
     // two CTAs per SM below that.
     const bool two_tiles = S.Sq >= P2_ROWS;
-    const int kv_rows = two_tiles ? P2_BN : PF_BN;
+    const bool pairs = two_tiles && ctx->prefill_kernel == 3;
+    const int kv_rows = pairs ? 64 : two_tiles ? P2_BN : PF_BN;
     const bool in_f16 = q->dtype == FUSOR_CUDA_F16;  // f16 tensors need no copy of V: the weights are f16 against V itself
     CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
     TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM, tmap_dtype(q->dtype)));
     TRY(make_tmap_bhsd(ctx, &tmK, k, kv_rows, tmap_dtype(k->dtype)));
-    TRY(make_tmap_bhsd(ctx, &tmV, v, kv_rows, tmap_dtype(v->dtype)));
+    TRY(make_tmap_bhsd(ctx, &tmV, v, pairs ? P3_BN : kv_rows, tmap_dtype(v->dtype)));
     TRY(make_tmap_bhsd(ctx, &tmO, out, two_tiles ? 32 : PF_BM, tmap_dtype(out->dtype)));
     tmV16 = tmV;
     const int* flag = nullptr;
@@ -443,7 +464,7 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
         fusor_cuda_tensor4 v16 = *v;
         v16.data = ctx->v16;
         set_contiguous(&v16);
-        TRY(make_tmap_bhsd(ctx, &tmV16, &v16, kv_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
+        TRY(make_tmap_bhsd(ctx, &tmV16, &v16, pairs ? P3_BN : kv_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
         flag = ctx->d_flags + slot;
     }
     PrefillParams P{};
@@ -462,6 +483,11 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.kmask_mul = 1.0f / scale;
     const long long grid = (long long)P.n_q_tiles * S.Hq * S.B;
     if (grid > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "grid too large");
+    if (pairs) {
+        const unsigned n_pairs = (unsigned)std::min<long long>(grid, ctx->max_pairs);  // persistent: one CTA pair per two SMs
+        prefill3_sm100_kernel<<<2 * n_pairs, P3_THREADS, P3_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
+        return launch_check(ctx, "prefill3_sm100_kernel");
+    }
     if (two_tiles) {
         const unsigned ctas = (unsigned)std::min<long long>(grid, ctx->num_sms);  // persistent: one CTA per SM
         prefill2_sm100_kernel<<<ctas, P2_THREADS, P2_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
@@ -699,7 +725,6 @@ struct fusor_cuda_kvcache {
     int decode_ctas = 0;              // 0 = automatic grid size
     float* part_o = nullptr;          // [max_slots][DEC_GP][D]
     float* part_ml = nullptr;         // [max_slots][DEC_GP][2]
-    unsigned int* seq_done = nullptr; // [max_batch * Hkv], zero between launches
     // dense staging for token-granular eviction, grown on demand
     __nv_bfloat16* shift_buf = nullptr;
     size_t shift_bytes = 0;
@@ -727,7 +752,6 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
     c->max_slots = max_batch * num_kv_heads + c->max_grid;
     bool ok = cudaMalloc(&c->k_pages, pool_bytes) == cudaSuccess && cudaMalloc(&c->v_pages, pool_bytes) == cudaSuccess &&
               cudaMalloc(&c->d_tables, ((size_t)2 * max_batch + (size_t)max_batch * max_pages_per_seq) * 4) == cudaSuccess &&
-              cudaMalloc(&c->seq_done, (size_t)max_batch * num_kv_heads * 4) == cudaSuccess &&
               cudaMalloc(&c->part_o, (size_t)c->max_slots * DEC_GP * head_dim * 4) == cudaSuccess &&
               cudaMalloc(&c->part_ml, (size_t)c->max_slots * DEC_GP * 2 * 4) == cudaSuccess;
     if (ok) {
@@ -738,8 +762,7 @@ extern "C" int32_t fusor_cuda_kvcache_create(fusor_cuda_ctx* ctx, int32_t max_ba
     if (ok) ok = cudaMemsetAsync(c->k_pages, 0, pool_bytes, ctx->stream) == cudaSuccess &&
                  cudaMemsetAsync(c->v_pages, 0, pool_bytes, ctx->stream) == cudaSuccess &&
                  cudaMemsetAsync(c->d_page_table, 0, (size_t)max_batch * max_pages_per_seq * 4, ctx->stream) == cudaSuccess &&
-                 cudaMemsetAsync(c->d_kv_len, 0, (size_t)max_batch * 4, ctx->stream) == cudaSuccess &&
-                 cudaMemsetAsync(c->seq_done, 0, (size_t)max_batch * num_kv_heads * 4, ctx->stream) == cudaSuccess;
+                 cudaMemsetAsync(c->d_kv_len, 0, (size_t)max_batch * 4, ctx->stream) == cudaSuccess;
     if (!ok) {
         cudaError_t e = cudaGetLastError();
         fusor_cuda_kvcache_destroy(c);
@@ -773,7 +796,7 @@ extern "C" int32_t fusor_cuda_kvcache_destroy(fusor_cuda_kvcache* c) {
     if (!c) return FUSOR_CUDA_OK;
     DeviceGuard g(c->ctx->device);
     cudaStreamSynchronize(c->ctx->stream);
-    void* ptrs[] = {c->k_pages, c->v_pages, c->d_tables, c->seq_done, c->part_o, c->part_ml, c->shift_buf};
+    void* ptrs[] = {c->k_pages, c->v_pages, c->d_tables, c->part_o, c->part_ml, c->shift_buf};
     for (void* p : ptrs)
         if (p) cudaFree(p);
 
@@ -1161,13 +1184,17 @@ extern "C" int32_t fusor_cuda_kvcache_set_decode_ctas(fusor_cuda_kvcache* c, int
     return FUSOR_CUDA_OK;
 }
 
+struct fusor_cuda_exchange;
+static void exchange_targets(const fusor_cuda_exchange* ex, PeerTargets* T);
+static void exchange_merge_params(const fusor_cuda_exchange* ex, PeerMergeParams* M, int64_t n_rows, int32_t head_dim, float* out);
+
 // Pages per CTA below which the automatic grid takes fewer CTAs per SM: a CTA's fixed cost (ring fill, per-segment
 // merge, its partial record and the share of the final merge) is spread over at least this many 8 KB page pairs.
 static constexpr long long kDecodeMinPagesPerCta = 24;
 
 static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fusor_cuda_tensor4* q, float scale, void* out,
-                           int out_dtype, long long o_sb, long long o_sh, int mode, const PeerTargets* push = nullptr) {
-    if (!ctx || !c || !q || !q->data || (!out && mode != 2)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
+                           int out_dtype, long long o_sb, long long o_sh, int mode, fusor_cuda_exchange* ex = nullptr) {
+    if (!ctx || !c || !q || !q->data || !out || (mode == 2 && !ex)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
     if (c->ctx != ctx) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "cache belongs to another context");
     if (!dtype_ok(q->dtype)) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "unknown dtype");
     if (c->active_B == 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "the cache is empty");
@@ -1206,15 +1233,36 @@ static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fus
     P.q = q->data; P.q_dtype = q->dtype; P.q_sb = q->stride[0]; P.q_sh = q->stride[1];
     P.page_table = c->d_page_table; P.max_pages = c->max_pages; P.num_pages = c->num_pages;
     P.kv_len = c->d_kv_len; P.B = B;
-    P.part_o = c->part_o; P.part_ml = c->part_ml; P.seq_done = c->seq_done;
+    P.part_o = c->part_o; P.part_ml = c->part_ml;
     P.Hkv = c->Hkv; P.g = g; P.scale_log2 = scale * 1.4426950408889634f; P.ring = ring; P.err = ctx->d_err;
-    P.out = out; P.out_dtype = out_dtype; P.o_sb = o_sb; P.o_sh = o_sh; P.Hq = Hq; P.mode = mode;
-    if (push) P.push = *push;
+    P.res.out = out; P.res.out_dtype = out_dtype; P.res.o_sb = o_sb; P.res.o_sh = o_sh; P.res.Hq = Hq; P.res.mode = mode;
     if (c->D == 128)
         decode_splitkv_kernel<128><<<grid, DEC_THREADS, smem, ctx->stream>>>(c->tmK, c->tmV, P);
     else
         decode_splitkv_kernel<64><<<grid, DEC_THREADS, smem, ctx->stream>>>(c->tmK, c->tmV, P);
-    return launch_check(ctx, "decode_splitkv_kernel");
+    TRY(launch_check(ctx, "decode_splitkv_kernel"));
+    // merge of the records of every (sequence, kv head) that was spread over several CTAs
+    CombineParams C{};
+    C.part_o = c->part_o; C.part_ml = c->part_ml; C.kv_len = c->d_kv_len;
+    C.B = B; C.Hkv = c->Hkv; C.g = g; C.D = c->D; C.grid = grid; C.res = P.res;
+    // record lanes per block: a kv head of a short sequence has one or two records, a 128 K-token sequence ~74
+    long long longest = 0;
+    for (int b = 0; b < B; ++b) longest = std::max<long long>(longest, (c->h_kv_len[b] + DEC_PT - 1) / DEC_PT);
+    const long long per_head = longest * grid / std::max<long long>(1, total) + 2;
+    const int lanes = per_head <= 4 ? 2 : per_head <= 32 ? 8 : DEC_CL;
+    if (mode != 2) {
+        // (the kernel's blocks return at once for heads whose pages all went to one CTA)
+        decode_combine_kernel<<<dim3(Hq, B), (c->D / 4) * lanes, 0, ctx->stream>>>(C);
+        return launch_check(ctx, "decode_combine_kernel");
+    }
+    // KV-chunk decode over several GPUs: merge + exchange in one launch
+    CombineExchangeParams X{};
+    X.C = C;
+    exchange_targets(ex, &X.T);
+    exchange_merge_params(ex, &X.M, (int64_t)B * Hq, c->D, static_cast<float*>(out));
+    const unsigned blocks = (unsigned)std::min<long long>((long long)B * Hq, ctx->num_sms);
+    decode_combine_exchange_kernel<<<blocks, (c->D / 4) * lanes, 0, ctx->stream>>>(X);
+    return launch_check(ctx, "decode_combine_exchange_kernel");
 }
 
 extern "C" int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
@@ -1398,8 +1446,8 @@ extern "C" int32_t fusor_cuda_exchange_lse_combine(fusor_cuda_exchange* ex, cons
     return launch_check(ctx, "peer_push_merge_kernel");
 }
 
-// KV-chunk decode over several GPUs in two launches: the split-KV kernel, whose last CTA per (sequence, kv head)
-// stores that head's merged records on every rank, and the merge of all ranks' records.
+// KV-chunk decode over several GPUs in two launches: the split-KV kernel over this rank's chunk, then one kernel that
+// merges this rank's records per query head, stores them on every rank, publishes, waits for all ranks and merges.
 extern "C" int32_t fusor_cuda_exchange_decode(fusor_cuda_exchange* ex, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
                                               float scale, float* out) {
     if (!ex || !cache || !q || !out) return fail(ex ? ex->ctx : nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument");
@@ -1409,15 +1457,7 @@ extern "C" int32_t fusor_cuda_exchange_decode(fusor_cuda_exchange* ex, fusor_cud
     if (n_rows <= 0 || n_rows * (cache->D + 2) > (long long)ex->slot_floats)
         return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "the records of %lld rows do not fit the exchange slots (%lld floats)", n_rows,
                     (long long)ex->slot_floats);
-    PeerTargets T{};
-    exchange_targets(ex, &T);
-    TRY(decode_impl(ctx, cache, q, scale, nullptr, FUSOR_CUDA_F32, 0, 0, 2, &T));
-    DeviceGuard g(ctx->device);
-    PeerMergeParams M{};
-    exchange_merge_params(ex, &M, n_rows, cache->D, out);
-    const unsigned blocks = (unsigned)std::min<long long>(n_rows, ctx->num_sms);
-    peer_merge_kernel<<<blocks, std::max(32, std::min(cache->D, 256)), 0, ctx->stream>>>(M);
-    return launch_check(ctx, "peer_merge_kernel");
+    return decode_impl(ctx, cache, q, scale, out, FUSOR_CUDA_F32, 0, 0, 2, ex);
 }
 
 // =============================================================================== communicator (tensor-parallel output projection)

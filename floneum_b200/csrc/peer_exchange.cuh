@@ -8,10 +8,10 @@
 //   buffers of one rank:  slots [2 parities][world][slot_floats]   flags [2 parities][world] (uint64 epoch)
 // Epoch e uses parity e & 1: a rank can only push epoch e + 2 after it has seen every peer's flag e + 1, and a peer
 // publishes e + 1 after it has finished reading epoch e, so two parities are enough.
-// Two producers of the records exist: the split-KV decode kernel itself (its last CTA per (sequence, kv head) stores
-// the merged records of that head on every rank: decode_splitkv.cuh, mode 2, followed by peer_merge_kernel) and
-// peer_push_merge_kernel, which takes records the caller already holds and does push, publish, wait and merge in one
-// launch.  Peer memory is only ever written by these kernels, never read.
+// Two producers of the records exist: decode_combine_exchange_kernel (decode_splitkv.cuh), which merges a rank's split-KV
+// records per query head, stores the result on every rank, publishes, waits and merges over the ranks in one launch, and
+// peer_push_merge_kernel, which does the same for records the caller already holds.  Peer memory is only ever written by
+// these kernels, never read.
 // Nothing here waits without a limit: when a peer never publishes, the merge records a time-out and returns.
 #pragma once
 #include <cuda_runtime.h>
@@ -123,14 +123,6 @@ __device__ __forceinline__ void peer_step_done(unsigned long long* epoch, unsign
             __threadfence();
         }
     }
-}
-
-// One block per row, after a kernel that pushed this rank's records (the decode kernel in mode 2).
-__global__ void peer_merge_kernel(const PeerMergeParams P) {
-    const unsigned long long e = *reinterpret_cast<volatile unsigned long long*>(P.epoch) + 1;
-    if (peer_wait_all(P.flags, P.world, e, P.err, P.wait_limit_cycles))
-        for (long long row = blockIdx.x; row < P.n_rows; row += gridDim.x) peer_merge_row(P.slots, P.slot_floats, P.world, e, row, P.D, P.out);
-    peer_step_done(P.epoch, P.done, e);
 }
 
 struct PeerPushMergeParams {

@@ -349,15 +349,11 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 const float m_new = (tmax > m_ref + PF_RESCALE_THRESHOLD) ? tmax : m_ref;  // also taken on the first block
                 const float alpha = (m_new == -INFINITY) ? 1.0f : fast_exp2(m_ref - m_new);
                 m_ref = m_new;
-                if (jj > 0) {
-                    // O must hold block jj-1 before it is rescaled and before any of P(jj) is handed over.  S(jj) is ready,
-                    // so the PV of block jj-1, issued before it on the in-order pipe, has completed: this wait is a formality
-                    // that keeps the phase bookkeeping (every phase observed once).
-                    ok = mbar_wait(pv_done + t, (cb - 1) & 1, abort_flag, P.err, 42 + t);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (__any_sync(0xffffffffu, alpha != 1.0f)) rescale_o_rows(o_tmem, alpha);
-                }
+                // O must hold block jj-1 before it is rescaled and before any of P(jj) is handed over.  It does: S(jj) is
+                // ready, and the PV of block jj-1 was issued before S(jj) on the in-order pipe, so the commit that signalled
+                // S(jj) covers it.  No wait on pv_done here (it is observed once per item, before the epilogue; the barrier
+                // has then completed exactly the phases of all earlier blocks, so the parity of the last one is exact).
+                if (jj > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) rescale_o_rows(o_tmem, alpha);
                 const float m_sub = (m_ref == -INFINITY) ? 0.0f : m_ref;
                 const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_sub, -m_sub);
                 float2 ps0 = make_float2(0.0f, 0.0f), ps1 = make_float2(0.0f, 0.0f);

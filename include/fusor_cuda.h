@@ -223,9 +223,10 @@ int32_t fusor_cuda_kvcache_gather(fusor_cuda_kvcache* cache, const fusor_cuda_te
  * models/kalosm-llama/src/raw/attention_layer.rs:405-448; all-zero mask [1, kv_len]).
  *   q [B,Hq,1,D] (bf16, f16 or f32; rounded to bf16, the type of the cached keys), out [B,Hq,1,D] (f32, bf16 or f16;
  *   rows start on a multiple of four elements).
- * Split-KV in one launch: the pages of all (sequence, kv head) pairs are dealt evenly to a persistent grid by the
- * kernel itself, from the lengths on the device (a step after an append uploads no plan); each CTA emits a partial
- * (m, l, O) per run of pages, and the CTA that completes a (sequence, kv head) merges its partials by log-sum-exp. */
+ * Split-KV: the pages of all (sequence, kv head) pairs are dealt evenly to a persistent grid by the kernel itself, from
+ * the lengths on the device (a step after an append plans and uploads nothing on the host); each CTA emits a partial
+ * (m, l, O) per run of pages, and a second kernel, which finds each head's partials with the same deal, merges them by
+ * log-sum-exp. */
 int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
                                           float scale, const fusor_cuda_tensor4* out);
 /* Same, but leaves the result un-normalised for a merge across GPUs that each hold a chunk of the keys:
@@ -247,8 +248,9 @@ int32_t fusor_cuda_kvcache_set_decode_ctas(fusor_cuda_kvcache* cache, int32_t ct
  *   lse_combine : collective, stream-ordered, one launch (push, publish, wait, merge).  records f32 [n_rows][head_dim + 2]
  *                 = { m (natural-log units), l, O[head_dim] } of this rank -> out f32 [n_rows][head_dim], merged over
  *                 all ranks as fusor_cuda_lse_combine does.
- *   decode      : collective, stream-ordered, two launches: fusor_cuda_flash_attention_decode_partial over this rank's
- *                 chunk of the keys with the records stored on every rank by the decode kernel itself, then the merge.
+ *   decode      : collective, stream-ordered, two launches: the split-KV kernel over this rank's chunk of the keys, then
+ *                 one kernel that merges the rank's records per query head, stores them on every rank, publishes the
+ *                 epoch, waits for all ranks and merges over the ranks.
  *                 q [B,Hq,1,D] is the same on every rank; out f32 [B*Hq][head_dim] is the attention over all ranks' keys.
  *   disconnect / destroy : teardown in two phases.  Every rank calls disconnect (waits for its stream, closes its
  *                 mappings of the other ranks' buffers); the caller then runs a barrier of its own over the ranks;

@@ -27,6 +27,13 @@ def test_library_exports_every_declared_symbol():
     assert sorted(_lib.SIGNATURES) == declared
 
 
+def test_integration_doc_binds_every_declared_symbol():
+    """The Rust `extern "C"` block a maintainer would add names every entry point of the header."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    bound = set(re.findall(r"pub fn (fusor_cuda_[a-z0-9_]+)\(", text))
+    assert sorted(bound) == _declared_symbols()
+
+
 def test_no_cpu_fallback_without_device():
     import torch
     if torch.cuda.is_available():

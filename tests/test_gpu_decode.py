@@ -167,7 +167,7 @@ def test_decode_through_the_reference_call_pattern(device):
         k, v = cache.append(device, T(ks[:, :, t:t + 1]), T(vs[:, :, t:t + 1]))
         before = device.launch_count()
         out = T(qs[:, :, t:t + 1]).flash_attention(k, v, scale, (masks.get_mask(1, t, None, device), fb.MaskKind.QKMask)).as_slice()
-        assert device.launch_count() - before == 2  # split-KV kernel + combine: the pages are read in place
+        assert device.launch_count() - before == 2  # split-KV kernel + merge of its records: the pages are read in place, nothing is planned on the host
         want = O.flash_attention(qs[:, :, t:t + 1], ks[:, :, :t + 1], vs[:, :, :t + 1], scale)
         assert_close(out, want, what=f"decode step {t}")
     # chunked continuation: 3 new tokens on a warm cache (structured.rs:143-150)
@@ -265,8 +265,8 @@ def test_peer_exchange_world_of_one_merges_like_lse_combine(device):
 @pytest.mark.parametrize("ctas", [1, 3, 37, 148, 592])
 def test_decode_grid_sizes_give_the_same_answer(device, ctas):
     """The deal of pages to CTAs is computed inside the kernel from the lengths on the device: any grid size must merge to
-    the same attention (1 CTA: every sequence-head is whole inside it; 592: most are spread over several CTAs and merged
-    by the CTA that finishes last)."""
+    the same attention (1 CTA: every sequence-head is whole inside it and written by it; 592: most are spread over several
+    CTAs and merged by the second kernel, which finds their records with the same deal)."""
     fb = _fb()
     from oracle import workloads as W
     w = W.cfg3(B=6, Hq=16, Hkv=4, lo=30, hi=2500)
@@ -274,7 +274,7 @@ def test_decode_grid_sizes_give_the_same_answer(device, ctas):
     cache.set_decode_ctas(ctas)
     q = fb.Tensor.from_slice(device, w.q.shape, w.q, 1)
     want = _oracle_decode(w)
-    for _ in range(2):  # twice: the per-sequence counters must be back at zero after a launch
+    for _ in range(2):
         assert_close(cache.decode(q, w.scale).as_slice(), want, what=f"decode with {ctas} CTAs")
     # 16-bit outputs and an f16 query tensor
     got_bf16 = cache.decode(q, w.scale, out_dtype=1).as_slice()
@@ -355,8 +355,8 @@ def test_lse_combine_of_empty_rows_gives_zeros(device):
 
 
 def test_exchange_decode_world_of_one(device):
-    """fusor_cuda_exchange_decode with a single rank: the decode kernel's last CTA per (sequence, kv head) stores the
-    merged records into the rank's own slot, the merge kernel waits for its own epoch.  Three steps: both slot parities."""
+    """fusor_cuda_exchange_decode with a single rank: the merge kernel stores the rank's merged records into its own
+    slot, publishes, waits for its own epoch and merges.  Three steps: both slot parities."""
     fb = _fb()
     from oracle import workloads as W
     from floneum_b200.sharding import PeerExchange

@@ -49,7 +49,7 @@ def _worker(rank, world, port, ret):
             full = W.cfg4(Skv=8192)
             want = O.flash_attention(full.q, full.k_dense[0][None], full.v_dense[0][None], full.scale)[:, :, 0]
             for step in range(4):  # several steps: both slot parities, epochs 1..4; both producers of the records
-                if step % 2 == 0:  # the decode kernel stores its records on every rank itself, then the merge
+                if step % 2 == 0:  # split-KV kernel, then one kernel: merge local records, store on every rank, wait, merge
                     ex.decode(cache, q, w.scale, fb.Tensor.from_torch(dev, out))
                 else:              # records the caller holds: push, publish, wait and merge in one launch
                     cache.decode_partial(q, w.scale, fb.Tensor.from_torch(dev, part))
