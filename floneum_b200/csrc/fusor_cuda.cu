@@ -25,7 +25,6 @@
 #include "general_attention.cuh"
 #include "prefill_sm100.cuh"
 #include "prefill2_sm100.cuh"
-#include "prefill3_sm100.cuh"
 #include "oproj_sm100.cuh"
 #include "peer_exchange.cuh"
 #include "rope_append.cuh"
@@ -54,8 +53,6 @@ struct fusor_cuda_ctx {
     unsigned flag_counter = 0;
     // copy streams of the _host entry points (host -> device, device -> host), created on first use
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
-    int max_pairs = 0;      // CTA pairs of prefill3_sm100_kernel that can be resident at once
-    int prefill_kernel = 0; // DEVELOPMENT SWITCH (to be removed): 0 = automatic, 2 = two-tile kernel, 3 = CTA-pair kernel
 };
 
 static thread_local std::string g_last_error;
@@ -155,23 +152,6 @@ extern "C" int32_t fusor_cuda_ctx_create(int32_t device, void* stream, fusor_cud
     // opt in to large dynamic shared memory once per context
     cudaFuncSetAttribute(prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES);
     cudaFuncSetAttribute(prefill2_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM_BYTES);
-    cudaFuncSetAttribute(prefill3_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P3_SMEM_BYTES);
-    {
-        // how many CTA pairs fit at once (a pair needs two SMs of one GPC): the persistent grid is sized to that
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * (unsigned)prop.multiProcessorCount, 1, 1);
-        cfg.blockDim = dim3(P3_THREADS, 1, 1);
-        cfg.dynamicSmemBytes = P3_SMEM_BYTES;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, prefill3_sm100_kernel, &cfg) == cudaSuccess && n > 0) ctx->max_pairs = n;
-        else { cudaGetLastError(); ctx->max_pairs = prop.multiProcessorCount / 2; }
-    }
-    if (const char* pk = std::getenv("FUSOR_DEV_PREFILL_KERNEL")) ctx->prefill_kernel = std::atoi(pk);
     cudaFuncSetAttribute(oproj_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)OP_SMEM_BYTES);
     cudaFuncSetAttribute(decode_splitkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(decode_splitkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -432,13 +412,12 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     // Two query tiles per CTA with 128-key blocks once a (batch, head) has 256 rows or more; the 64-key kernel with
     // two CTAs per SM below that.
     const bool two_tiles = S.Sq >= P2_ROWS;
-    const bool pairs = two_tiles && ctx->prefill_kernel == 3;
-    const int kv_rows = pairs ? 64 : two_tiles ? P2_BN : PF_BN;
+    const int kv_rows = two_tiles ? P2_BN : PF_BN;
     const bool in_f16 = q->dtype == FUSOR_CUDA_F16;  // f16 tensors need no copy of V: the weights are f16 against V itself
     CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
     TRY(make_tmap_bhsd(ctx, &tmQ, q, PF_BM, tmap_dtype(q->dtype)));
     TRY(make_tmap_bhsd(ctx, &tmK, k, kv_rows, tmap_dtype(k->dtype)));
-    TRY(make_tmap_bhsd(ctx, &tmV, v, pairs ? P3_BN : kv_rows, tmap_dtype(v->dtype)));
+    TRY(make_tmap_bhsd(ctx, &tmV, v, kv_rows, tmap_dtype(v->dtype)));
     TRY(make_tmap_bhsd(ctx, &tmO, out, two_tiles ? 32 : PF_BM, tmap_dtype(out->dtype)));
     tmV16 = tmV;
     const int* flag = nullptr;
@@ -464,7 +443,7 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
         fusor_cuda_tensor4 v16 = *v;
         v16.data = ctx->v16;
         set_contiguous(&v16);
-        TRY(make_tmap_bhsd(ctx, &tmV16, &v16, pairs ? P3_BN : kv_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
+        TRY(make_tmap_bhsd(ctx, &tmV16, &v16, kv_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
         flag = ctx->d_flags + slot;
     }
     PrefillParams P{};
@@ -483,11 +462,6 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.kmask_mul = 1.0f / scale;
     const long long grid = (long long)P.n_q_tiles * S.Hq * S.B;
     if (grid > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "grid too large");
-    if (pairs) {
-        const unsigned n_pairs = (unsigned)std::min<long long>(grid, ctx->max_pairs);  // persistent: one CTA pair per two SMs
-        prefill3_sm100_kernel<<<2 * n_pairs, P3_THREADS, P3_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
-        return launch_check(ctx, "prefill3_sm100_kernel");
-    }
     if (two_tiles) {
         const unsigned ctas = (unsigned)std::min<long long>(grid, ctx->num_sms);  // persistent: one CTA per SM
         prefill2_sm100_kernel<<<ctas, P2_THREADS, P2_SMEM_BYTES, ctx->stream>>>(tmQ, tmK, tmV, tmV16, tmO, P);
