@@ -810,9 +810,9 @@ def gpu_arm(args, rank, world, local_rank):
             if key in r:
                 line[key] = r[key]
         line.update(extras)
-        print(json.dumps(line))
     if use_dist:
         dist.destroy_process_group()
+    return line if rank == 0 else None
 
 
 def main():
@@ -840,7 +840,20 @@ def main():
         reference_arm(args, rank)
         return
     args.warmup = max(args.warmup, 3)
-    gpu_arm(args, rank, world, local_rank)
+    # stdout carries the JSON line and nothing else: libraries that print there (NCCL announces its version on stdout when a
+    # communicator is first made) are sent to stderr for the duration of the run
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        line = gpu_arm(args, rank, world, local_rank)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    if line is not None:
+        print(json.dumps(line))
+        sys.stdout.flush()
 
 
 if __name__ == "__main__":
