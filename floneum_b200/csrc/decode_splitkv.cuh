@@ -121,7 +121,7 @@ struct DecodeParams {
     const int* page_table;
     int max_pages;
     int num_pages;
-    const int* kv_len;         // [B] device-resident lengths; every sequence holds at least one token
+    const int* kv_len;         // [B] device-resident lengths; a sequence may be empty when records are asked for (modes 1, 2)
     int B;
     float* part_o;             // [slots][DEC_GP][D], slots >= B * Hkv + grid
     float* part_ml;            // [slots][DEC_GP][2]  (m in log2 units, l)
@@ -139,7 +139,7 @@ __device__ __forceinline__ void decode_emit(const DecodeOutput& R, int D, int g,
     const int h = hk * g + rr, d = dg * 4;
     if (R.mode == 0) {
         const long long idx = (long long)b * R.o_sb + (long long)h * R.o_sh + d;
-        const float inv = 1.0f / L;
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;  // no keys: zeros
         if (R.out_dtype == 0) {
             *reinterpret_cast<float4*>(reinterpret_cast<float*>(R.out) + idx) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         } else {
@@ -525,6 +525,11 @@ __device__ __forceinline__ void decode_head_records(const int* kv_len, int B, in
     }
     const int T = total * Hkv;
     const int pages = (kv_len[b] + DEC_PT - 1) / DEC_PT;
+    if (pages <= 0) {  // an empty sequence (a rank's KV chunk of a short sequence): no CTA holds a record of it
+        first_slot = 0;
+        n_rec = 0;
+        return;
+    }
     const int p0 = Hkv * before + hk * pages;
     const int c_first = decode_page_owner(T, grid, p0), c_last = decode_page_owner(T, grid, p0 + pages - 1);
     first_slot = b * Hkv + hk + c_first;

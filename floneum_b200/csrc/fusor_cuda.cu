@@ -1129,7 +1129,7 @@ extern "C" int32_t fusor_cuda_decode_plan(const int32_t* kv_len, int32_t B, int3
         return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "null argument or non-positive size");
     long long total = 0;
     for (int b = 0; b < B; ++b) {
-        if (kv_len[b] <= 0) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "sequence %d is empty", b);
+        if (kv_len[b] < 0) return fail(nullptr, FUSOR_CUDA_INVALID_ARGUMENT, "kv_len[%d] is negative", b);
         total += (long long)((kv_len[b] + DEC_PT - 1) / DEC_PT) * num_kv_heads;
     }
     static_assert(sizeof(DecodeSegment) == 9 * sizeof(int32_t), "segment record layout");
@@ -1187,7 +1187,9 @@ static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fus
         return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "decode output rows must start on a multiple of four elements");
     long long total = 0;
     for (int b = 0; b < B; ++b) {
-        if (c->h_kv_len[b] <= 0) return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "sequence %d is empty; decode needs at least one cached token", b);
+        // attention over no keys has no value; a partial record of an empty KV chunk does: {m = -inf, l = 0, O = 0}
+        if (c->h_kv_len[b] <= 0 && mode == 0)
+            return fail(ctx, FUSOR_CUDA_INVALID_ARGUMENT, "sequence %d is empty; decode needs at least one cached token", b);
         total += (long long)((c->h_kv_len[b] + DEC_PT - 1) / DEC_PT) * c->Hkv;
     }
     DeviceGuard guard(ctx->device);
@@ -1210,11 +1212,13 @@ static int32_t decode_impl(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* c, const fus
     P.part_o = c->part_o; P.part_ml = c->part_ml;
     P.Hkv = c->Hkv; P.g = g; P.scale_log2 = scale * 1.4426950408889634f; P.ring = ring; P.err = ctx->d_err;
     P.res.out = out; P.res.out_dtype = out_dtype; P.res.o_sb = o_sb; P.res.o_sh = o_sh; P.res.Hq = Hq; P.res.mode = mode;
-    if (c->D == 128)
-        decode_splitkv_kernel<128><<<grid, DEC_THREADS, smem, ctx->stream>>>(c->tmK, c->tmV, P);
-    else
-        decode_splitkv_kernel<64><<<grid, DEC_THREADS, smem, ctx->stream>>>(c->tmK, c->tmV, P);
-    TRY(launch_check(ctx, "decode_splitkv_kernel"));
+    if (total > 0) {  // (every chunk empty: only the merge kernel runs and writes empty records)
+        if (c->D == 128)
+            decode_splitkv_kernel<128><<<grid, DEC_THREADS, smem, ctx->stream>>>(c->tmK, c->tmV, P);
+        else
+            decode_splitkv_kernel<64><<<grid, DEC_THREADS, smem, ctx->stream>>>(c->tmK, c->tmV, P);
+        TRY(launch_check(ctx, "decode_splitkv_kernel"));
+    }
     // merge of the records of every (sequence, kv head) that was spread over several CTAs
     CombineParams C{};
     C.part_o = c->part_o; C.part_ml = c->part_ml; C.kv_len = c->d_kv_len;

@@ -230,7 +230,10 @@ int32_t fusor_cuda_kvcache_gather(fusor_cuda_kvcache* cache, const fusor_cuda_te
 int32_t fusor_cuda_flash_attention_decode(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache, const fusor_cuda_tensor4* q,
                                           float scale, const fusor_cuda_tensor4* out);
 /* Same, but leaves the result un-normalised for a merge across GPUs that each hold a chunk of the keys:
- * partial f32 [B][Hq][D+2] = { m = max scaled score, l = sum exp(s - m), O[D] = sum exp(s - m) v }. */
+ * partial f32 [B][Hq][D+2] = { m = max scaled score, l = sum exp(s - m), O[D] = sum exp(s - m) v }.
+ * A sequence of which this cache holds no key (the chunk of a rank when a sequence is shorter than the number of ranks)
+ * gives the empty record { -inf, 0, 0... }, which the merge skips; fusor_cuda_flash_attention_decode itself rejects
+ * empty sequences (INVALID_ARGUMENT): attention over no keys has no value. */
 int32_t fusor_cuda_flash_attention_decode_partial(fusor_cuda_ctx* ctx, fusor_cuda_kvcache* cache,
                                                   const fusor_cuda_tensor4* q, float scale, float* partial);
 /* Grid size of the decode kernel: 0 (default) = chosen from the number of cached pages, in whole multiples of the SM

@@ -306,6 +306,63 @@ def test_live_decode_steps_need_no_plan(device):
         assert_close(got, want, what=f"live decode step {step}")
 
 
+def test_decode_partial_of_empty_chunks(device):
+    """A sequence shorter than the number of ranks leaves some ranks an empty KV chunk: their partial record is the empty
+    one {-inf, 0, 0...}, the merge over all chunks equals attention over the whole sequence, and the normalising decode
+    still rejects an empty sequence (attention over no keys has no value) without harming the context."""
+    fb = _fb()
+    from floneum_b200 import _lib
+    from floneum_b200.cache import lse_combine
+    from floneum_b200.sharding import kv_chunk_range
+    rng = np.random.default_rng(91)
+    B, Hq, Hkv, D, world = 3, 8, 2, 128, 8
+    lens = [5, 0, 37]  # sequence 1 holds nothing anywhere: zeros after the merge
+    k = [O.bf16_round(rng.standard_normal((Hkv, n, D)).astype(np.float32)) for n in lens]
+    v = [O.bf16_round(rng.standard_normal((Hkv, n, D)).astype(np.float32)) for n in lens]
+    qn = O.bf16_round(rng.standard_normal((B, Hq, 1, D)).astype(np.float32))
+    q = fb.Tensor.from_slice(device, qn.shape, qn, 1)
+    scale = D ** -0.5
+    parts = []
+    for r in range(world):
+        cache = fb.PagedKvCache(device, B, Hkv, D, num_pages=8, max_pages_per_seq=2)
+        table = np.zeros((B, 2), np.int32)
+        kp = np.zeros((8, Hkv, 16, D), np.float32)
+        vp = np.zeros_like(kp)
+        mine, page = [], 0
+        for b in range(B):
+            lo, hi = kv_chunk_range(lens[b], r, world)
+            mine.append(hi - lo)
+            for j in range((hi - lo + 15) // 16):
+                n = min(16, hi - lo - 16 * j)
+                kp[page, :, :n] = k[b][:, lo + 16 * j:lo + 16 * j + n]
+                vp[page, :, :n] = v[b][:, lo + 16 * j:lo + 16 * j + n]
+                table[b, j] = page
+                page += 1
+        cache.write_pages(0, O.bf16_bits(kp), O.bf16_bits(vp))
+        cache.set_page_table(table, np.array(mine, np.int32))
+        rec = cache.decode_partial(q, scale).as_slice()
+        for b in range(B):
+            if mine[b] == 0:
+                assert np.all(rec[b, :, 0] == -np.inf) and np.all(rec[b, :, 1:] == 0), (r, b)
+            else:
+                lo, hi = kv_chunk_range(lens[b], r, world)
+                want = O.attention_partial(qn[b:b + 1], k[b][None], v[b][None], scale, lo, hi)[0, :, 0]
+                assert np.abs(rec[b, :, 0] - want[:, 0]).max() < 1e-4 and np.abs(rec[b, :, 1] / want[:, 1] - 1).max() < 2e-3
+        if any(n == 0 for n in mine):
+            with pytest.raises(fb.FusorCudaError) as e:
+                cache.decode(q, scale)
+            assert e.value.code == _lib.INVALID_ARGUMENT and "empty" in str(e.value)
+        parts.append(rec)
+        cache.close()
+    merged = lse_combine(device, fb.Tensor.from_slice(device, (world,) + parts[0].shape, np.stack(parts))).as_slice()
+    for b in range(B):
+        if lens[b] == 0:
+            assert np.all(merged[b] == 0)
+        else:
+            want = O.flash_attention(qn[b:b + 1], k[b][None], v[b][None], scale)[0, :, 0]
+            assert_close(merged[b], want, what=f"sequence {b} of {lens[b]} keys in {world} chunks")
+
+
 def test_cfg4_full_size_eight_chunks_on_one_gpu(device):
     """BASELINE config 4 at full size (B1 Hq64 Hkv8 D128, 131072 keys) on one GPU: the whole sequence in one call, and as
     the 8 contiguous KV chunks of the multi-GPU partition, each through decode_partial, merged by lse_combine and by the
