@@ -594,11 +594,13 @@ extern "C" int32_t fusor_cuda_flash_attention_host(fusor_cuda_ctx* ctx, const fu
     dout.data = p; p += align256(ob);
     set_contiguous(&dq); set_contiguous(&dk); set_contiguous(&dv); set_contiguous(&dout);
     // Without a mask tensor every (batch, group of kv heads) is an independent problem on contiguous slices of all four
-    // tensors: large calls are cut into about eight such chunks and pipelined over three streams, so the copies in,
+    // tensors: large calls are cut into up to 32 such chunks and pipelined over three streams, so the copies in,
     // the kernels and the copy out of different chunks overlap (PCIe is full duplex) instead of running one after another.
+    // What is not hidden is the first chunk's copy in and the last one's copy out, hence many small chunks: the kernels
+    // of a chunk take far less time than its copies whatever its size.
     const long long chunks_per_batch = [&]() -> long long {
         if (has_mask || qb + kb + vb + ob < (8u << 20)) return 0;
-        long long want = std::max<long long>(1, (8 + S.B - 1) / S.B), best = 1;
+        long long want = std::max<long long>(1, (32 + S.B - 1) / S.B), best = 1;
         for (long long d = 1; d <= S.Hkv && d <= want; ++d)
             if (S.Hkv % d == 0) best = d;
         return S.B * best >= 2 ? best : 0;
