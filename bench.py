@@ -469,10 +469,13 @@ def gpu_arm(args, rank, world, local_rank):
             dist.all_gather_into_tensor(gathered, part)
             lse_combine(dev, tgath, tout3)
 
-        def measure(step, kernels_per_step):
+        def measure(step):
             """Warm-up, one CUDA graph per cache copy (a decode step is launch-bound at small shard sizes), K timed steps."""
             with torch.cuda.stream(stream):
-                for i in range(max(args.warmup, copies)):
+                l0 = dev.launch_count()
+                step(0)
+                kernels_per_step = dev.launch_count() - l0  # the library's own count of its launches in one step
+                for i in range(1, max(args.warmup, copies)):
                     step(i)
                 barrier()
                 graphs = None
@@ -501,7 +504,7 @@ def gpu_arm(args, rank, world, local_rank):
 
         sampler.start()
         t_busy0 = time.time()
-        ms, ms_mine, per_step, launches, graphed = measure(step_main, 2)
+        ms, ms_mine, per_step, launches, graphed = measure(step_main)
         clocks = sampler.stop(t_busy0, time.time())
         res = (out3 if collective else out).float().cpu().numpy().copy()
         bytes_rank = kv_bytes_rank + B * (q1 - q0) * D * 6 + 4 * float(np.sum((w.kv_len + 15) // 16))
@@ -519,13 +522,13 @@ def gpu_arm(args, rank, world, local_rank):
         if tag:
             r["config"]["workload"] += tag
         if collective and with_variants:
-            loc_ms, _, _, _, _ = measure(step_local, 2)
+            loc_ms, _, _, _, _ = measure(step_local)
             r["collective"] = {"local_chunk_only_ms": loc_ms, "step_ms": ms, "share_of_step": max(0.0, 1.0 - loc_ms / ms),
                                "what": "step = split-KV kernel + one kernel that merges the rank's records, stores them on every rank, "
-                                       "waits for all ranks and merges; local_chunk_only = split-KV kernel + local merge, no exchange"}
-            n_ms, _, _, _, _ = measure(step_nccl, 3)
+                                       "waits for all ranks and merges; local_chunk_only = the rank's partial record alone, no exchange"}
+            n_ms, _, _, _, _ = measure(step_nccl)
             r["nccl_gather"] = {"value": bytes_all / (n_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": n_ms,
-                                "what": "decode_partial (two launches) + NCCL all_gather_into_tensor + lse_combine"}
+                                "what": "decode_partial + NCCL all_gather_into_tensor + lse_combine"}
         # e2e: host q up, result down, through the C ABI
         if not args.quick:
             qh = torch.from_numpy(np.ascontiguousarray(qn, dtype=np.float32)).pin_memory()
