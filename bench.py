@@ -35,6 +35,7 @@ import numpy as np  # noqa: E402
 
 METRIC = "attention TFLOP/s (prefill) and KV GB/s (decode) at 1/2/4/8 B200 vs roofline"
 DATA = "synthetic (seeded N(0,1) rounded to bf16; random values, no weights)"
+EXTRAS_DEADLINE_S = 240  # the extras of a multi-rank run take well under a minute when every collective returns
 
 
 def load_peaks():
@@ -260,6 +261,10 @@ def gpu_arm(args, rank, world, local_rank):
     fake_world = args.shard_of if (world == 1 and args.shard_of > 1) else 0
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # The extras run under a deadline (below): a rank may then leave with a collective of another rank still in flight,
+        # which must not happen while its memory is bound to an NVLink multicast object.  In-switch reduction is therefore
+        # off for this program's communicators unless the caller asks for it.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     use_dist = world > 1
     if fake_world:
@@ -302,11 +307,14 @@ def gpu_arm(args, rank, world, local_rank):
             return
         t_end = time.time() + seconds
         i = 0
-        while time.time() < t_end:
+        while True:
             for _ in range(16):
                 step(i)
                 i += 1
             torch.cuda.synchronize()
+            # every rank must run the same number of steps (a step may hold a collective): the ranks agree on going on
+            if max_over_ranks(t_end - time.time()) <= 0.0:
+                break
 
     def timed(step, steps):
         """K steps back to back on the stream between two barriers; returns (total ms max over ranks, this rank's total ms,
@@ -741,6 +749,41 @@ def gpu_arm(args, rank, world, local_rank):
 
     # ----------------------------------------------------------------------- run the selected workload
     extras = {}
+
+    def build_line(r, dtype):
+        if fake_world:
+            r["config"]["shard_of"] = f"rank 0 of a {fake_world}-rank job on one GPU: value is extrapolated as {fake_world} x this shard"
+        line = {"metric": METRIC, "value": r["value"], "unit": r["unit"], "n_gpus": 1 if fake_world else world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": dtype, "data": DATA,
+                "config": r["config"], "roofline": r["roofline"], "e2e": r.get("e2e"), "clocks": r.get("clocks"),
+                "gpu_launches": r["gpu_launches"], "parity": r.get("parity")}
+        for key in ("cpu_baseline", "rank_ms_per_step", "collective", "nccl_gather", "input_copies", "bytes_per_step", "kv_copies", "launch"):
+            if key in r:
+                line[key] = r[key]
+        line.update(extras)
+        return line
+
+    # The extras of a multi-rank run hold collectives (record exchange, NCCL).  Should one of them never return, the
+    # headline measurement, which is complete by then, must still be reported: after EXTRAS_DEADLINE_S every rank leaves,
+    # rank 0 first printing the line with the extras that did finish and the name of the one that did not.
+    deadline = None
+    pending = {"name": None}
+
+    def start_deadline(r, dtype):
+        import threading
+
+        def give_up():
+            if rank == 0:
+                extras[pending["name"] or "extras"] = {"error": f"did not finish within {EXTRAS_DEADLINE_S} s; left out"}
+                os.write(args.real_stdout, (json.dumps(build_line(r, dtype)) + "\n").encode())
+            sys.stderr.write(f"rank {rank}: extras ran past their deadline in {pending['name']}; leaving\n")
+            sys.stderr.flush()
+            os._exit(0)
+        t = threading.Timer(EXTRAS_DEADLINE_S, give_up)
+        t.daemon = True
+        t.start()
+        return t
     name = args.workload
     if name in ("oproj", "rope"):
         r = run_oproj() if name == "oproj" else run_rope()
@@ -775,15 +818,20 @@ def gpu_arm(args, rank, world, local_rank):
                                  "sample": desc, "seconds_per_sample": sec}
         if name == "cfg2" and not args.no_extras and not args.quick and not fake_world:
             # the decode configurations and the step after attention ride on the same line, at every N
+            if use_dist:
+                deadline = start_deadline(r, dtype)
+            pending["name"] = "decode"
             wd = load_cfg3()
             d = decode_parity(run_decode(wd, "cfg3", chunked=False), wd, "cfg3")
             extras["decode"] = d
             del wd
+            pending["name"] = "decode_long"
             mine, full = load_cfg4()
             d4 = decode_parity(run_decode(mine, "cfg4", chunked=True), mine, "cfg4", full)
             extras["decode_long"] = d4
             del mine, full
             if use_dist:
+                pending["name"] = "oproj"
                 extras["oproj"] = run_oproj()
     else:
         if name == "cfg3":
@@ -801,18 +849,9 @@ def gpu_arm(args, rank, world, local_rank):
                                  "sample": desc, "seconds_per_sample": sec}
         dtype = "bf16"
 
-    if rank == 0:
-        if fake_world:
-            r["config"]["shard_of"] = f"rank 0 of a {fake_world}-rank job on one GPU: value is extrapolated as {fake_world} x this shard"
-        line = {"metric": METRIC, "value": r["value"], "unit": r["unit"], "n_gpus": 1 if fake_world else world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": dtype, "data": DATA,
-                "config": r["config"], "roofline": r["roofline"], "e2e": r.get("e2e"), "clocks": r.get("clocks"),
-                "gpu_launches": r["gpu_launches"], "parity": r.get("parity")}
-        for key in ("cpu_baseline", "rank_ms_per_step", "collective", "nccl_gather", "input_copies", "bytes_per_step", "kv_copies", "launch"):
-            if key in r:
-                line[key] = r[key]
-        line.update(extras)
+    if deadline is not None:
+        deadline.cancel()
+    line = build_line(r, dtype) if rank == 0 else None
     if use_dist:
         dist.destroy_process_group()
     return line if rank == 0 else None
@@ -847,6 +886,7 @@ def main():
     # communicator is first made) are sent to stderr for the duration of the run
     sys.stdout.flush()
     real_stdout = os.dup(1)
+    args.real_stdout = real_stdout
     os.dup2(2, 1)
     try:
         line = gpu_arm(args, rank, world, local_rank)
