@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
     uint64_t* v_full = bars + 6;    // [2]
     uint64_t* v_empty = bars + 8;   // [2]
     uint64_t* s_full = bars + 10;   // [2] per tile: S of the tile's next block is in TMEM
-    uint64_t* p_full = bars + 12;   // [2] per tile: the first P2_SPLIT keys of P written (128 arrivals), O rescaled if it had to be
+    uint64_t* p_full = bars + 12;   // [2] per tile: the first P2_SPLIT keys of P written (4 arrivals, one per warp), O rescaled if it had to be
     uint64_t* p_full2 = bars + 18;  // [2] per tile: the remaining keys of P written
     uint64_t* pv_done = bars + 14;  // [2] per tile: O holds every block issued so far
     uint64_t* q_empty = bars + 16;  // [2] per tile: the item's last S = Q K^T of the tile has completed
@@ -136,8 +136,8 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
             mbar_init(v_full + i, 1);
             mbar_init(v_empty + i, 1);
             mbar_init(s_full + i, 1);
-            mbar_init(p_full + i, 128);
-            mbar_init(p_full2 + i, 128);
+            mbar_init(p_full + i, 4);   // one arrival per softmax warp of the tile, made by a lane after the warp's stores are complete
+            mbar_init(p_full2 + i, 4);
             mbar_init(pv_done + i, 1);
         }
         *abort_flag = 0;
@@ -394,7 +394,8 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                         if (g == P2_SPLIT / 4 - 1) {  // keys 0 .. P2_SPLIT-1 are in place: the MMA warp may start on them
                             tc_wait_st();
                             tc_fence_before();
-                            mbar_arrive(p_full + t);
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(p_full + t);
                         }
                     }
                 }
@@ -405,7 +406,8 @@ __global__ void __launch_bounds__(P2_THREADS, 1)
                 l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
                 tc_wait_st();
                 tc_fence_before();
-                mbar_arrive(p_full2 + t);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full2 + t);
             }
             if (ok && nb > 0) ok = mbar_wait(pv_done + t, (cb - 1) & 1, abort_flag, P.err, 44 + t);
             // Epilogue, per warp: 32 rows x 128 bytes of O / l at a time through this warp's staging area, TMA store.
