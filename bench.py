@@ -774,7 +774,7 @@ def gpu_arm(args, rank, world, local_rank):
         import threading
 
         def give_up():
-            if rank == 0:
+            if rank == 0 and not pending.get("printed"):
                 extras[pending["name"] or "extras"] = {"error": f"did not finish within {EXTRAS_DEADLINE_S} s; left out"}
                 os.write(args.real_stdout, (json.dumps(build_line(r, dtype)) + "\n").encode())
             sys.stderr.write(f"rank {rank}: extras ran past their deadline in {pending['name']}; leaving\n")
@@ -820,19 +820,26 @@ def gpu_arm(args, rank, world, local_rank):
             # the decode configurations and the step after attention ride on the same line, at every N
             if use_dist:
                 deadline = start_deadline(r, dtype)
-            pending["name"] = "decode"
-            wd = load_cfg3()
-            d = decode_parity(run_decode(wd, "cfg3", chunked=False), wd, "cfg3")
-            extras["decode"] = d
-            del wd
-            pending["name"] = "decode_long"
-            mine, full = load_cfg4()
-            d4 = decode_parity(run_decode(mine, "cfg4", chunked=True), mine, "cfg4", full)
-            extras["decode_long"] = d4
-            del mine, full
-            if use_dist:
-                pending["name"] = "oproj"
-                extras["oproj"] = run_oproj()
+            try:
+                pending["name"] = "decode"
+                wd = load_cfg3()
+                d = decode_parity(run_decode(wd, "cfg3", chunked=False), wd, "cfg3")
+                extras["decode"] = d
+                del wd
+                pending["name"] = "decode_long"
+                mine, full = load_cfg4()
+                d4 = decode_parity(run_decode(mine, "cfg4", chunked=True), mine, "cfg4", full)
+                extras["decode_long"] = d4
+                del mine, full
+                if use_dist:
+                    pending["name"] = "oproj"
+                    extras["oproj"] = run_oproj()
+            except Exception as e:  # an extra must not take the headline measurement with it
+                if not use_dist:
+                    raise
+                import traceback
+                traceback.print_exc()
+                extras[pending["name"]] = {"error": f"{type(e).__name__}: {e}"}
     else:
         if name == "cfg3":
             w = load_cfg3()
@@ -849,11 +856,18 @@ def gpu_arm(args, rank, world, local_rank):
                                  "sample": desc, "seconds_per_sample": sec}
         dtype = "bf16"
 
-    if deadline is not None:
-        deadline.cancel()
     line = build_line(r, dtype) if rank == 0 else None
     if use_dist:
+        # the line leaves before the teardown, which is a collective of its own and stays under the deadline
+        if rank == 0:
+            pending["printed"] = True
+            os.write(args.real_stdout, (json.dumps(line) + "\n").encode())
+            line = None
+        if deadline is None:
+            deadline = start_deadline(r, dtype)
         dist.destroy_process_group()
+    if deadline is not None:
+        deadline.cancel()
     return line if rank == 0 else None
 
 
