@@ -393,8 +393,8 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
                              const fusor_cuda_tensor4* v, float scale, int32_t mask_kind, const fusor_cuda_tensor4* out,
                              const fusor_cuda_tensor2* mask = nullptr) {
     if (S.D != PF_D) return false;
-    if (mask_kind == FUSOR_CUDA_MASK_BATCH_KEY) {
-        // [B, Skv] additive key mask with contiguous rows
+    if (mask_kind == FUSOR_CUDA_MASK_BATCH_KEY || mask_kind == FUSOR_CUDA_MASK_QK) {
+        // [B, Skv] additive key mask or [Sq, Skv] additive mask, rows contiguous
         if (!mask || mask->stride[1] != 1) return false;
     } else if (!(mask_kind == FUSOR_CUDA_MASK_NONE || mask_kind == FUSOR_CUDA_MASK_CAUSAL || mask_kind == FUSOR_CUDA_MASK_SLIDING)) {
         return false;
@@ -413,10 +413,12 @@ static bool prefill_eligible(const AttnShape& S, const fusor_cuda_tensor4* q, co
 // the device when some |v| does not fit f16).
 static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fusor_cuda_tensor4* q,
                               const fusor_cuda_tensor4* k, const fusor_cuda_tensor4* v, float scale, int32_t mask_kind,
-                              const fusor_cuda_tensor4* out, int window = 0, const fusor_cuda_tensor2* key_mask = nullptr) {
+                              const fusor_cuda_tensor4* out, int window = 0, const fusor_cuda_tensor2* key_mask = nullptr,
+                              const fusor_cuda_tensor2* qk_mask = nullptr) {
     // Two query tiles per CTA with 128-key blocks once a (batch, head) has 256 rows or more; the 64-key kernel with
-    // two CTAs per SM below that.
-    const bool two_tiles = S.Sq >= P2_ROWS;
+    // two CTAs per SM below that, and for calls with an additive [Sq, Skv] mask tensor (each softmax thread then reads a
+    // row of mask values per tile: the 64-key kernel has the registers for it).
+    const bool two_tiles = S.Sq >= P2_ROWS && qk_mask == nullptr;
     const int kv_rows = two_tiles ? P2_BN : PF_BN;
     const bool in_f16 = q->dtype == FUSOR_CUDA_F16;  // f16 tensors need no copy of V: the weights are f16 against V itself
     CUtensorMap tmQ, tmK, tmV, tmV16, tmO;
@@ -465,6 +467,8 @@ static int32_t launch_prefill(fusor_cuda_ctx* ctx, const AttnShape& S, const fus
     P.kmask = key_mask ? static_cast<const float*>(key_mask->data) : nullptr;
     P.kmask_stride = key_mask ? key_mask->stride[0] : 0;
     P.kmask_mul = 1.0f / scale;
+    P.qkmask = qk_mask ? static_cast<const float*>(qk_mask->data) : nullptr;
+    P.qkmask_stride = qk_mask ? qk_mask->stride[0] : 0;
     const long long grid = (long long)P.n_q_tiles * S.Hq * S.B;
     if (grid > 0x7fffffffLL) return fail(ctx, FUSOR_CUDA_UNSUPPORTED, "grid too large");
     if (two_tiles) {
@@ -484,7 +488,8 @@ extern "C" int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_c
     DeviceGuard g(ctx->device);
     if (prefill_eligible(S, q, k, v, scale, mask_kind, out, mask))
         return launch_prefill(ctx, S, q, k, v, scale, mask_kind, out, window,
-                              mask_kind == FUSOR_CUDA_MASK_BATCH_KEY ? mask : nullptr);
+                              mask_kind == FUSOR_CUDA_MASK_BATCH_KEY ? mask : nullptr,
+                              mask_kind == FUSOR_CUDA_MASK_QK ? mask : nullptr);
     return launch_general(ctx, S, q, k, v, scale, mask, mask_kind, window, out);
 }
 

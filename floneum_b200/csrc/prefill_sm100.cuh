@@ -63,6 +63,8 @@ struct PrefillParams {
     const float* kmask;        // optional additive key mask [B][Skv] f32 (MaskKind::BatchKeyMask), added to the scaled scores
     long long kmask_stride;    // elements between batches
     float kmask_mul;           // 1 / scale: the mask is added to the raw scores as mask / scale, before the common scaling
+    const float* qkmask;       // optional additive mask [Sq][Skv] f32 (MaskKind::QKMask), shared by batches and heads; 64-key kernel only
+    long long qkmask_stride;   // elements between query rows
 };
 
 constexpr size_t PF_SMEM_BYTES = 1024 + (size_t)PF_Q_BYTES + 2 * PF_SBUF * (size_t)PF_KV_BYTES + 512 + 6 * 128 * 4;
@@ -245,6 +247,13 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
                 const float* mk = P.kmask + (long long)b * P.kmask_stride;
 #pragma unroll
                 for (int i = 0; i < PF_CPT; ++i) s[i] = fmaf(__ldg(mk + min(k0 + i, P.Skv - 1)), P.kmask_mul, s[i]);
+            }
+            if (P.qkmask != nullptr) {
+                // additive [Sq, Skv] mask tensor: each thread reads its own row's values for this tile (-inf entries give
+                // -inf scores, which the code below treats like keys outside a window); no tile can be skipped
+                const float* mr = P.qkmask + (long long)min(qi, P.Sq - 1) * P.qkmask_stride;
+#pragma unroll
+                for (int i = 0; i < PF_CPT; ++i) s[i] = fmaf(__ldg(mr + min(k0 + i, P.Skv - 1)), P.kmask_mul, s[i]);
             }
             if (k0 + PF_CPT - 1 > k_limit || k0 < k_first) {  // diagonal, ragged or window-edge tile: mask in the raw domain
 #pragma unroll

@@ -104,10 +104,11 @@ int32_t fusor_cuda_cast(fusor_cuda_ctx* ctx, void* dst, int32_t dst_dtype, const
  * (fusor-ml/core/src/composite/flash_attention.rs:28-52,56-557).
  *   q [B,Hq,Sq,D], k and v [B,Hkv,Skv,D], out [B,Hq,Sq,D]; Hq % Hkv == 0, query head h reads kv head h/(Hq/Hkv).
  *   out = softmax(q k^T * scale + mask) v, f32 accumulation.
- * Dispatch: q/k/v all bf16 or all f16 with D == 128 and an analytic mask (NONE / CAUSAL / SLIDING) or a [B, Skv] key
- * mask (MASK_BATCH_KEY, rows contiguous) run the tcgen05 tensor-core kernels (two query tiles per CTA from Sq = 256,
- * one below); everything else (f32 inputs, mixed types, any other D <= 256, [Sq, Skv] mask tensors) runs the general
- * kernel in f32 arithmetic.  out dtype f32, bf16 or f16.  `mask` is read only for MASK_QK / MASK_BATCH_KEY;
+ * Dispatch: q/k/v all bf16 or all f16 with D == 128 run the tcgen05 tensor-core kernels: two query tiles per CTA from
+ * Sq = 256 and one below for an analytic mask (NONE / CAUSAL / SLIDING) or a [B, Skv] key mask (MASK_BATCH_KEY, rows
+ * contiguous); the one-tile kernel at any Sq for an additive [Sq, Skv] mask tensor (MASK_QK, rows contiguous; every key
+ * tile is visited and each row reads its mask values).  Everything else (f32 inputs, mixed types, any other D <= 256,
+ * strided mask rows) runs the general kernel in f32 arithmetic.  out dtype f32, bf16 or f16.  `mask` is read only for MASK_QK / MASK_BATCH_KEY;
  * `window` only for MASK_SLIDING. */
 int32_t fusor_cuda_flash_attention(fusor_cuda_ctx* ctx, const fusor_cuda_tensor4* q, const fusor_cuda_tensor4* k,
                                    const fusor_cuda_tensor4* v, float scale, const fusor_cuda_tensor2* mask,

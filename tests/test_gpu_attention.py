@@ -218,6 +218,45 @@ def test_prefill_sliding_window_tensor_core(device, Sq, off, w):
     assert_close(got, want, what=f"sliding window {Sq},{off},{w}")
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,kind", [
+    (1, 4, 4, 64, 64, "causal"), (2, 8, 2, 300, 300, "causal"), (1, 4, 1, 130, 257, "offset"), (1, 2, 2, 513, 513, "window"),
+    (1, 4, 2, 77, 200, "dense"), (1, 2, 1, 1, 90, "dense"),
+])
+def test_additive_mask_tensor_on_the_tensor_core_kernel(device, B, Hq, Hkv, Sq, Skv, kind):
+    """The reference's main fuzz pattern (a causal mask with random +-0.25 on the allowed part, passed as a plain [Sq, Skv]
+    tensor, so nothing about it is analytic) on bf16 tensors of head_dim 128: the call runs on the tensor-core kernel (two
+    launches: the V pre-pass and the 64-key kernel, also from 256 rows on), rows whose first key tiles are entirely masked
+    included, and agrees with the oracle and with the f32-arithmetic kernel."""
+    import ctypes
+    fb = _mods()
+    from floneum_b200 import _lib
+    rng = np.random.default_rng(5000 + Sq + Skv)
+    q, k, v, scale = _bf16_case(31 * Sq + Skv, B, Hq, Hkv, Sq, Skv)
+    if kind == "dense":
+        base = np.zeros((Sq, Skv), np.float32)
+    elif kind == "window":
+        base = O.get_mask(Sq, Skv - Sq, 100)  # the leading key tiles of later rows are all -inf
+    else:
+        base = O.get_mask(Sq, Skv - Sq, None)
+    mask = np.where(np.isinf(base), base, rng.uniform(-0.25, 0.25, base.shape).astype(np.float32)).astype(np.float32)
+    want = O.flash_attention(q, k, v, scale, mask, O.MASK_QK)
+    tm = fb.Tensor.from_slice(device, mask.shape, mask)
+    before = device.launch_count()
+    got = _run(device, q, k, v, scale, (tm, fb.MaskKind.QKMask), dtype=1)
+    # upload of three tensors costs no kernel; the attention is the pre-pass + the 64-key tensor-core kernel
+    assert device.launch_count() - before == 2
+    assert_close(got, want, what=f"additive mask {kind} {B}x{Hq}/{Hkv}x{Sq}/{Skv}")
+    # the f32-arithmetic kernel on the same inputs
+    L = _lib.load()
+    tq, tk, tv = (fb.Tensor.from_slice(device, a.shape, a, 1) for a in (q, k, v))
+    out = fb.Tensor.empty(device, q.shape, 0)
+    cq, ck, cv, co, cm = tq._c4(), tk._c4(), tv._c4(), out._c4(), tm._c2()
+    _lib.check(L.fusor_cuda_flash_attention_general(device.handle, ctypes.byref(cq), ctypes.byref(ck), ctypes.byref(cv),
+                                                    ctypes.c_float(scale), ctypes.byref(cm), _lib.MASK_QK, 0, ctypes.byref(co)),
+               device.handle)
+    assert_close(got, out.as_slice(), what="tensor-core against general kernel")
+
+
 def test_prefill_golden_fixture(device):
     fb = _mods()
     z = np.load(__file__.replace("test_gpu_attention.py", "golden/seeded_bf16_d128_causal.npz"))
@@ -310,7 +349,7 @@ def test_prefill_value_overflowing_f16_falls_back(device):
     fb = _mods()
     q, k, v, scale = _bf16_case(77, 1, 2, 1, 512, 512)
     v = v.copy()
-    v[0, 0, 3, 5] = O.bf16_round(np.float32(1.0e5))
+    v[0, 0, 3, 5] = float(np.ravel(O.bf16_round(np.float32(1.0e5)))[0])
     mask = (fb.MaskCache().get_mask(512, 0, None, device), fb.MaskKind.QKMask)
     got = _run(device, q, k, v, scale, mask, dtype=1)
     want = O.flash_attention(q, k, v, scale, mask_kind=O.MASK_CAUSAL, skip_masked=True)
