@@ -248,6 +248,26 @@ def t4(ptr, shape, dtype, strides=None):
     return t
 
 
+def start_exit_timer(seconds, rank, stdout_fd, last_line, where=lambda: None):
+    """After `seconds` the process leaves with exit code 0: rank 0 first writes the JSON line `last_line()` returns (unless
+    it returns None) to `stdout_fd`.  Returns the timer; cancel() it when the guarded part has finished.  The timer thread
+    runs while the main thread sits in a blocking CUDA or NCCL call (those release the interpreter lock)."""
+    import threading
+
+    def give_up():
+        if rank == 0:
+            line = last_line()
+            if line is not None:
+                os.write(stdout_fd, (json.dumps(line) + "\n").encode())
+        sys.stderr.write(f"rank {rank}: ran past the deadline of {seconds} s in {where()}; leaving\n")
+        sys.stderr.flush()
+        os._exit(0)
+    t = threading.Timer(seconds, give_up)
+    t.daemon = True
+    t.start()
+    return t
+
+
 def gpu_arm(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -771,19 +791,12 @@ def gpu_arm(args, rank, world, local_rank):
     pending = {"name": None}
 
     def start_deadline(r, dtype):
-        import threading
-
-        def give_up():
-            if rank == 0 and not pending.get("printed"):
-                extras[pending["name"] or "extras"] = {"error": f"did not finish within {EXTRAS_DEADLINE_S} s; left out"}
-                os.write(args.real_stdout, (json.dumps(build_line(r, dtype)) + "\n").encode())
-            sys.stderr.write(f"rank {rank}: extras ran past their deadline in {pending['name']}; leaving\n")
-            sys.stderr.flush()
-            os._exit(0)
-        t = threading.Timer(EXTRAS_DEADLINE_S, give_up)
-        t.daemon = True
-        t.start()
-        return t
+        def last_line():
+            if pending.get("printed"):
+                return None
+            extras[pending["name"] or "extras"] = {"error": f"did not finish within {EXTRAS_DEADLINE_S} s; left out"}
+            return build_line(r, dtype)
+        return start_exit_timer(EXTRAS_DEADLINE_S, rank, args.real_stdout, last_line, lambda: pending["name"])
     name = args.workload
     if name in ("oproj", "rope"):
         r = run_oproj() if name == "oproj" else run_rope()
