@@ -550,15 +550,18 @@ def gpu_arm(args, rank, world, local_rank):
         if tag:
             r["config"]["workload"] += tag
         if collective and with_variants:
+            phase(f"{name}: the rank's chunk alone")
             loc_ms, _, _, _, _ = measure(step_local)
             r["collective"] = {"local_chunk_only_ms": loc_ms, "step_ms": ms, "share_of_step": max(0.0, 1.0 - loc_ms / ms),
                                "what": "step = split-KV kernel + one kernel that merges the rank's records, stores them on every rank, "
                                        "waits for all ranks and merges; local_chunk_only = the rank's partial record alone, no exchange"}
+            phase(f"{name}: NCCL all-gather variant")
             n_ms, _, _, _, _ = measure(step_nccl)
             r["nccl_gather"] = {"value": bytes_all / (n_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": n_ms,
                                 "what": "decode_partial + NCCL all_gather_into_tensor + lse_combine"}
         # e2e: host q up, result down, through the C ABI
         if not args.quick:
+            phase(f"{name}: host-buffer steps")
             qh = torch.from_numpy(np.ascontiguousarray(qn, dtype=np.float32)).pin_memory()
             host_out = torch.empty(qn.shape if not collective else (B, Hq, D), dtype=torch.float32).pin_memory()
             if not collective:
@@ -769,6 +772,7 @@ def gpu_arm(args, rank, world, local_rank):
 
     # ----------------------------------------------------------------------- run the selected workload
     extras = {}
+    t_start = time.time()
 
     def build_line(r, dtype):
         if fake_world:
@@ -789,6 +793,13 @@ def gpu_arm(args, rank, world, local_rank):
     # rank 0 first printing the line with the extras that did finish and the name of the one that did not.
     deadline = None
     pending = {"name": None}
+
+    def phase(name):
+        """Names the part that runs next (the deadline reports it) and leaves a trace of progress on stderr."""
+        pending["name"] = name
+        if rank == 0:
+            sys.stderr.write(f"[bench] {name} starts at {time.time() - t_start:.1f} s\n")
+            sys.stderr.flush()
 
     def start_deadline(r, dtype):
         def last_line():
@@ -834,18 +845,18 @@ def gpu_arm(args, rank, world, local_rank):
             if use_dist:
                 deadline = start_deadline(r, dtype)
             try:
-                pending["name"] = "decode"
+                phase("decode")
                 wd = load_cfg3()
                 d = decode_parity(run_decode(wd, "cfg3", chunked=False), wd, "cfg3")
                 extras["decode"] = d
                 del wd
-                pending["name"] = "decode_long"
+                phase("decode_long")
                 mine, full = load_cfg4()
                 d4 = decode_parity(run_decode(mine, "cfg4", chunked=True), mine, "cfg4", full)
                 extras["decode_long"] = d4
                 del mine, full
                 if use_dist:
-                    pending["name"] = "oproj"
+                    phase("oproj")
                     extras["oproj"] = run_oproj()
             except Exception as e:  # an extra must not take the headline measurement with it
                 if not use_dist:
