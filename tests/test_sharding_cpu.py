@@ -32,6 +32,25 @@ def test_partition_helpers():
         assert max(sizes) - min(sizes) <= 1
 
 
+def test_kv_chunks_of_a_sequence_shorter_than_the_world():
+    """Five keys over eight ranks: three ranks hold nothing, their partial record is the empty one {-inf, 0, 0...}, and
+    the merge of all eight records is the attention over the five keys (the rule the GPU path follows for empty chunks)."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((1, 4, 1, 16)).astype(np.float32)
+    k, v = (rng.standard_normal((1, 2, 5, 16)).astype(np.float32) for _ in range(2))
+    parts, empty = [], 0
+    for r in range(8):
+        lo, hi = sharding.kv_chunk_range(5, r, 8)
+        p = O.attention_partial(q, k, v, 0.25, lo, hi)[:, :, 0]
+        if lo == hi:
+            empty += 1
+            assert np.all(p[..., 0] == -np.inf) and np.all(p[..., 1:] == 0)
+        parts.append(p)
+    assert empty == 3
+    assert np.abs(O.lse_combine(np.stack(parts)) - O.flash_attention(q, k, v, 0.25)[:, :, 0]).max() < 1e-6
+
+
 def _worker(rank, world, port, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
