@@ -430,6 +430,17 @@ def test_exchange_decode_world_of_one(device):
         out = fb.Tensor.zeros(device, (B, Hq, D))
         ex.decode(cache, q, w.scale, out)
         assert_close(out.as_slice(), want, what=f"exchange decode, {ctas} CTAs")
+    # a rank whose chunk of every sequence is empty only runs the merge kernel: its records are the empty ones, and with
+    # no other rank the merged result is zeros (two steps: both slot parities again)
+    none = fb.PagedKvCache(device, B, w.k_pages.shape[1], D, num_pages=2, max_pages_per_seq=1)
+    none.set_page_table(np.zeros((B, 1), np.int32), np.zeros(B, np.int32))
+    for _ in range(2):
+        out = fb.Tensor.from_slice(device, (B, Hq, D), np.full((B, Hq, D), 7.0, np.float32))
+        before = device.launch_count()
+        ex.decode(none, q, w.scale, out)
+        assert device.launch_count() - before == 1
+        assert np.all(out.as_slice() == 0)
+    none.close()
     ex.close()
 
 
