@@ -262,7 +262,8 @@ def start_exit_timer(seconds, rank, stdout_fd, last_line, where=lambda: None):
         sys.stderr.write(f"rank {rank}: ran past the deadline of {seconds} s in {where()}; leaving\n")
         sys.stderr.flush()
         os._exit(0)
-    t = threading.Timer(seconds, give_up)
+    # (the other ranks leave two seconds after rank 0, so that nothing of their going can reach it before the line is out)
+    t = threading.Timer(seconds if rank == 0 else seconds + 2.0, give_up)
     t.daemon = True
     t.start()
     return t
