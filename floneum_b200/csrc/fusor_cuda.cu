@@ -1477,7 +1477,8 @@ static const NcclApi* nccl_api() {
     if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // the copy the host program already uses
     if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
     if (!h) {
-        g_nccl.error = std::string("libnccl.so.2 cannot be loaded: ") + (dlerror() ? dlerror() : "unknown error");
+        const char* why = dlerror();  // (a second call would return null: the first one clears the message)
+        g_nccl.error = std::string("libnccl.so.2 cannot be loaded: ") + (why ? why : "unknown error");
         return nullptr;
     }
     auto sym = [&](const char* name) { return dlsym(h, name); };
