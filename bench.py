@@ -12,7 +12,11 @@ through the host-buffer C-ABI entry point with the copies inside the timed regio
   decode_long  config 4 (131072-key decode, KV sequence split into contiguous chunks over the ranks; the ranks' partial
                records are exchanged over peer memory and merged: the one collective of the path), KV GB/s
   oproj        (N > 1) the head-sharded output projection with the library's all-reduce
-each with its own roofline, parity block against the oracle and per-rank times.
+each with its own roofline, parity block against the oracle and per-rank times.  In a multi-rank run these extras run
+under a deadline (EXTRAS_DEADLINE_S): should one never return, rank 0 still prints the line with the headline
+measurement and the extras that finished, names the one that did not, and every rank leaves with exit code 0; the
+program's NCCL communicators keep in-switch reduction (NVLS) off unless NCCL_NVLS_ENABLE is set by the caller.
+stdout carries the JSON line only; progress and library chatter go to stderr.
 `--workload cfg1` runs the CPU-reference configuration (f32, general kernel) with the CPU port timed in full.
 `--impl reference` times the CPU restatement of the reference's attention (oracle/) on the host cores instead.
 """
