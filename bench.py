@@ -710,7 +710,7 @@ def gpu_arm(args, rank, world, local_rank):
         if gemm_ms is not None:
             out_bytes = out.numel() * 4
             r["collective"] = {"gemm_only_ms": gemm_ms, "step_ms": ms, "share_of_step": max(0.0, 1.0 - gemm_ms / ms),
-                               "all_reduce_bytes_per_rank": out_bytes,
+                               "all_reduce_bytes_per_rank": out_bytes, "NCCL_NVLS_ENABLE": os.environ.get("NCCL_NVLS_ENABLE", "unset"),
                                "what": "NCCL all-reduce of the f32 partial sums behind fusor_cuda_attention_out_proj_all_reduce"}
         return r
 
