@@ -115,6 +115,20 @@ def test_decode_plan_partitions_every_page_once_and_evenly(kv_len, Hkv, grid):
         assert sorted(s[5] for s in lst) == list(range(first, first + n_rec))
 
 
+def test_decode_plan_seeded_fuzz():
+    """The same properties on 60 seeded random cases: ragged lengths with empty sequences among them, 1-8 kv heads, grids
+    from one CTA to four per SM, and grids larger than the number of pages clipped as the host does."""
+    rng = np.random.default_rng(424242)
+    for _ in range(60):
+        B = int(rng.integers(1, 40))
+        kv_len = [int(x) for x in rng.integers(0, int(rng.choice([3, 40, 700, 9000])), B)]
+        if sum(kv_len) == 0:
+            kv_len[0] = 1
+        Hkv = int(rng.integers(1, 9))
+        grid = int(rng.choice([1, 2, 7, 148, 296, 592]))
+        test_decode_plan_partitions_every_page_once_and_evenly(kv_len, Hkv, grid)
+
+
 def test_decode_plan_rejects_bad_input():
     from floneum_b200 import _lib
     L = _lib.load()
